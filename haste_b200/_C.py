@@ -1,0 +1,100 @@
+"""ctypes binding of libhaste_b200.so (the C ABI declared in include/haste_b200.h).
+
+The library is built in-tree by `haste_b200.build`.  There is no fallback: if the
+shared object is missing or a call fails, an exception is raised.
+"""
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libhaste_b200.so")
+
+F32, BF16 = 0, 1
+PATH_AUTO, PATH_STEPWISE, PATH_PERSISTENT = 0, 1, 2
+GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05 = 0, 1, 2
+
+_i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
+
+# name -> argument types, in the order of include/haste_b200.h
+SIGNATURES = {
+    "haste_b200_lstm_forward": [_i] * 6 + [_p] * 8 + [_f, _p, _p],
+    "haste_b200_lstm_backward": [_i] * 6 + [_p] * 17,
+    "haste_b200_gru_forward": [_i] * 6 + [_p] * 9 + [_f, _p, _p],
+    "haste_b200_gru_backward": [_i] * 6 + [_p] * 18,
+    "haste_b200_indrnn_forward": [_i] * 6 + [_p] * 6 + [_f, _p, _p],
+    "haste_b200_indrnn_backward": [_i] * 6 + [_p] * 14,
+    "haste_b200_layer_norm_forward": [_i] * 3 + [_p] * 6,
+    "haste_b200_layer_norm_backward": [_i] * 3 + [_p] * 8,
+    "haste_b200_layer_norm_lstm_forward": [_i] * 6 + [_p] * 17 + [_f, _p, _p],
+    "haste_b200_layer_norm_lstm_backward": [_i] * 6 + [_p] * 29,
+    "haste_b200_layer_norm_gru_forward": [_i] * 6 + [_p] * 14 + [_f, _p, _p],
+    "haste_b200_layer_norm_gru_backward": [_i] * 6 + [_p] * 24,
+    "haste_b200_layer_norm_indrnn_forward": [_i] * 6 + [_p] * 9 + [_f, _p, _p],
+    "haste_b200_layer_norm_indrnn_backward": [_i] * 6 + [_p] * 18,
+    "haste_b200_gemm": [_i] * 4 + [_p, _ll, _ll, _p, _ll, _ll, _p, _ll, _i, _p],
+    "haste_b200_set_recurrence_path": [_i],
+    "haste_b200_set_gemm_path": [_i],
+    "haste_b200_profile_enable": [_i],
+    "haste_b200_profile_read": [_p, _i],
+}
+OTHER_SYMBOLS = ["haste_b200_last_error", "haste_b200_version", "haste_b200_launch_count"]
+
+_lib = None
+
+
+class HasteError(RuntimeError):
+    pass
+
+
+def lib():
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise ImportError(
+                f"{LIB_PATH} not found: build it with `python -m haste_b200.build` "
+                "(there is no CPU or PyTorch fallback)")
+        L = ctypes.CDLL(LIB_PATH)
+        for name, args in SIGNATURES.items():
+            fn = getattr(L, name)
+            fn.argtypes = args
+            fn.restype = _i
+        L.haste_b200_last_error.restype = ctypes.c_char_p
+        L.haste_b200_version.restype = ctypes.c_char_p
+        L.haste_b200_launch_count.restype = _ll
+        _lib = L
+    return _lib
+
+
+def call(name, *args):
+    L = lib()
+    status = getattr(L, name)(*args)
+    if status != 0:
+        msg = L.haste_b200_last_error().decode()
+        raise HasteError(f"{name} failed with status {status}: {msg}")
+
+
+def launch_count():
+    return int(lib().haste_b200_launch_count())
+
+
+def set_recurrence_path(path):
+    call("haste_b200_set_recurrence_path", path)
+
+
+def set_gemm_path(path):
+    call("haste_b200_set_gemm_path", path)
+
+
+PHASES = ["input_projection", "recurrence_fwd", "recurrence_bwd", "weight_grad", "input_grad",
+          "other"]
+
+
+def profile_enable(on=True):
+    call("haste_b200_profile_enable", int(on))
+
+
+def profile_read():
+    """ms per phase since the last read, as a dict keyed by PHASES."""
+    buf = (ctypes.c_float * len(PHASES))()
+    call("haste_b200_profile_read", ctypes.cast(buf, ctypes.c_void_p), len(PHASES))
+    return dict(zip(PHASES, [float(v) for v in buf]))

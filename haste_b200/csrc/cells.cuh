@@ -1,0 +1,120 @@
+// Argument blocks and driver entry points of the six cells (internal C++ layer
+// directly under the C ABI of include/haste_b200.h; field meanings are documented
+// there).
+#pragma once
+
+#include "common.cuh"
+#include "util.cuh"
+
+namespace hb {
+
+struct LstmFwd {
+  int dtype, training, T, N, C, H;
+  const void *W, *R, *b, *x;
+  void *h, *c, *v, *tmp_Rh;
+  float zoneout_prob;
+  const void* zoneout_mask;
+};
+struct LstmBwd {
+  int dtype, transposed_inputs, T, N, C, H;
+  const void *W, *R, *b, *x, *h, *c, *dh_new, *dc_new;
+  void *dx, *dW, *dR, *db, *dh, *dc, *v;
+  const void* zoneout_mask;
+};
+struct GruFwd {
+  int dtype, training, T, N, C, H;
+  const void *W, *R, *bx, *br, *x;
+  void *h, *v, *tmp_Wx, *tmp_Rh;
+  float zoneout_prob;
+  const void* zoneout_mask;
+};
+struct GruBwd {
+  int dtype, transposed_inputs, T, N, C, H;
+  const void *W, *R, *bx, *br, *x, *h, *v, *dh_new;
+  void *dx, *dW, *dR, *dbx, *dbr, *dh, *dp, *dq;
+  const void* zoneout_mask;
+};
+struct IndrnnFwd {
+  int dtype, training, T, N, C, H;
+  const void *W, *u, *b, *x;
+  void *h, *workspace;
+  float zoneout_prob;
+  const void* zoneout_mask;
+  // LayerNorm variant only (gamma == nullptr selects the plain cell)
+  const void* gamma;
+  void *act_Wx, *cache_Wx;
+};
+struct IndrnnBwd {
+  int dtype, transposed_inputs, T, N, C, H;
+  const void *W, *u, *b, *x, *h, *dh_new;
+  void *dx, *dW, *du, *db, *dh, *workspace;
+  const void* zoneout_mask;
+  const void* gamma;
+  void* dgamma;
+  const void *act_Wx, *cache_Wx;
+};
+struct LnLstmFwd {
+  int dtype, training, T, N, C, H;
+  const void *W, *R, *b, *gamma, *gamma_h, *beta_h, *x;
+  void *h, *c, *act_Wx, *act_Wx_norm, *cache_Wx, *act_Rh, *cache_Rh, *act_c_norm, *cache_c,
+      *tmp_Rh;
+  float zoneout_prob;
+  const void* zoneout_mask;
+};
+struct LnLstmBwd {
+  int dtype, transposed_inputs, T, N, C, H;
+  const void *W, *R, *b, *gamma, *gamma_h, *beta_h, *x, *h, *c, *dh_new, *dc_new;
+  void *dx, *dW, *dR, *db, *dgamma, *dgamma_h, *dbeta_h, *dh, *dc, *act_Wx, *act_Wx_norm;
+  const void* cache_Wx;
+  void* act_Rh;
+  const void* cache_Rh;
+  void* act_c_norm;
+  const void* cache_c;
+  const void* zoneout_mask;
+};
+struct LnGruFwd {
+  int dtype, training, T, N, C, H;
+  const void *W, *R, *bx, *br, *gamma, *x;
+  void *h, *v, *act_Wx, *cache_Wx, *tmp_Wx_norm, *act_Rh, *cache_Rh, *tmp_Rh_norm;
+  float zoneout_prob;
+  const void* zoneout_mask;
+};
+struct LnGruBwd {
+  int dtype, transposed_inputs, T, N, C, H;
+  const void *W, *R, *bx, *br, *gamma, *x, *h, *v, *dh_new;
+  void *dx, *dW, *dR, *dbx, *dbr, *dgamma, *dh, *dp, *dq;
+  const void *act_Wx, *cache_Wx;
+  void* act_Rh;  // overwritten with d(h.R)
+  const void* cache_Rh;
+  const void* zoneout_mask;
+};
+
+int lstm_forward(const LstmFwd& a, cudaStream_t s);
+int lstm_backward(const LstmBwd& a, cudaStream_t s);
+int gru_forward(const GruFwd& a, cudaStream_t s);
+int gru_backward(const GruBwd& a, cudaStream_t s);
+int indrnn_forward(const IndrnnFwd& a, cudaStream_t s);
+int indrnn_backward(const IndrnnBwd& a, cudaStream_t s);
+int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s);
+int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s);
+int layer_norm_gru_forward(const LnGruFwd& a, cudaStream_t s);
+int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s);
+
+// Persistent-kernel implementations of the recurrences (recurrent_sm100.cu).
+// Each returns HASTE_B200_ERR_UNSUPPORTED (without touching any buffer) when the
+// shape does not fit, in which case the caller runs its step-wise path.
+// Forward: the input projection is already in a.v (LSTM) / a.tmp_Wx (GRU).
+// Backward: carries are fp32 [N,H] buffers, read at entry and written at exit.
+int lstm_forward_persistent(const LstmFwd& a, cudaStream_t s);
+int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry, cudaStream_t s);
+int gru_forward_persistent(const GruFwd& a, cudaStream_t s);
+int gru_backward_persistent(const GruBwd& a, float* dh_carry, cudaStream_t s);
+
+// Per-step contraction (M = batch rows): always the CUDA-core kernel.
+inline int gemm_small(const GemmDesc& g, cudaStream_t s) { return gemm_simt(g, s); }
+
+// Process-wide knobs (set through the C ABI).
+int recurrence_path();
+int gemm_path();
+
+}  // namespace hb

@@ -1,0 +1,285 @@
+// LayerNormLSTM: v = LN(x.W; gamma0) + LN(h.R; gamma1) + b, c' = f*c + i*g,
+// h' = o * tanh(LN(c'; gamma_h, beta_h)), with zoneout on h.
+//
+// Buffers and their reuse follow the reference so that the saved-tensor contract is
+// the same (lib/layer_norm_lstm_forward_gpu.cu.cc:26-109,191-340 and
+// lib/layer_norm_lstm_backward_gpu.cu.cc:27-118,207-352):
+//   forward : act_Wx = x.W, act_Wx_norm = LN1(act_Wx) then overwritten per step with
+//             the gate activations, act_Rh[t] = h_t.R (pre-norm), c = un-normalised
+//             cell state, act_c_norm[t] = LN3(c[t+1]).
+//   backward: act_c_norm[t] is overwritten with d/dLN3, then d/dc'; act_Wx_norm[t]
+//             with the gate pre-activation gradients; act_Rh[t] with d/d(h.R);
+//             act_Wx with d/d(x.W).
+#include "cells.cuh"
+
+namespace hb {
+namespace {
+
+template <typename T, bool Training>
+__global__ void lnlstm_cell_state(int N, int H, T* v, const T* __restrict__ Rh_norm,
+                                  const T* __restrict__ b, const T* __restrict__ c_prev,
+                                  T* __restrict__ c_out) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = blockIdx.y;
+  if (j >= H) return;
+  const long long g0 = (long long)n * 4 * H + j;
+  const long long o0 = (long long)n * H + j;
+  const float i = sigmoidf_(ld(v + g0 + 0 * H) + ld(Rh_norm + g0 + 0 * H) + ld(b + j + 0 * H));
+  const float g = tanhf(ld(v + g0 + 1 * H) + ld(Rh_norm + g0 + 1 * H) + ld(b + j + 1 * H));
+  const float f = sigmoidf_(ld(v + g0 + 2 * H) + ld(Rh_norm + g0 + 2 * H) + ld(b + j + 2 * H));
+  const float o = sigmoidf_(ld(v + g0 + 3 * H) + ld(Rh_norm + g0 + 3 * H) + ld(b + j + 3 * H));
+  if (Training) {
+    st(v + g0 + 0 * H, i);
+    st(v + g0 + 1 * H, g);
+    st(v + g0 + 2 * H, f);
+  }
+  st(v + g0 + 3 * H, o);
+  st(c_out + o0, f * ld(c_prev + o0) + i * g);
+}
+
+template <typename T, bool Training, bool Zoneout>
+__global__ void lnlstm_cell_output(int N, int H, const T* __restrict__ h_prev,
+                                   const T* __restrict__ c_norm, const T* __restrict__ v,
+                                   T* __restrict__ h_out, float zoneout_prob,
+                                   const T* __restrict__ mask) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = blockIdx.y;
+  if (j >= H) return;
+  const long long o0 = (long long)n * H + j;
+  const float o = ld(v + (long long)n * 4 * H + j + 3 * H);
+  float h_new = o * tanhf(ld(c_norm + o0));
+  if (Zoneout) {
+    const float hp = ld(h_prev + o0);
+    h_new = zoneout<Training>(h_new, hp, zoneout_prob, Training ? ld(mask + o0) : 0.f);
+  }
+  st(h_out + o0, h_new);
+}
+
+// Backward, first half: through h' = o * tanh(c_norm).  Writes d/dc_norm over
+// c_norm and d/d(pre-activation of o) over v.o.
+template <typename T, bool Zoneout>
+__global__ void lnlstm_output_grad(int N, int H, T* c_norm, const T* __restrict__ dh_new,
+                                   float* __restrict__ dh_carry, T* v,
+                                   const T* __restrict__ mask) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = blockIdx.y;
+  if (j >= H) return;
+  const long long o0 = (long long)n * H + j;
+  const long long oi = (long long)n * 4 * H + j + 3 * H;
+  float dh_total = ld(dh_new + o0) + dh_carry[o0];
+  if (Zoneout) {
+    const float m = ld(mask + o0);
+    dh_carry[o0] = (1.0f - m) * dh_total;
+    dh_total = m * dh_total;
+  } else {
+    dh_carry[o0] = 0.0f;
+  }
+  const float c_tanh = tanhf(ld(c_norm + o0));
+  const float o = ld(v + oi);
+  st(c_norm + o0, d_tanh(c_tanh) * (o * dh_total));
+  st(v + oi, d_sigmoid(o) * (c_tanh * dh_total));
+}
+
+// Backward, second half: through c' = f*c + i*g.  `dln` holds d/dc' from LayerNorm 3.
+template <typename T>
+__global__ void lnlstm_gate_grad(int N, int H, const T* __restrict__ c_prev, T* v,
+                                 const T* __restrict__ dc_new, const T* __restrict__ dln,
+                                 float* __restrict__ dc_carry) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int n = blockIdx.y;
+  if (j >= H) return;
+  const long long g0 = (long long)n * 4 * H + j;
+  const long long o0 = (long long)n * H + j;
+  const float i = ld(v + g0 + 0 * H), g = ld(v + g0 + 1 * H), f = ld(v + g0 + 2 * H);
+  const float dc_total = ld(dc_new + o0) + dc_carry[o0] + ld(dln + o0);
+  const float df = ld(c_prev + o0) * dc_total;
+  const float di = g * dc_total;
+  const float dg = i * dc_total;
+  dc_carry[o0] = f * dc_total;
+  st(v + g0 + 0 * H, d_sigmoid(i) * di);
+  st(v + g0 + 1 * H, d_tanh(g) * dg);
+  st(v + g0 + 2 * H, d_sigmoid(f) * df);
+  // v.o already holds its pre-activation gradient
+}
+
+template <typename T>
+int forward_steps(const LnLstmFwd& a, cudaStream_t s) {
+  const int N = a.N, H = a.H;
+  const long long NH = (long long)N * H;
+  const size_t es = sizeof(T);
+  T* h = (T*)a.h;
+  T* c = (T*)a.c;
+  T* v = (T*)a.act_Wx_norm;
+  T* act_Rh = (T*)a.act_Rh;
+  T* c_norm = (T*)a.act_c_norm;
+  const T* gamma1 = (const T*)a.gamma + 4 * H;
+  const T* mask = (const T*)a.zoneout_mask;
+  const bool zo = a.zoneout_prob != 0.0f && mask != nullptr;
+  dim3 block(128), grid(ceil_div(H, 128), N);
+  for (int t = 0; t < a.T; ++t) {
+    T* Rh_t = act_Rh + t * NH * 4;
+    GemmDesc g{a.dtype, a.dtype, N, 4 * H, H, h + t * NH, H, 1, a.R, 4LL * H, 1, Rh_t, 4LL * H, 0};
+    HB_TRY(gemm_small(g, s));
+    HB_TRY(layer_norm_forward(a.dtype, N, 4 * H, gamma1, nullptr, Rh_t, a.tmp_Rh,
+                              (char*)a.cache_Rh + (size_t)t * N * 2 * es, s));
+    T* vt = v + t * NH * 4;
+    if (a.training)
+      lnlstm_cell_state<T, true><<<grid, block, 0, s>>>(N, H, vt, (const T*)a.tmp_Rh,
+                                                        (const T*)a.b, c + t * NH, c + (t + 1) * NH);
+    else
+      lnlstm_cell_state<T, false><<<grid, block, 0, s>>>(N, H, vt, (const T*)a.tmp_Rh,
+                                                         (const T*)a.b, c + t * NH, c + (t + 1) * NH);
+    HB_LAUNCH_OK();
+    HB_TRY(layer_norm_forward(a.dtype, N, H, a.gamma_h, a.beta_h, c + (t + 1) * NH,
+                              c_norm + t * NH, (char*)a.cache_c + (size_t)t * N * 2 * es, s));
+    const T* mt = zo ? mask + t * NH : nullptr;
+#define HB_ARGS N, H, h + t * NH, c_norm + t * NH, vt, h + (t + 1) * NH, a.zoneout_prob, mt
+    if (a.training) {
+      if (zo) lnlstm_cell_output<T, true, true><<<grid, block, 0, s>>>(HB_ARGS);
+      else    lnlstm_cell_output<T, true, false><<<grid, block, 0, s>>>(HB_ARGS);
+    } else {
+      if (zo) lnlstm_cell_output<T, false, true><<<grid, block, 0, s>>>(HB_ARGS);
+      else    lnlstm_cell_output<T, false, false><<<grid, block, 0, s>>>(HB_ARGS);
+    }
+#undef HB_ARGS
+    HB_LAUNCH_OK();
+    count_launch(2);
+  }
+  return HASTE_B200_OK;
+}
+
+template <typename T>
+int backward_steps(const LnLstmBwd& a, float* dh_carry, float* dc_carry, void* dgamma1,
+                   void* dgamma_h, void* dbeta_h, int acc_dtype, float* lns, cudaStream_t s) {
+  const int N = a.N, H = a.H;
+  const long long NH = (long long)N * H;
+  const size_t es = sizeof(T);
+  const T* c = (const T*)a.c;
+  T* v = (T*)a.act_Wx_norm;
+  T* act_Rh = (T*)a.act_Rh;
+  T* c_norm = (T*)a.act_c_norm;
+  const T* gamma1 = (const T*)a.gamma + 4 * H;
+  const T* mask = (const T*)a.zoneout_mask;
+  const long long r_rs = a.transposed_inputs ? H : 1;
+  const long long r_cs = a.transposed_inputs ? 1 : 4LL * H;
+  dim3 block(128), grid(ceil_div(H, 128), N);
+  for (int t = a.T - 1; t >= 0; --t) {
+    T* vt = v + t * NH * 4;
+    T* cn = c_norm + t * NH;
+    const T* dh_new = (const T*)a.dh_new + (t + 1) * NH;
+    if (mask)
+      lnlstm_output_grad<T, true><<<grid, block, 0, s>>>(N, H, cn, dh_new, dh_carry, vt,
+                                                         mask + t * NH);
+    else
+      lnlstm_output_grad<T, false><<<grid, block, 0, s>>>(N, H, cn, dh_new, dh_carry, vt, nullptr);
+    HB_LAUNCH_OK();
+    // LayerNorm 3 backward: input was c[t+1]; d/dLN3 -> d/dc' in place.
+    HB_TRY(layer_norm_backward(a.dtype, N, H, a.gamma_h, c + (t + 1) * NH, cn, cn, acc_dtype,
+                               dgamma_h, dbeta_h, (const char*)a.cache_c + (size_t)t * N * 2 * es,
+                               lns, s));
+    lnlstm_gate_grad<T><<<grid, block, 0, s>>>(N, H, c + t * NH, vt,
+                                               (const T*)a.dc_new + (t + 1) * NH, cn, dc_carry);
+    HB_LAUNCH_OK();
+    count_launch(2);
+    // LayerNorm 2 backward: input was act_Rh[t]; result replaces it.
+    T* Rh_t = act_Rh + t * NH * 4;
+    HB_TRY(layer_norm_backward(a.dtype, N, 4 * H, gamma1, Rh_t, vt, Rh_t, acc_dtype, dgamma1,
+                               nullptr, (const char*)a.cache_Rh + (size_t)t * N * 2 * es, lns, s));
+    GemmDesc g{a.dtype, HASTE_B200_F32, N, H, 4 * H, Rh_t, 4LL * H, 1, a.R, r_rs, r_cs, dh_carry,
+               H, 1};
+    HB_TRY(gemm_small(g, s));
+  }
+  return HASTE_B200_OK;
+}
+
+}  // namespace
+
+int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
+  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
+  HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
+  HB_REQUIRE(a.W && a.R && a.b && a.gamma && a.gamma_h && a.beta_h && a.h && a.c && a.act_Wx &&
+                 a.act_Wx_norm && a.cache_Wx && a.act_Rh && a.cache_Rh && a.act_c_norm &&
+                 a.cache_c && a.tmp_Rh, "null pointer");
+  if (a.T == 0) return HASTE_B200_OK;
+  HB_REQUIRE(a.x, "x is null");
+  const long long TN = (long long)a.T * a.N;
+  HB_REQUIRE(TN < (1LL << 31), "T*N too large");
+  GemmDesc g{a.dtype, a.dtype, (int)TN, 4 * a.H, a.C, a.x, a.C, 1, a.W, 4LL * a.H, 1, a.act_Wx,
+             4LL * a.H, 0};
+  HB_TRY(gemm(g, s));
+  HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma, nullptr, a.act_Wx, a.act_Wx_norm,
+                            a.cache_Wx, s));
+  if (a.dtype == HASTE_B200_F32) return forward_steps<float>(a, s);
+  return forward_steps<__nv_bfloat16>(a, s);
+}
+
+int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
+  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
+  HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
+  HB_REQUIRE(a.W && a.R && a.gamma && a.gamma_h && a.h && a.c && a.dh_new && a.dc_new && a.dW &&
+                 a.dR && a.db && a.dgamma && a.dgamma_h && a.dbeta_h && a.dh && a.dc &&
+                 a.act_Wx && a.act_Wx_norm && a.cache_Wx && a.act_Rh && a.cache_Rh &&
+                 a.act_c_norm && a.cache_c, "null pointer");
+  if (a.T == 0) return HASTE_B200_OK;
+  HB_REQUIRE(a.x && a.dx, "x/dx is null");
+  const int N = a.N, H = a.H, C = a.C;
+  const long long TN = (long long)a.T * N;
+  HB_REQUIRE(TN < (1LL << 31), "T*N too large");
+  const size_t NH = (size_t)N * H;
+  const bool bf = a.dtype == HASTE_B200_BF16;
+  const size_t csf = colsum_scratch_floats((int)TN, 4 * H);
+  const size_t lnf = layer_norm_backward_scratch_floats((int)TN, 4 * H);
+  Arena ws;
+  HB_TRY(make_arena(&ws, s, 2 * Arena::pad(NH * 4) + Arena::pad(csf * 4) + Arena::pad(lnf * 4) +
+                                Arena::pad(6 * H * 4) + 2048));
+  float* dh_carry = ws.take<float>(NH);
+  float* dc_carry = ws.take<float>(NH);
+  float* cs = ws.take<float>(csf);
+  float* lns = ws.take<float>(lnf);
+  float* acc = ws.take<float>(6 * H);  // fp32 accumulators for bf16 runs: dgamma1, dgamma_h, dbeta_h
+  HB_REQUIRE(dh_carry && dc_carry && cs && lns && acc, "scratch arena");
+  HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
+  HB_TRY(to_float(a.dtype, a.dc, dc_carry, NH, s));
+
+  const size_t es = dtype_size(a.dtype);
+  void* dgamma1 = (char*)a.dgamma + (size_t)4 * H * es;
+  void* dgamma_h = a.dgamma_h;
+  void* dbeta_h = a.dbeta_h;
+  if (bf) {
+    HB_CUDA_OK(cudaMemsetAsync(acc, 0, 6 * H * sizeof(float), s));
+    dgamma1 = acc;
+    dgamma_h = acc + 4 * H;
+    dbeta_h = acc + 5 * H;
+  }
+  int st_ = bf ? backward_steps<__nv_bfloat16>(a, dh_carry, dc_carry, dgamma1, dgamma_h, dbeta_h,
+                                               HASTE_B200_F32, lns, s)
+               : backward_steps<float>(a, dh_carry, dc_carry, dgamma1, dgamma_h, dbeta_h,
+                                       HASTE_B200_F32, lns, s);
+  HB_TRY(st_);
+  if (bf) {
+    HB_TRY(add_float_into(a.dtype, acc, (char*)a.dgamma + (size_t)4 * H * es, 4 * H, s));
+    HB_TRY(add_float_into(a.dtype, acc + 4 * H, a.dgamma_h, H, s));
+    HB_TRY(add_float_into(a.dtype, acc + 5 * H, a.dbeta_h, H, s));
+  }
+  HB_TRY(from_float(a.dtype, dh_carry, a.dh, NH, s));
+  HB_TRY(from_float(a.dtype, dc_carry, a.dc, NH, s));
+
+  // act_Wx_norm now holds the gradient w.r.t. (LN1(x.W) + LN2(h.R) + b).
+  HB_TRY(colsum(a.dtype, a.act_Wx_norm, 4LL * H, (int)TN, 4 * H, a.dtype, a.db, 1, cs, s));
+  // LayerNorm 1 backward over all steps: act_Wx <- d/d(x.W).
+  HB_TRY(layer_norm_backward(a.dtype, (int)TN, 4 * H, a.gamma, a.act_Wx, a.act_Wx_norm, a.act_Wx,
+                             a.dtype, a.dgamma, nullptr, a.cache_Wx, lns, s));
+  const bool tr = a.transposed_inputs != 0;
+  GemmDesc gw{a.dtype, a.dtype, C, 4 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.act_Wx,
+              4LL * H, 1, a.dW, 4LL * H, 1};
+  HB_TRY(gemm(gw, s));
+  GemmDesc gr{a.dtype, a.dtype, H, 4 * H, (int)TN, a.h, 1, H, a.act_Rh, 4LL * H, 1, a.dR,
+              4LL * H, 1};
+  HB_TRY(gemm(gr, s));
+  GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 4 * H, a.act_Wx, 4LL * H, 1, a.W, tr ? C : 1,
+              tr ? 1 : 4LL * H, a.dx, C, 0};
+  HB_TRY(gemm(gx, s));
+  return HASTE_B200_OK;
+}
+
+}  // namespace hb

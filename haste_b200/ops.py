@@ -1,0 +1,322 @@
+"""The twelve tensor-level ops of the reference's `haste_pytorch_lib` extension,
+re-implemented over the haste_b200 C ABI.
+
+Names, argument order and returned lists mirror the reference's pybind functions
+(frameworks/pytorch/{lstm,gru,indrnn,layer_norm_lstm,layer_norm_gru,layer_norm_indrnn}.cc);
+like them, each op allocates its outputs and scratch with torch and runs on torch's
+current CUDA stream.  Additions: bfloat16 tensors are accepted, and every
+`*_backward` takes `transposed=` - True (the reference's convention) means `x`,
+`kernel` and `recurrent_kernel` arrive pre-transposed as `[C,T,N]`, `[G*H,C]`,
+`[G*H,H]`; False means they arrive in forward layout and are used without a copy.
+"""
+import torch
+
+from . import _C
+
+
+def _dtype(t):
+    if t.dtype == torch.float32:
+        return _C.F32
+    if t.dtype == torch.bfloat16:
+        return _C.BF16
+    raise TypeError(f"haste_b200 supports float32 and bfloat16 tensors, got {t.dtype}")
+
+
+def _check(*tensors):
+    dev, dt = tensors[0].device, tensors[0].dtype
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("haste_b200: tensor must be a CUDA tensor")
+        if not t.is_contiguous():
+            raise RuntimeError("haste_b200: tensor must be contiguous")
+        if t.numel() and (t.device != dev or t.dtype != dt):
+            raise RuntimeError("haste_b200: all tensors must share one device and dtype")
+
+
+def _p(t):
+    return None if t is None or t.numel() == 0 else t.data_ptr()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _mask_ptr(zoneout_prob, mask):
+    has = bool(zoneout_prob) and mask is not None and mask.numel() > 0
+    return (mask.data_ptr() if has else None), (float(zoneout_prob) if has else 0.0)
+
+
+def _dims_fwd(x, recurrent):
+    T, N, C = x.shape
+    return T, N, C, recurrent.shape[0]
+
+
+def _dims_bwd(x, transposed, H):
+    if transposed:
+        C, T, N = x.shape
+    else:
+        T, N, C = x.shape
+    return T, N, C, H
+
+
+# ---------------------------------------------------------------- LSTM
+def lstm_forward(training, zoneout_prob, x, h0, c0, kernel, recurrent_kernel, bias, zoneout_mask):
+    _check(x, h0, c0, kernel, recurrent_kernel, bias, zoneout_mask)
+    T, N, C, H = _dims_fwd(x, recurrent_kernel)
+    with torch.cuda.device(x.device):
+        h = x.new_empty(T + 1, N, H)
+        c = x.new_empty(T + 1, N, H)
+        h[0] = h0
+        c[0] = c0
+        cache = x.new_empty(T, N, 4 * H)
+        tmp_Rh = x.new_empty(N, 4 * H)
+        mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
+        _C.call("haste_b200_lstm_forward", _dtype(x), int(training), T, N, C, H, _p(kernel),
+                _p(recurrent_kernel), _p(bias), _p(x), _p(h), _p(c), _p(cache), _p(tmp_Rh),
+                zp, mp, _stream())
+    return [h, c, cache]
+
+
+def lstm_backward(x, kernel, recurrent_kernel, bias, zoneout_mask, h, c, cache, dh_new, dc_new,
+                  transposed=True):
+    _check(x, kernel, recurrent_kernel, bias, zoneout_mask, h, c, cache, dh_new, dc_new)
+    H = h.shape[2]
+    T, N, C, H = _dims_bwd(x, transposed, H)
+    with torch.cuda.device(h.device):
+        dx = h.new_empty(T, N, C)
+        dW = h.new_zeros(C, 4 * H)
+        dR = h.new_zeros(H, 4 * H)
+        db = h.new_zeros(4 * H)
+        dh = h.new_zeros(N, H)
+        dc = h.new_zeros(N, H)
+        _C.call("haste_b200_lstm_backward", _dtype(h), int(transposed), T, N, C, H, _p(kernel),
+                _p(recurrent_kernel), _p(bias), _p(x), _p(h), _p(c), _p(dh_new), _p(dc_new),
+                _p(dx), _p(dW), _p(dR), _p(db), _p(dh), _p(dc), _p(cache), _p(zoneout_mask),
+                _stream())
+    return [dx, dh, dc, dW, dR, db]
+
+
+# ---------------------------------------------------------------- GRU
+def gru_forward(training, zoneout_prob, x, h0, kernel, recurrent_kernel, bias, recurrent_bias,
+                zoneout_mask):
+    _check(x, h0, kernel, recurrent_kernel, bias, recurrent_bias, zoneout_mask)
+    T, N, C, H = _dims_fwd(x, recurrent_kernel)
+    with torch.cuda.device(x.device):
+        h = x.new_empty(T + 1, N, H)
+        h[0] = h0
+        cache = x.new_empty(T, N, 4 * H) if training else x.new_empty(0)
+        tmp_Wx = x.new_empty(T, N, 3 * H)
+        tmp_Rh = x.new_empty(N, 3 * H)
+        mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
+        _C.call("haste_b200_gru_forward", _dtype(x), int(training), T, N, C, H, _p(kernel),
+                _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(x), _p(h), _p(cache),
+                _p(tmp_Wx), _p(tmp_Rh), zp, mp, _stream())
+    return [h, cache]
+
+
+def gru_backward(x, kernel, recurrent_kernel, bias, recurrent_bias, zoneout_mask, h, cache,
+                 dh_new, transposed=True):
+    _check(x, kernel, recurrent_kernel, bias, recurrent_bias, zoneout_mask, h, cache, dh_new)
+    H = h.shape[2]
+    T, N, C, H = _dims_bwd(x, transposed, H)
+    with torch.cuda.device(h.device):
+        dx = h.new_empty(T, N, C)
+        dW = h.new_zeros(C, 3 * H)
+        dR = h.new_zeros(H, 3 * H)
+        dbx = h.new_zeros(3 * H)
+        dbr = h.new_zeros(3 * H)
+        dh = h.new_zeros(N, H)
+        dp = h.new_empty(T, N, 3 * H)
+        dq = h.new_empty(T, N, 3 * H)
+        _C.call("haste_b200_gru_backward", _dtype(h), int(transposed), T, N, C, H, _p(kernel),
+                _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(x), _p(h), _p(cache),
+                _p(dh_new), _p(dx), _p(dW), _p(dR), _p(dbx), _p(dbr), _p(dh), _p(dp), _p(dq),
+                _p(zoneout_mask), _stream())
+    return [dx, dh, dW, dR, dbx, dbr]
+
+
+# ---------------------------------------------------------------- IndRNN
+def indrnn_forward(training, zoneout_prob, x, h0, kernel, recurrent_scale, bias, zoneout_mask):
+    _check(x, h0, kernel, recurrent_scale, bias, zoneout_mask)
+    T, N, C = x.shape
+    H = kernel.shape[1]
+    with torch.cuda.device(x.device):
+        h = x.new_empty(T + 1, N, H)
+        h[0] = h0
+        workspace = x.new_empty(T, N, H)
+        mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
+        _C.call("haste_b200_indrnn_forward", _dtype(x), int(training), T, N, C, H, _p(kernel),
+                _p(recurrent_scale), _p(bias), _p(x), _p(h), _p(workspace), zp, mp, _stream())
+    return h
+
+
+def indrnn_backward(x, kernel, recurrent_scale, bias, zoneout_mask, h, dh_new, transposed=True):
+    _check(x, kernel, recurrent_scale, bias, zoneout_mask, h, dh_new)
+    H = h.shape[2]
+    T, N, C, H = _dims_bwd(x, transposed, H)
+    with torch.cuda.device(h.device):
+        dx = h.new_empty(T, N, C)
+        dW = h.new_zeros(C, H)
+        du = h.new_zeros(H)
+        db = h.new_zeros(H)
+        dh = h.new_zeros(N, H)
+        workspace = h.new_empty(T, N, H)
+        _C.call("haste_b200_indrnn_backward", _dtype(h), int(transposed), T, N, C, H, _p(kernel),
+                _p(recurrent_scale), _p(bias), _p(x), _p(h), _p(dh_new), _p(dx), _p(dW), _p(du),
+                _p(db), _p(dh), _p(workspace), _p(zoneout_mask), _stream())
+    return [dx, dh, dW, du, db]
+
+
+# ---------------------------------------------------------------- LayerNormLSTM
+def layer_norm_lstm_forward(training, zoneout_prob, x, h0, c0, kernel, recurrent_kernel, bias,
+                            gamma, gamma_h, beta_h, zoneout_mask):
+    _check(x, h0, c0, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h, zoneout_mask)
+    T, N, C, H = _dims_fwd(x, recurrent_kernel)
+    with torch.cuda.device(x.device):
+        h = x.new_empty(T + 1, N, H)
+        c = x.new_empty(T + 1, N, H)
+        h[0] = h0
+        c[0] = c0
+        act_Wx = x.new_empty(T, N, 4 * H)
+        act_Wx_norm = x.new_empty(T, N, 4 * H)
+        cache_Wx = x.new_empty(T, N, 2)
+        act_Rh = x.new_empty(T, N, 4 * H)
+        cache_Rh = x.new_empty(T, N, 2)
+        act_c_norm = x.new_empty(T, N, H)
+        cache_c = x.new_empty(T, N, 2)
+        tmp_Rh = x.new_empty(N, 4 * H)
+        mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
+        _C.call("haste_b200_layer_norm_lstm_forward", _dtype(x), int(training), T, N, C, H,
+                _p(kernel), _p(recurrent_kernel), _p(bias), _p(gamma), _p(gamma_h), _p(beta_h),
+                _p(x), _p(h), _p(c), _p(act_Wx), _p(act_Wx_norm), _p(cache_Wx), _p(act_Rh),
+                _p(cache_Rh), _p(act_c_norm), _p(cache_c), _p(tmp_Rh), zp, mp, _stream())
+    return [h, c, act_Wx, act_Wx_norm, cache_Wx, act_Rh, cache_Rh, act_c_norm, cache_c]
+
+
+def layer_norm_lstm_backward(x, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h,
+                             zoneout_mask, h, c, act_Wx, act_Wx_norm, cache_Wx, act_Rh, cache_Rh,
+                             act_c_norm, cache_c, dh_new, dc_new, transposed=True):
+    _check(x, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h, zoneout_mask, h, c, act_Wx,
+           act_Wx_norm, cache_Wx, act_Rh, cache_Rh, act_c_norm, cache_c, dh_new, dc_new)
+    H = h.shape[2]
+    T, N, C, H = _dims_bwd(x, transposed, H)
+    with torch.cuda.device(h.device):
+        dx = h.new_empty(T, N, C)
+        dW = h.new_zeros(C, 4 * H)
+        dR = h.new_zeros(H, 4 * H)
+        db = h.new_zeros(4 * H)
+        dgamma = torch.zeros_like(gamma)
+        dgamma_h = torch.zeros_like(gamma_h)
+        dbeta_h = torch.zeros_like(beta_h)
+        dh = h.new_zeros(N, H)
+        dc = h.new_zeros(N, H)
+        _C.call("haste_b200_layer_norm_lstm_backward", _dtype(h), int(transposed), T, N, C, H,
+                _p(kernel), _p(recurrent_kernel), _p(bias), _p(gamma), _p(gamma_h), _p(beta_h),
+                _p(x), _p(h), _p(c), _p(dh_new), _p(dc_new), _p(dx), _p(dW), _p(dR), _p(db),
+                _p(dgamma), _p(dgamma_h), _p(dbeta_h), _p(dh), _p(dc), _p(act_Wx),
+                _p(act_Wx_norm), _p(cache_Wx), _p(act_Rh), _p(cache_Rh), _p(act_c_norm),
+                _p(cache_c), _p(zoneout_mask), _stream())
+    return [dx, dh, dc, dW, dR, db, dgamma, dgamma_h, dbeta_h]
+
+
+# ---------------------------------------------------------------- LayerNormGRU
+def layer_norm_gru_forward(training, zoneout_prob, x, h0, kernel, recurrent_kernel, bias,
+                           recurrent_bias, gamma, zoneout_mask):
+    _check(x, h0, kernel, recurrent_kernel, bias, recurrent_bias, gamma, zoneout_mask)
+    T, N, C, H = _dims_fwd(x, recurrent_kernel)
+    with torch.cuda.device(x.device):
+        h = x.new_empty(T + 1, N, H)
+        h[0] = h0
+        cache = x.new_empty(T, N, 4 * H) if training else x.new_empty(0)
+        act_Wx = x.new_empty(T, N, 3 * H)
+        tmp_Wx_norm = x.new_empty(T, N, 3 * H)
+        cache_Wx = x.new_empty(T, N, 2)
+        act_Rh = x.new_empty(T, N, 3 * H)
+        tmp_Rh_norm = x.new_empty(N, 3 * H)
+        cache_Rh = x.new_empty(T, N, 2)
+        mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
+        _C.call("haste_b200_layer_norm_gru_forward", _dtype(x), int(training), T, N, C, H,
+                _p(kernel), _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(gamma), _p(x),
+                _p(h), _p(cache), _p(act_Wx), _p(cache_Wx), _p(tmp_Wx_norm), _p(act_Rh),
+                _p(cache_Rh), _p(tmp_Rh_norm), zp, mp, _stream())
+    return [h, cache, act_Wx, cache_Wx, act_Rh, cache_Rh]
+
+
+def layer_norm_gru_backward(x, kernel, recurrent_kernel, bias, recurrent_bias, gamma,
+                            zoneout_mask, h, cache, act_Wx, cache_Wx, act_Rh, cache_Rh, dh_new,
+                            transposed=True):
+    _check(x, kernel, recurrent_kernel, bias, recurrent_bias, gamma, zoneout_mask, h, cache,
+           act_Wx, cache_Wx, act_Rh, cache_Rh, dh_new)
+    H = h.shape[2]
+    T, N, C, H = _dims_bwd(x, transposed, H)
+    with torch.cuda.device(h.device):
+        dx = h.new_empty(T, N, C)
+        dW = h.new_zeros(C, 3 * H)
+        dR = h.new_zeros(H, 3 * H)
+        dbx = h.new_zeros(3 * H)
+        dbr = h.new_zeros(3 * H)
+        dh = h.new_zeros(N, H)
+        dp = h.new_empty(T, N, 3 * H)
+        dq = h.new_empty(T, N, 3 * H)
+        dgamma = torch.zeros_like(gamma)
+        _C.call("haste_b200_layer_norm_gru_backward", _dtype(h), int(transposed), T, N, C, H,
+                _p(kernel), _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(gamma), _p(x),
+                _p(h), _p(cache), _p(dh_new), _p(dx), _p(dW), _p(dR), _p(dbx), _p(dbr),
+                _p(dgamma), _p(dh), _p(dp), _p(dq), _p(act_Wx), _p(cache_Wx), _p(act_Rh),
+                _p(cache_Rh), _p(zoneout_mask), _stream())
+    return [dx, dh, dW, dR, dbx, dbr, dgamma]
+
+
+# ---------------------------------------------------------------- LayerNormIndRNN
+def layer_norm_indrnn_forward(training, zoneout_prob, x, h0, kernel, recurrent_scale, bias, gamma,
+                              zoneout_mask):
+    _check(x, h0, kernel, recurrent_scale, bias, gamma, zoneout_mask)
+    T, N, C = x.shape
+    H = kernel.shape[1]
+    with torch.cuda.device(x.device):
+        h = x.new_empty(T + 1, N, H)
+        h[0] = h0
+        workspace = x.new_empty(T, N, H)
+        act_Wx = x.new_empty(T, N, H)
+        cache_Wx = x.new_empty(T, N, 2)
+        mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
+        # gamma is [2,H]; only row 0 is used (frameworks/pytorch/layer_norm_indrnn.cc:67-72)
+        _C.call("haste_b200_layer_norm_indrnn_forward", _dtype(x), int(training), T, N, C, H,
+                _p(kernel), _p(recurrent_scale), _p(bias), _p(gamma), _p(x), _p(h),
+                _p(workspace), _p(act_Wx), _p(cache_Wx), zp, mp, _stream())
+    return [h, act_Wx, cache_Wx]
+
+
+def layer_norm_indrnn_backward(x, kernel, recurrent_scale, bias, gamma, zoneout_mask, h, act_Wx,
+                               cache_Wx, dh_new, transposed=True):
+    _check(x, kernel, recurrent_scale, bias, gamma, zoneout_mask, h, act_Wx, cache_Wx, dh_new)
+    H = h.shape[2]
+    T, N, C, H = _dims_bwd(x, transposed, H)
+    with torch.cuda.device(h.device):
+        dx = h.new_empty(T, N, C)
+        dW = h.new_zeros(C, H)
+        du = h.new_zeros(H)
+        db = h.new_zeros(H)
+        dh = h.new_zeros(N, H)
+        dgamma = torch.zeros_like(gamma)
+        workspace = h.new_empty(T, N, H)
+        _C.call("haste_b200_layer_norm_indrnn_backward", _dtype(h), int(transposed), T, N, C, H,
+                _p(kernel), _p(recurrent_scale), _p(bias), _p(gamma), _p(x), _p(h), _p(dh_new),
+                _p(dx), _p(dW), _p(du), _p(db), _p(dgamma), _p(dh), _p(workspace), _p(act_Wx),
+                _p(cache_Wx), _p(zoneout_mask), _stream())
+    return [dx, dh, dW, du, db, dgamma]
+
+
+# ---------------------------------------------------------------- helpers for tests/bench
+def gemm(a, b, out=None, accumulate=False):
+    """out (+)= a @ b for 2-D CUDA tensors with arbitrary strides (views allowed)."""
+    M, K = a.shape
+    K2, N = b.shape
+    assert K == K2
+    if out is None:
+        out = a.new_zeros(M, N)
+    with torch.cuda.device(a.device):
+        _C.call("haste_b200_gemm", _dtype(a), M, N, K, a.data_ptr(), a.stride(0), a.stride(1),
+                b.data_ptr(), b.stride(0), b.stride(1), out.data_ptr(), out.stride(0),
+                int(accumulate), _stream())
+    return out

@@ -34,3 +34,70 @@ def load_golden(path, dtype=torch.float64):
 
 
 max_rel_err = oracle.max_rel_err
+
+
+# ---------------------------------------------------------------------------
+# CUDA side: run one layer through the haste_b200 ops (C ABI) with the oracle's
+# input dictionary, returning outputs and gradients under the oracle's names.
+# ---------------------------------------------------------------------------
+def run_cuda(cell, d, zoneout=0.0, dtype=torch.float32, transposed=False, training=True,
+             backward=True, device="cuda"):
+    from haste_b200 import ops
+    _, names, has_c = oracle.CELLS[cell]
+    t = {k: (v.to(device=device, dtype=dtype).contiguous() if v is not None else None)
+         for k, v in d.items()}
+    mask = t["mask"] if t.get("mask") is not None else torch.empty(0, 0, 0, device=device, dtype=dtype)
+    x = t["x"]
+    if cell == "lstm":
+        ins = (x, t["h0"], t["c0"], t["W"], t["R"], t["b"], mask)
+    elif cell == "gru":
+        ins = (x, t["h0"], t["W"], t["R"], t["bx"], t["br"], mask)
+    elif cell == "indrnn":
+        ins = (x, t["h0"], t["W"], t["u"], t["b"], mask)
+    elif cell == "layer_norm_lstm":
+        ins = (x, t["h0"], t["c0"], t["W"], t["R"], t["b"], t["gamma"], t["gamma_h"], t["beta_h"], mask)
+    elif cell == "layer_norm_gru":
+        ins = (x, t["h0"], t["W"], t["R"], t["bx"], t["br"], t["gamma"], mask)
+    else:
+        ins = (x, t["h0"], t["W"], t["u"], t["b"], t["gamma"], mask)
+    fwd = getattr(ops, cell + "_forward")(training, zoneout, *ins)
+    fwd = fwd if isinstance(fwd, (list, tuple)) else [fwd]
+    out = {"h": fwd[0]}
+    if has_c:
+        out["c"] = fwd[1]
+    if not backward:
+        return out, {}
+    xx = x.permute(2, 0, 1).contiguous() if transposed else x
+    W = t["W"].t().contiguous() if transposed else t["W"]
+    saved = list(fwd[2:]) if has_c else list(fwd[1:])
+    if "indrnn" in cell:
+        rec = t["u"]
+    else:
+        rec = t["R"].t().contiguous() if transposed else t["R"]
+    if cell == "lstm":
+        args = (xx, W, rec, t["b"], mask, fwd[0], fwd[1], *saved, t["dh"], t["dc"])
+        gn = ["x", "h0", "c0", "W", "R", "b"]
+    elif cell == "gru":
+        args = (xx, W, rec, t["bx"], t["br"], mask, fwd[0], *saved, t["dh"])
+        gn = ["x", "h0", "W", "R", "bx", "br"]
+    elif cell == "indrnn":
+        args = (xx, W, rec, t["b"], mask, fwd[0], t["dh"])
+        gn = ["x", "h0", "W", "u", "b"]
+    elif cell == "layer_norm_lstm":
+        args = (xx, W, rec, t["b"], t["gamma"], t["gamma_h"], t["beta_h"], mask, fwd[0], fwd[1],
+                *saved, t["dh"], t["dc"])
+        gn = ["x", "h0", "c0", "W", "R", "b", "gamma", "gamma_h", "beta_h"]
+    elif cell == "layer_norm_gru":
+        args = (xx, W, rec, t["bx"], t["br"], t["gamma"], mask, fwd[0], *saved, t["dh"])
+        gn = ["x", "h0", "W", "R", "bx", "br", "gamma"]
+    else:
+        args = (xx, W, rec, t["b"], t["gamma"], mask, fwd[0], *saved, t["dh"])
+        gn = ["x", "h0", "W", "u", "b", "gamma"]
+    grads = getattr(ops, cell + "_backward")(*args, transposed=transposed)
+    return out, dict(zip(gn, grads))
+
+
+def assert_close(got, want, tol, what=""):
+    err = max_rel_err(got, want)
+    assert err < tol, f"{what}: max rel err {err:.3e} >= {tol:.1e}"
+    return err

@@ -1,0 +1,105 @@
+"""GPU parity tests: the CUDA path (through the C ABI) against the reference-generated
+fixtures and against the CPU oracle.  Bars: 1e-4 (fp32), 2e-2 (bf16), max|a-b|/max|b|."""
+import os
+
+import pytest
+import torch
+
+import haste_oracle as oracle
+from helpers import (TOL_BF16, TOL_F32, assert_close, golden_files, load_golden, run_cuda)
+
+pytestmark = pytest.mark.gpu
+
+CELLS = list(oracle.CELLS)
+
+
+def _compare(cell, d, out, grads, ref_out, ref_grads, tol):
+    assert_close(out["h"], ref_out["h"], tol, f"{cell} h")
+    if "c" in ref_out:
+        assert_close(out["c"], ref_out["c"], tol, f"{cell} c")
+    for k, ref in ref_grads.items():
+        got = grads[k]
+        if k == "gamma" and cell == "layer_norm_indrnn":
+            got, ref = got[0], ref[0]  # row 1 of gamma is unused by this cell
+        assert_close(got, ref, tol, f"{cell} d{k}")
+
+
+@pytest.mark.parametrize("transposed", [False, True])
+@pytest.mark.parametrize("path", golden_files(), ids=os.path.basename)
+def test_against_reference_fixture(path, transposed):
+    cell, dims, zo, d, ref_out, ref_grads = load_golden(path, torch.float64)
+    out, grads = run_cuda(cell, d, zoneout=zo, dtype=torch.float32, transposed=transposed)
+    _compare(cell, d, out, grads, ref_out, ref_grads, TOL_F32)
+
+
+@pytest.mark.parametrize("path", golden_files(), ids=os.path.basename)
+def test_inference_against_reference_fixture(path):
+    cell, dims, zo, d, ref_out, _ = load_golden(path, torch.float64)
+    out, _ = run_cuda(cell, d, zoneout=zo, training=False, backward=False)
+    assert_close(out["h"], ref_out["h_inference"], TOL_F32, f"{cell} inference h")
+
+
+# (T, N, C, H): ragged and tile-unfriendly shapes as well as aligned ones
+SHAPES = [(9, 1, 5, 7), (6, 3, 16, 24), (12, 17, 33, 40), (16, 32, 64, 64), (10, 64, 128, 128)]
+
+
+@pytest.mark.parametrize("zoneout", [0.0, 0.25])
+@pytest.mark.parametrize("shape", SHAPES, ids=lambda s: "T%d_N%d_C%d_H%d" % s)
+@pytest.mark.parametrize("cell", CELLS)
+def test_fp32_against_oracle(cell, shape, zoneout):
+    T, N, C, H = shape
+    d = oracle.make_inputs(cell, T, N, C, H, seed=T * 1000 + H, zoneout=zoneout)
+    ref_out, ref_grads = oracle.forward_backward(cell, d, zoneout=zoneout)
+    out, grads = run_cuda(cell, d, zoneout=zoneout, dtype=torch.float32)
+    _compare(cell, d, out, grads, ref_out, ref_grads, TOL_F32)
+
+
+@pytest.mark.parametrize("shape", [(6, 3, 16, 24), (16, 32, 64, 64)],
+                         ids=lambda s: "T%d_N%d_C%d_H%d" % s)
+@pytest.mark.parametrize("cell", CELLS)
+def test_bf16_against_oracle(cell, shape):
+    T, N, C, H = shape
+    zoneout = 0.25
+    d = oracle.make_inputs(cell, T, N, C, H, seed=77 + H, zoneout=zoneout)
+    # the oracle sees the bf16-rounded inputs, so only arithmetic differences remain
+    dq = {k: (v.to(torch.bfloat16).to(torch.float64) if v is not None else None)
+          for k, v in d.items()}
+    ref_out, ref_grads = oracle.forward_backward(cell, dq, zoneout=zoneout)
+    out, grads = run_cuda(cell, dq, zoneout=zoneout, dtype=torch.bfloat16)
+    _compare(cell, dq, out, grads, ref_out, ref_grads, TOL_BF16)
+
+
+@pytest.mark.parametrize("cell", CELLS)
+def test_repeated_runs_are_bit_identical(cell):
+    d = oracle.make_inputs(cell, 8, 5, 12, 16, seed=5, zoneout=0.3)
+    runs = [run_cuda(cell, d, zoneout=0.3) for _ in range(3)]
+    for out, grads in runs[1:]:
+        assert torch.equal(out["h"], runs[0][0]["h"])
+        for k in grads:
+            assert torch.equal(grads[k], runs[0][1][k]), k
+
+
+def test_long_sequence_stays_within_tolerance():
+    # error must not build up over a long recurrence
+    for cell in ["lstm", "gru"]:
+        d = oracle.make_inputs(cell, 300, 8, 32, 64, seed=9)
+        ref_out, ref_grads = oracle.forward_backward(cell, d)
+        out, grads = run_cuda(cell, d)
+        _compare(cell, d, out, grads, ref_out, ref_grads, TOL_F32)
+
+
+def test_zero_steps_and_error_reporting():
+    from haste_b200 import _C, ops
+    x = torch.zeros(0, 2, 3, device="cuda")
+    h0 = torch.zeros(2, 4, device="cuda")
+    W = torch.zeros(3, 16, device="cuda")
+    R = torch.zeros(4, 16, device="cuda")
+    b = torch.zeros(16, device="cuda")
+    h, c, _ = ops.lstm_forward(True, 0.0, x, h0, h0, W, R, b, torch.empty(0, 0, 0, device="cuda"))
+    assert h.shape == (1, 2, 4) and torch.equal(h[0], h0)
+    with pytest.raises(RuntimeError):
+        ops.lstm_forward(True, 0.0, x.cpu(), h0, h0, W, R, b, torch.empty(0, 0, 0, device="cuda"))
+    with pytest.raises(TypeError):
+        ops.lstm_forward(True, 0.0, x.double(), h0.double(), h0.double(), W.double(), R.double(),
+                         b.double(), torch.empty(0, 0, 0, device="cuda").double())
+    assert _C.launch_count() >= 0
