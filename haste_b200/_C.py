@@ -34,6 +34,7 @@ SIGNATURES = {
     "haste_b200_gemm": [_i] * 4 + [_p, _ll, _ll, _p, _ll, _ll, _p, _ll, _i, _p],
     "haste_b200_set_recurrence_path": [_i],
     "haste_b200_set_gemm_path": [_i],
+    "haste_b200_sync_check": [_p],
     "haste_b200_profile_enable": [_i],
     "haste_b200_profile_read": [_p, _i],
 }
@@ -83,6 +84,11 @@ def set_recurrence_path(path):
 
 def set_gemm_path(path):
     call("haste_b200_set_gemm_path", path)
+
+
+def sync_check(stream=None):
+    """Synchronises `stream` (a raw cudaStream_t or None) and raises if a kernel timed out."""
+    call("haste_b200_sync_check", stream)
 
 
 PHASES = ["input_projection", "recurrence_fwd", "recurrence_bwd", "weight_grad", "input_grad",

@@ -56,7 +56,7 @@ def build(force=False, verbose=False):
             print(log)
     if (force or not os.path.exists(LIB)
             or any(os.path.getmtime(o) > os.path.getmtime(LIB) for o in objs)):
-        r = subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-lcuda"],
+        r = subprocess.run([NVCC, "-shared", "-o", LIB, *objs],
                            capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")

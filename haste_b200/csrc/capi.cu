@@ -31,6 +31,17 @@ int haste_b200_profile_read(float* ms, int n) {
   return HASTE_B200_OK;
 }
 
+int haste_b200_sync_check(void* stream) {
+  HB_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
+  const int code = hb::take_error_word();
+  if (code != 0) {
+    hb::set_last_error("a kernel gave up on a bounded wait (code %d); results are incomplete",
+                       code);
+    return HASTE_B200_ERR_TIMEOUT;
+  }
+  return HASTE_B200_OK;
+}
+
 int haste_b200_set_recurrence_path(int path) {
   if (path < 0 || path > 2) return HASTE_B200_ERR_INVALID;
   g_rec_path.store(path);

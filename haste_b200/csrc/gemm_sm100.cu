@@ -1,7 +1,587 @@
+// Dense contraction on the 5th-generation tensor cores (sm_100a):
+//   TMA (cp.async.bulk.tensor, 128-byte swizzle) -> shared memory -> tcgen05.mma with
+//   the fp32 accumulator in tensor memory -> tcgen05.ld epilogue.
+//
+//   C[M,N] (+)= sum over products p of A_p[M,K] . B_p[K,N]        (bf16 operands)
+//
+// * bf16 storage: one product, operands read in place.
+// * fp32 storage: every operand is first split into two bf16 planes, x = hi + lo with
+//   hi = bf16(x), lo = bf16(x - hi), and three products are accumulated
+//   (hi.hi + hi.lo + lo.hi).  The dropped lo.lo term and the plane rounding leave a
+//   relative error near 2^-17 per product, far inside the 1e-4 parity bar, at 3/16 of
+//   the fp32 CUDA-core cost.
+// * Either operand may be K-major or MN-major (every transpose the cells need), chosen
+//   from its strides; no data is ever transposed in memory.
+// * Persistent kernel: one CTA per SM walks (tile, k-split) work items.  Warp 0 issues
+//   TMA, warp 1 issues MMA, warps 2-5 drain the accumulator; two accumulators in tensor
+//   memory let the epilogue of one tile overlap the main loop of the next.
+// * Long-K, small-output contractions (the weight gradients, K = T*N) are split along K;
+//   partial tiles go to scratch and a second kernel sums them in a fixed order.
+// * Every wait on an mbarrier is bounded; on expiry the kernel raises an error word,
+//   all roles drain and exit, tensor memory is released and the host returns
+//   HASTE_B200_ERR_TIMEOUT.
+//
+// Replaces the cuBLAS calls of the reference (lib/blas.h:48-61 and the call sites in
+// lib/*_gpu.cu.cc).
+#include <cuda.h>
+#include <cudaTypedefs.h>
+
+#include <mutex>
+
 #include "cells.cuh"
+
 namespace hb {
-int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
-  set_last_error("gemm_sm100: not available for this operand layout");
-  return HASTE_B200_ERR_UNSUPPORTED;
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;   // CTA tile; BK bf16 = one 128-byte swizzle row
+constexpr int UK = 16;                       // K of one tcgen05.mma (bf16)
+constexpr int TILE_BYTES = BM * BK * 2;      // one operand plane of one stage (A or B): 16 KiB
+constexpr int THREADS = 192;                 // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
+constexpr int TMEM_COLS = 2 * BN;            // two fp32 accumulators of BN columns
+constexpr long long SPIN_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
+
+// ----------------------------------------------------------------------------
+// PTX wrappers
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
 }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait.  Returns false if the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          int* err_word, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  uint32_t it = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++it & 255u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        *reinterpret_cast<volatile int*>(err_word) = code;
+        return false;
+      }
+    }
+  }
+  return true;
+}
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b,
+                                            uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
+      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
+      : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
+      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+__device__ __forceinline__ void tc_wait_ld() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
+                                              uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;
+  d |= 2ull << 61;
+  return d;
+}
+
+struct Params {
+  int M, N, K;
+  int a_mn_major, b_mn_major;  // 0: K contiguous, 1: M/N contiguous
+  int tiles_m, tiles_n, splits, kb_per_split, kb_total;
+  int c_is_bf16, accumulate;   // direct epilogue only
+  void* c;
+  long long ldc;
+  float* partial;              // non-null: write fp32 partial tiles [split][M][N]
+  int* err;
+};
+
+template <int NPROD>
+struct Cfg {
+  static constexpr int PLANES = NPROD == 1 ? 1 : 2;
+  static constexpr int STAGE_BYTES = 2 * PLANES * TILE_BYTES;
+  static constexpr int STAGES = NPROD == 1 ? 6 : 3;
+  static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+};
+
+template <int NPROD>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a_hi,
+                    const __grid_constant__ CUtensorMap map_a_lo,
+                    const __grid_constant__ CUtensorMap map_b_hi,
+                    const __grid_constant__ CUtensorMap map_b_lo, const Params p) {
+  using C = Cfg<NPROD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + C::STAGES * C::STAGE_BYTES);
+  // barrier slots: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+  auto accf_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + a); };
+  auto acce_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(accf_bar(a), 1);
+      mbar_init(acce_bar(a), 128);
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_items = p.tiles_m * p.tiles_n * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int tn = item % p.tiles_n;
+        const int tm = (item / p.tiles_n) % p.tiles_m;
+        const int sp = item / (p.tiles_n * p.tiles_m);
+        const int kb0 = sp * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err, 1)) { ok = false; break; }
+          mbar_expect_tx(full_bar(stage), C::STAGE_BYTES);
+          const uint32_t sa = base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::PLANES * TILE_BYTES;
+          const int k0 = kb * BK, m0 = tm * BM, n0 = tn * BN;
+#pragma unroll
+          for (int pl = 0; pl < C::PLANES; ++pl) {
+            const CUtensorMap* ma = pl == 0 ? &map_a_hi : &map_a_lo;
+            const CUtensorMap* mb = pl == 0 ? &map_b_hi : &map_b_lo;
+            const uint32_t da = sa + pl * TILE_BYTES, db = sb + pl * TILE_BYTES;
+            if (p.a_mn_major) {  // two boxes of 64 (m) x 64 (k)
+              tma_load_2d(da, ma, full_bar(stage), m0, k0);
+              tma_load_2d(da + TILE_BYTES / 2, ma, full_bar(stage), m0 + 64, k0);
+            } else {             // one box of 64 (k) x 128 (m)
+              tma_load_2d(da, ma, full_bar(stage), k0, m0);
+            }
+            if (p.b_mn_major) {
+              tma_load_2d(db, mb, full_bar(stage), n0, k0);
+              tma_load_2d(db + TILE_BYTES / 2, mb, full_bar(stage), n0 + 64, k0);
+            } else {
+              tma_load_2d(db, mb, full_bar(stage), k0, n0);
+            }
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                             ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                             ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+      // K-major: 8-row groups 1024 B apart, a K step of 16 elements is 32 B along the row.
+      // MN-major: 8-k-row groups 1024 B apart, 64-element MN chunks one box (8192 B) apart,
+      //           a K step of 16 rows is 2048 B.
+      const uint32_t a_lbo = p.a_mn_major ? TILE_BYTES / 2 : 16, a_kstep = p.a_mn_major ? 2048 : 32;
+      const uint32_t b_lbo = p.b_mn_major ? TILE_BYTES / 2 : 16, b_kstep = p.b_mn_major ? 2048 : 32;
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc_phase[2] = {0, 0};
+      int it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
+        const int sp = item / (p.tiles_n * p.tiles_m);
+        const int kb0 = sp * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const int acc = it & 1;
+        if (!mbar_wait(acce_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err, 2)) { ok = false; break; }
+        acc_phase[acc] ^= 1u;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        uint32_t first = 1;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t sa = base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::PLANES * TILE_BYTES;
+#pragma unroll
+          for (int pr = 0; pr < NPROD; ++pr) {
+            // products: (hi,hi), (hi,lo), (lo,hi)
+            const uint32_t pa = sa + (pr == 2 ? TILE_BYTES : 0);
+            const uint32_t pb = sb + (pr == 1 ? TILE_BYTES : 0);
+#pragma unroll
+            for (int ks = 0; ks < BK / UK; ++ks) {
+              const uint64_t da = smem_desc(pa + ks * a_kstep, a_lbo, 1024);
+              const uint64_t db = smem_desc(pb + ks * b_kstep, b_lbo, 1024);
+              tc_mma_bf16(d_tmem, da, db, idesc, first ? 0u : 1u);
+              first = 0;
+            }
+          }
+          tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(accf_bar(acc));  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue
+    const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
+    uint32_t acc_phase[2] = {0, 0};
+    int it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
+      const int tn = item % p.tiles_n;
+      const int tm = (item / p.tiles_n) % p.tiles_m;
+      const int sp = item / (p.tiles_n * p.tiles_m);
+      const int acc = it & 1;
+      if (ok) ok = mbar_wait(accf_bar(acc), acc_phase[acc], abort_flag, p.err, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      acc_phase[acc] ^= 1u;
+      tc_fence_after();
+      const int m = tm * BM + quad * 32 + lane;
+      const int n0 = tn * BN;
+      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+#pragma unroll 1
+      for (int ch = 0; ch < BN / 32; ++ch) {
+        uint32_t r[32];
+        tc_ld32(taddr + ch * 32, r);
+        tc_wait_ld();
+        const int nb = n0 + ch * 32;
+        if (m < p.M && nb < p.N) {
+          if (p.partial) {
+            float* dst = p.partial + ((long long)sp * p.M + m) * p.N + nb;
+            if (nb + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) =
+                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+              for (int j = 0; j < 32 && nb + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
+            }
+          } else if (p.c_is_bf16) {
+            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)m * p.ldc + nb;
+            for (int j = 0; j < 32 && nb + j < p.N; ++j) {
+              float v = __uint_as_float(r[j]);
+              if (p.accumulate) v += __bfloat162float(dst[j]);
+              dst[j] = __float2bfloat16_rn(v);
+            }
+          } else {
+            float* dst = reinterpret_cast<float*>(p.c) + (long long)m * p.ldc + nb;
+            if (nb + 32 <= p.N && (p.ldc & 3) == 0 && !p.accumulate) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) =
+                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+            } else {
+              for (int j = 0; j < 32 && nb + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]);
+                if (p.accumulate) v += dst[j];
+                dst[j] = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(acce_bar(acc));
+    }
+  }
+
+  // Drain: every role arrives here, also after a time-out, so tensor memory is released.
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// x -> (hi, lo) bf16 planes, same orientation, leading dimension ld_dst (multiple of 8).
+__global__ void split_planes_kernel(const float* __restrict__ src, long long ld_src, int rows,
+                                    int cols, __nv_bfloat16* __restrict__ hi,
+                                    __nv_bfloat16* __restrict__ lo, long long ld_dst) {
+  const long long total = (long long)rows * ld_dst;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / ld_dst;
+    const int c = (int)(i - r * ld_dst);
+    float x = (c < cols) ? src[r * ld_src + c] : 0.0f;
+    const __nv_bfloat16 h = __float2bfloat16_rn(x);
+    hi[i] = h;
+    lo[i] = __float2bfloat16_rn(x - __bfloat162float(h));
+  }
+}
+
+template <typename TC>
+__global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits, long long MN,
+                                     int N, TC* __restrict__ c, long long ldc, int accumulate) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < MN;
+       i += (long long)gridDim.x * blockDim.x) {
+    float s = 0.f;
+    for (int k = 0; k < splits; ++k) s += part[k * MN + i];
+    const long long m = i / N;
+    TC* dst = c + m * ldc + (i - m * N);
+    if (accumulate) s += ld(dst);
+    st(dst, s);
+  }
+}
+
+// ----------------------------------------------------------------------------
+// Host side
+// ----------------------------------------------------------------------------
+PFN_cuTensorMapEncodeTiled encode_fn() {
+  static PFN_cuTensorMapEncodeTiled fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* f = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(f);
+    cudaGetLastError();
+  });
+  return fn;
+}
+
+// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements.
+bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld,
+              int box_inner, int box_outer) {
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+struct Operand {
+  bool mn_major;       // contiguous along M (A) or N (B)
+  long long ld;        // elements between consecutive outer indices
+  const void* hi;
+  const void* lo;
+};
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+std::once_flag g_attr_once;
+
+}  // namespace
+
+int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
+  auto unsupported = [](const char* why) {
+    set_last_error("gemm_sm100: %s", why);
+    return HASTE_B200_ERR_UNSUPPORTED;
+  };
+  if (!encode_fn()) return unsupported("cuTensorMapEncodeTiled not available");
+  if (g.M <= 0 || g.N <= 0) return HASTE_B200_OK;
+  if (g.K <= 0) return unsupported("K == 0");
+  // Small problems are launch-bound either way; keep them on the generic kernel.
+  if ((long long)g.M * g.N * g.K < (1LL << 21) || g.M < 32 || g.N < 32)
+    return unsupported("problem too small for the tensor-core path");
+  const bool f32 = g.dtype == HASTE_B200_F32;
+  const bool a_k = g.a_cs == 1, a_m = g.a_rs == 1 && !a_k;
+  const bool b_k = g.b_rs == 1, b_n = g.b_cs == 1 && !b_k;
+  if (!(a_k || a_m) || !(b_k || b_n)) return unsupported("operand has no unit stride");
+
+  const int M = g.M, N = g.N, K = g.K;
+  Operand A, B;
+  A.mn_major = !a_k;
+  B.mn_major = !b_k;
+  // extents in (outer rows, inner contiguous) form
+  const long long a_rows = a_k ? M : K, a_cols = a_k ? K : M;
+  const long long b_rows = b_k ? N : K, b_cols = b_k ? K : N;
+  const long long a_ld_src = a_k ? g.a_rs : g.a_cs;
+  const long long b_ld_src = b_k ? g.b_cs : g.b_rs;
+
+  // scratch: planes for fp32 operands, partial tiles for split-K
+  const int tiles_m = ceil_div(M, BM), tiles_n = ceil_div(N, BN);
+  const int kb_total = ceil_div(K, BK);
+  int splits = 1;
+  const int sms = sm_count();
+  if (tiles_m * tiles_n < sms && kb_total >= 8) {
+    splits = min(min(kb_total / 4, ceil_div(2 * sms, tiles_m * tiles_n)), 64);
+    if (splits < 1) splits = 1;
+  }
+  int kb_per_split = ceil_div(kb_total, splits);
+  splits = ceil_div(kb_total, kb_per_split);
+
+  const long long a_ld = f32 ? ((a_cols + 7) & ~7LL) : a_ld_src;
+  const long long b_ld = f32 ? ((b_cols + 7) & ~7LL) : b_ld_src;
+  if (!f32) {
+    if ((a_ld % 8) || (b_ld % 8) || ((uintptr_t)g.a & 15) || ((uintptr_t)g.b & 15))
+      return unsupported("bf16 operand not 16-byte aligned for TMA");
+  }
+  size_t bytes = 0;
+  const size_t a_plane = f32 ? Arena::pad((size_t)a_rows * a_ld * 2) : 0;
+  const size_t b_plane = f32 ? Arena::pad((size_t)b_rows * b_ld * 2) : 0;
+  const size_t part_bytes = splits > 1 ? Arena::pad((size_t)splits * M * N * 4) : 0;
+  bytes = 2 * a_plane + 2 * b_plane + part_bytes + 1024;
+  Arena ws;
+  HB_TRY(make_arena(&ws, stream, bytes, /*slot=*/1));
+  int* err = device_error_word();
+  if (!err) return unsupported("error word allocation failed");
+  if (f32) {
+    __nv_bfloat16* ah = ws.take<__nv_bfloat16>(a_plane / 2);
+    __nv_bfloat16* al = ws.take<__nv_bfloat16>(a_plane / 2);
+    __nv_bfloat16* bh = ws.take<__nv_bfloat16>(b_plane / 2);
+    __nv_bfloat16* bl = ws.take<__nv_bfloat16>(b_plane / 2);
+    if (!ah || !al || !bh || !bl) return unsupported("scratch arena");
+    const int blocks = 4 * sms;
+    split_planes_kernel<<<blocks, 256, 0, stream>>>((const float*)g.a, a_ld_src, (int)a_rows,
+                                                    (int)a_cols, ah, al, a_ld);
+    HB_LAUNCH_OK();
+    split_planes_kernel<<<blocks, 256, 0, stream>>>((const float*)g.b, b_ld_src, (int)b_rows,
+                                                    (int)b_cols, bh, bl, b_ld);
+    HB_LAUNCH_OK();
+    count_launch(2);
+    A.hi = ah; A.lo = al; B.hi = bh; B.lo = bl;
+  } else {
+    A.hi = A.lo = g.a;
+    B.hi = B.lo = g.b;
+  }
+  A.ld = a_ld;
+  B.ld = b_ld;
+  float* partial = nullptr;
+  if (splits > 1) {
+    partial = ws.take<float>(part_bytes / 4);
+    if (!partial) return unsupported("scratch arena");
+  }
+
+  CUtensorMap m_ah, m_al, m_bh, m_bl;
+  bool ok = true;
+  // K-major: inner = K, box 64 (k) x 128 rows.  MN-major: inner = M/N, box 64 x 64 (k).
+  ok &= make_map(&m_ah, A.hi, a_cols, a_rows, A.ld, 64, A.mn_major ? 64 : BM);
+  ok &= make_map(&m_al, A.lo, a_cols, a_rows, A.ld, 64, A.mn_major ? 64 : BM);
+  ok &= make_map(&m_bh, B.hi, b_cols, b_rows, B.ld, 64, B.mn_major ? 64 : BN);
+  ok &= make_map(&m_bl, B.lo, b_cols, b_rows, B.ld, 64, B.mn_major ? 64 : BN);
+  if (!ok) return unsupported("tensor map encoding rejected the operand");
+
+  Params p;
+  p.M = M; p.N = N; p.K = K;
+  p.a_mn_major = A.mn_major; p.b_mn_major = B.mn_major;
+  p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.splits = splits;
+  p.kb_per_split = kb_per_split; p.kb_total = kb_total;
+  p.c_is_bf16 = g.dtype_c == HASTE_B200_BF16;
+  p.accumulate = g.accumulate;
+  p.c = g.c; p.ldc = g.ldc;
+  p.partial = partial;
+  p.err = err;
+
+  std::call_once(g_attr_once, [] {
+    cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg<1>::SMEM);
+    cudaFuncSetAttribute(gemm_tcgen05_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg<3>::SMEM);
+  });
+  const int grid = min(sms, tiles_m * tiles_n * splits);
+  if (f32)
+    gemm_tcgen05_kernel<3><<<grid, THREADS, Cfg<3>::SMEM, stream>>>(m_ah, m_al, m_bh, m_bl, p);
+  else
+    gemm_tcgen05_kernel<1><<<grid, THREADS, Cfg<1>::SMEM, stream>>>(m_ah, m_al, m_bh, m_bl, p);
+  HB_LAUNCH_OK();
+  count_launch(1);
+  if (splits > 1) {
+    const long long MN = (long long)M * N;
+    const int blocks = min(ceil_div(MN, 256), 8 * sms);
+    if (g.dtype_c == HASTE_B200_BF16)
+      splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+          partial, splits, MN, N, (__nv_bfloat16*)g.c, g.ldc, g.accumulate);
+    else
+      splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(partial, splits, MN, N, (float*)g.c,
+                                                              g.ldc, g.accumulate);
+    HB_LAUNCH_OK();
+    count_launch(1);
+  }
+  return HASTE_B200_OK;
+}
+
 }  // namespace hb

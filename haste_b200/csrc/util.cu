@@ -5,6 +5,7 @@
 #include <cstdio>
 #include <map>
 #include <mutex>
+#include <tuple>
 #include <utility>
 #include <vector>
 
@@ -26,6 +27,35 @@ const char* last_error() { return g_err; }
 static std::atomic<long long> g_launches{0};
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 long long launch_count() { return g_launches.load(std::memory_order_relaxed); }
+
+// ---------------------------------------------------------------------------
+// Error word shared with the kernels.
+// ---------------------------------------------------------------------------
+namespace {
+std::once_flag g_errw_once;
+int* g_errw = nullptr;
+}  // namespace
+
+int* device_error_word() {
+  std::call_once(g_errw_once, [] {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, 64, cudaHostAllocPortable | cudaHostAllocMapped) == cudaSuccess) {
+      g_errw = static_cast<int*>(p);
+      *g_errw = 0;
+    } else {
+      cudaGetLastError();
+    }
+  });
+  return g_errw;  // unified addressing: the host pointer is valid on every device
+}
+
+int take_error_word() {
+  if (!g_errw) return 0;
+  volatile int* w = g_errw;
+  const int v = *w;
+  if (v) *w = 0;
+  return v;
+}
 
 // ---------------------------------------------------------------------------
 // Per-phase timing.
@@ -79,17 +109,17 @@ void profile_read(float* ms, int n) {
 namespace {
 struct Block { void* p = nullptr; size_t n = 0; };
 std::mutex g_ws_mu;
-std::map<std::pair<int, cudaStream_t>, Block> g_ws;
+std::map<std::tuple<int, cudaStream_t, int>, Block> g_ws;
 }  // namespace
 
-void* workspace(cudaStream_t stream, size_t bytes) {
+void* workspace(cudaStream_t stream, size_t bytes, int slot) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) {
     set_last_error("cudaGetDevice failed");
     return nullptr;
   }
   std::lock_guard<std::mutex> lk(g_ws_mu);
-  Block& b = g_ws[{dev, stream}];
+  Block& b = g_ws[std::make_tuple(dev, stream, slot)];
   if (b.n >= bytes && b.p) return b.p;
   if (b.p) {
     // Work already queued on this stream may still read the old block.
@@ -114,8 +144,8 @@ void* workspace(cudaStream_t stream, size_t bytes) {
   return b.p;
 }
 
-int make_arena(Arena* a, cudaStream_t stream, size_t bytes) {
-  a->base = static_cast<char*>(workspace(stream, bytes));
+int make_arena(Arena* a, cudaStream_t stream, size_t bytes, int slot) {
+  a->base = static_cast<char*>(workspace(stream, bytes, slot));
   a->cap = bytes;
   a->off = 0;
   return a->base ? HASTE_B200_OK : HASTE_B200_ERR_CUDA;

@@ -9,11 +9,18 @@ namespace hb {
 // Counts kernels launched by this library (reported through the C ABI).
 void count_launch(int n);
 
-// Library-owned scratch.  One grow-only buffer per (device, stream) pair, so
+// One process-wide error word in pinned, device-visible host memory.  Kernels that give
+// up on a bounded wait store a non-zero code there; the host reads it without having to
+// copy anything back.  device_error_word() is the pointer kernels get;
+// take_error_word() returns the current value and clears it.
+int* device_error_word();
+int take_error_word();
+
+// Library-owned scratch.  One grow-only buffer per (device, stream, slot), so
 // calls issued on different streams never share scratch.  The pointer stays
 // valid until the next larger request on the same stream.  Returns nullptr
 // (and sets the last error) if the allocation fails.
-void* workspace(cudaStream_t stream, size_t bytes);
+void* workspace(cudaStream_t stream, size_t bytes, int slot = 0);
 
 // Bump allocator over one workspace() block; every sub-buffer is 256-byte aligned.
 struct Arena {
@@ -28,7 +35,7 @@ struct Arena {
     return p;
   }
 };
-int make_arena(Arena* a, cudaStream_t stream, size_t bytes);
+int make_arena(Arena* a, cudaStream_t stream, size_t bytes, int slot = 0);
 
 // out[j] (+)= sum_r in[r*ld + j], r < rows, j < width.  Deterministic: a fixed
 // two-stage tree whatever the launch timing.  `in_dtype`/`out_dtype` are

@@ -62,6 +62,10 @@ long long haste_b200_launch_count(void);
  * milliseconds spent since the previous read in: 0 input projection, 1 forward
  * recurrence, 2 backward recurrence, 3 weight-gradient contractions, 4 input-gradient
  * contraction, 5 everything else.  Reading synchronises with the recorded work. */
+/* Waits for the work queued on `stream` and reports whether any kernel of this library
+ * abandoned a bounded wait since the last check (HASTE_B200_ERR_TIMEOUT) - the
+ * asynchronous entry points cannot report that themselves. */
+int haste_b200_sync_check(void* stream);
 int haste_b200_profile_enable(int on);
 int haste_b200_profile_read(float* ms, int n);
 
