@@ -103,6 +103,10 @@ struct GemmDesc {
   const void* b; long long b_rs, b_cs;
   void* c; long long ldc;
   int accumulate;
+  // fp32 storage only: split operands into three bf16 planes (six products) instead of two
+  // (three products); the result is then accurate to fp32 rounding.  The LayerNorm cells
+  // ask for it because normalisation amplifies the input projection's error.
+  int precise = 0;
 };
 int gemm(const GemmDesc& g, cudaStream_t stream);
 int gemm_simt(const GemmDesc& g, cudaStream_t stream);

@@ -85,12 +85,13 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
   return true;
 }
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1) {
+// Tile load: coordinates are (contiguous index, row index, plane).
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
   asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4}], [%2];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1)
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
+      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
       : "memory");
 }
 __device__ __forceinline__ void tc_fence_before() {
@@ -154,18 +155,18 @@ struct Params {
 
 template <int NPROD>
 struct Cfg {
-  static constexpr int PLANES = NPROD == 1 ? 1 : 2;
+  // 1 product: bf16 operands as they are.  3 products: (hi, lo) planes.  6 products:
+  // (hi, mid, lo) planes, accurate to fp32 rounding (used where LayerNorm amplifies error).
+  static constexpr int PLANES = NPROD == 1 ? 1 : (NPROD == 3 ? 2 : 3);
   static constexpr int STAGE_BYTES = 2 * PLANES * TILE_BYTES;
-  static constexpr int STAGES = NPROD == 1 ? 6 : 3;
+  static constexpr int STAGES = NPROD == 1 ? 6 : (NPROD == 3 ? 3 : 2);
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 template <int NPROD>
 __global__ void __launch_bounds__(THREADS, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a_hi,
-                    const __grid_constant__ CUtensorMap map_a_lo,
-                    const __grid_constant__ CUtensorMap map_b_hi,
-                    const __grid_constant__ CUtensorMap map_b_lo, const Params p) {
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
+                    const __grid_constant__ CUtensorMap map_b, const Params p) {
   using C = Cfg<NPROD>;
   extern __shared__ uint8_t smem_raw[];
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -227,20 +228,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a_hi,
           const int k0 = kb * BK, m0 = tm * BM, n0 = tn * BN;
 #pragma unroll
           for (int pl = 0; pl < C::PLANES; ++pl) {
-            const CUtensorMap* ma = pl == 0 ? &map_a_hi : &map_a_lo;
-            const CUtensorMap* mb = pl == 0 ? &map_b_hi : &map_b_lo;
+            const CUtensorMap* ma = &map_a;
+            const CUtensorMap* mb = &map_b;
             const uint32_t da = sa + pl * TILE_BYTES, db = sb + pl * TILE_BYTES;
             if (p.a_mn_major) {  // two boxes of 64 (m) x 64 (k)
-              tma_load_2d(da, ma, full_bar(stage), m0, k0);
-              tma_load_2d(da + TILE_BYTES / 2, ma, full_bar(stage), m0 + 64, k0);
+              tma_load_3d(da, ma, full_bar(stage), m0, k0, pl);
+              tma_load_3d(da + TILE_BYTES / 2, ma, full_bar(stage), m0 + 64, k0, pl);
             } else {             // one box of 64 (k) x 128 (m)
-              tma_load_2d(da, ma, full_bar(stage), k0, m0);
+              tma_load_3d(da, ma, full_bar(stage), k0, m0, pl);
             }
             if (p.b_mn_major) {
-              tma_load_2d(db, mb, full_bar(stage), n0, k0);
-              tma_load_2d(db + TILE_BYTES / 2, mb, full_bar(stage), n0 + 64, k0);
+              tma_load_3d(db, mb, full_bar(stage), n0, k0, pl);
+              tma_load_3d(db + TILE_BYTES / 2, mb, full_bar(stage), n0 + 64, k0, pl);
             } else {
-              tma_load_2d(db, mb, full_bar(stage), k0, n0);
+              tma_load_3d(db, mb, full_bar(stage), k0, n0, pl);
             }
           }
           if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
@@ -279,9 +280,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a_hi,
           const uint32_t sb = sa + C::PLANES * TILE_BYTES;
 #pragma unroll
           for (int pr = 0; pr < NPROD; ++pr) {
-            // products: (hi,hi), (hi,lo), (lo,hi)
-            const uint32_t pa = sa + (pr == 2 ? TILE_BYTES : 0);
-            const uint32_t pb = sb + (pr == 1 ? TILE_BYTES : 0);
+            // plane pairs, most significant first:
+            //   (0,0) (0,1) (1,0) | (1,1) (0,2) (2,0)      0 = hi, 1 = mid/lo, 2 = lo
+            const int ia = pr == 2 ? 1 : (pr == 3 ? 1 : (pr == 5 ? 2 : 0));
+            const int ib = pr == 1 ? 1 : (pr == 3 ? 1 : (pr == 4 ? 2 : 0));
+            const uint32_t pa = sa + ia * TILE_BYTES;
+            const uint32_t pb = sb + ib * TILE_BYTES;
 #pragma unroll
             for (int ks = 0; ks < BK / UK; ++ks) {
               const uint64_t da = smem_desc(pa + ks * a_kstep, a_lbo, 1024);
@@ -373,19 +377,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a_hi,
   }
 }
 
-// x -> (hi, lo) bf16 planes, same orientation, leading dimension ld_dst (multiple of 8).
+// x -> `planes` bf16 planes (x = p0 + p1 (+ p2), each the bf16 rounding of what is left),
+// same orientation as the source, leading dimension ld_dst (a multiple of 8), planes
+// `plane_stride` elements apart.
 __global__ void split_planes_kernel(const float* __restrict__ src, long long ld_src, int rows,
-                                    int cols, __nv_bfloat16* __restrict__ hi,
-                                    __nv_bfloat16* __restrict__ lo, long long ld_dst) {
+                                    int cols, __nv_bfloat16* __restrict__ dst, long long ld_dst,
+                                    long long plane_stride, int planes) {
   const long long total = (long long)rows * ld_dst;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     const long long r = i / ld_dst;
     const int c = (int)(i - r * ld_dst);
     float x = (c < cols) ? src[r * ld_src + c] : 0.0f;
-    const __nv_bfloat16 h = __float2bfloat16_rn(x);
-    hi[i] = h;
-    lo[i] = __float2bfloat16_rn(x - __bfloat162float(h));
+    for (int pl = 0; pl < planes; ++pl) {
+      const __nv_bfloat16 h = __float2bfloat16_rn(x);
+      dst[pl * plane_stride + i] = h;
+      x -= __bfloat162float(h);
+    }
   }
 }
 
@@ -420,14 +428,15 @@ PFN_cuTensorMapEncodeTiled encode_fn() {
   return fn;
 }
 
-// 2-D bf16 tensor map: `inner` contiguous elements, `outer` rows of `ld` elements.
+// bf16 tensor map over `planes` matrices of `outer` rows x `inner` contiguous elements
+// (leading dimension ld, planes plane_stride elements apart).
 bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld,
-              int box_inner, int box_outer) {
-  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+              long long plane_stride, int planes, int box_inner, int box_outer) {
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)planes};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(planes > 1 ? plane_stride : ld * outer) * 2};
+  cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims,
                            strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -435,10 +444,10 @@ bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long oute
 }
 
 struct Operand {
-  bool mn_major;       // contiguous along M (A) or N (B)
-  long long ld;        // elements between consecutive outer indices
-  const void* hi;
-  const void* lo;
+  bool mn_major;          // contiguous along M (A) or N (B)
+  long long ld;           // elements between consecutive outer indices
+  long long plane_stride; // elements between planes
+  const void* base;
 };
 
 int sm_count() {
@@ -500,33 +509,32 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
     if ((a_ld % 8) || (b_ld % 8) || ((uintptr_t)g.a & 15) || ((uintptr_t)g.b & 15))
       return unsupported("bf16 operand not 16-byte aligned for TMA");
   }
-  size_t bytes = 0;
+  const int planes = f32 ? (g.precise ? 3 : 2) : 1;
   const size_t a_plane = f32 ? Arena::pad((size_t)a_rows * a_ld * 2) : 0;
   const size_t b_plane = f32 ? Arena::pad((size_t)b_rows * b_ld * 2) : 0;
   const size_t part_bytes = splits > 1 ? Arena::pad((size_t)splits * M * N * 4) : 0;
-  bytes = 2 * a_plane + 2 * b_plane + part_bytes + 1024;
+  const size_t bytes = planes * (a_plane + b_plane) + part_bytes + 1024;
   Arena ws;
   HB_TRY(make_arena(&ws, stream, bytes, /*slot=*/1));
   int* err = device_error_word();
   if (!err) return unsupported("error word allocation failed");
   if (f32) {
-    __nv_bfloat16* ah = ws.take<__nv_bfloat16>(a_plane / 2);
-    __nv_bfloat16* al = ws.take<__nv_bfloat16>(a_plane / 2);
-    __nv_bfloat16* bh = ws.take<__nv_bfloat16>(b_plane / 2);
-    __nv_bfloat16* bl = ws.take<__nv_bfloat16>(b_plane / 2);
-    if (!ah || !al || !bh || !bl) return unsupported("scratch arena");
+    __nv_bfloat16* ap = ws.take<__nv_bfloat16>(planes * a_plane / 2);
+    __nv_bfloat16* bp = ws.take<__nv_bfloat16>(planes * b_plane / 2);
+    if (!ap || !bp) return unsupported("scratch arena");
     const int blocks = 4 * sms;
     split_planes_kernel<<<blocks, 256, 0, stream>>>((const float*)g.a, a_ld_src, (int)a_rows,
-                                                    (int)a_cols, ah, al, a_ld);
+                                                    (int)a_cols, ap, a_ld, a_plane / 2, planes);
     HB_LAUNCH_OK();
     split_planes_kernel<<<blocks, 256, 0, stream>>>((const float*)g.b, b_ld_src, (int)b_rows,
-                                                    (int)b_cols, bh, bl, b_ld);
+                                                    (int)b_cols, bp, b_ld, b_plane / 2, planes);
     HB_LAUNCH_OK();
     count_launch(2);
-    A.hi = ah; A.lo = al; B.hi = bh; B.lo = bl;
+    A.base = ap; A.plane_stride = a_plane / 2;
+    B.base = bp; B.plane_stride = b_plane / 2;
   } else {
-    A.hi = A.lo = g.a;
-    B.hi = B.lo = g.b;
+    A.base = g.a; A.plane_stride = 0;
+    B.base = g.b; B.plane_stride = 0;
   }
   A.ld = a_ld;
   B.ld = b_ld;
@@ -536,13 +544,13 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
     if (!partial) return unsupported("scratch arena");
   }
 
-  CUtensorMap m_ah, m_al, m_bh, m_bl;
+  CUtensorMap m_a, m_b;
   bool ok = true;
   // K-major: inner = K, box 64 (k) x 128 rows.  MN-major: inner = M/N, box 64 x 64 (k).
-  ok &= make_map(&m_ah, A.hi, a_cols, a_rows, A.ld, 64, A.mn_major ? 64 : BM);
-  ok &= make_map(&m_al, A.lo, a_cols, a_rows, A.ld, 64, A.mn_major ? 64 : BM);
-  ok &= make_map(&m_bh, B.hi, b_cols, b_rows, B.ld, 64, B.mn_major ? 64 : BN);
-  ok &= make_map(&m_bl, B.lo, b_cols, b_rows, B.ld, 64, B.mn_major ? 64 : BN);
+  ok &= make_map(&m_a, A.base, a_cols, a_rows, A.ld, A.plane_stride, planes, 64,
+                 A.mn_major ? 64 : BM);
+  ok &= make_map(&m_b, B.base, b_cols, b_rows, B.ld, B.plane_stride, planes, 64,
+                 B.mn_major ? 64 : BN);
   if (!ok) return unsupported("tensor map encoding rejected the operand");
 
   Params p;
@@ -561,12 +569,16 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
                          Cfg<1>::SMEM);
     cudaFuncSetAttribute(gemm_tcgen05_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          Cfg<3>::SMEM);
+    cudaFuncSetAttribute(gemm_tcgen05_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         Cfg<6>::SMEM);
   });
   const int grid = min(sms, tiles_m * tiles_n * splits);
-  if (f32)
-    gemm_tcgen05_kernel<3><<<grid, THREADS, Cfg<3>::SMEM, stream>>>(m_ah, m_al, m_bh, m_bl, p);
+  if (planes == 3)
+    gemm_tcgen05_kernel<6><<<grid, THREADS, Cfg<6>::SMEM, stream>>>(m_a, m_b, p);
+  else if (planes == 2)
+    gemm_tcgen05_kernel<3><<<grid, THREADS, Cfg<3>::SMEM, stream>>>(m_a, m_b, p);
   else
-    gemm_tcgen05_kernel<1><<<grid, THREADS, Cfg<1>::SMEM, stream>>>(m_ah, m_al, m_bh, m_bl, p);
+    gemm_tcgen05_kernel<1><<<grid, THREADS, Cfg<1>::SMEM, stream>>>(m_a, m_b, p);
   HB_LAUNCH_OK();
   count_launch(1);
   if (splits > 1) {

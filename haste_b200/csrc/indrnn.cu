@@ -142,6 +142,7 @@ int indrnn_forward(const IndrnnFwd& a, cudaStream_t s) {
   HB_REQUIRE(TN < (1LL << 31), "T*N too large");
   void* proj = a.gamma ? a.act_Wx : a.workspace;
   GemmDesc g{a.dtype, a.dtype, (int)TN, a.H, a.C, a.x, a.C, 1, a.W, a.H, 1, proj, a.H, 0};
+  g.precise = a.gamma ? 1 : 0;
   HB_TRY(gemm(g, s));
   if (a.gamma)
     HB_TRY(layer_norm_forward(a.dtype, (int)TN, a.H, a.gamma, nullptr, a.act_Wx, a.workspace,
@@ -187,9 +188,11 @@ int indrnn_backward(const IndrnnBwd& a, cudaStream_t s) {
   // dW[C,H] = x^T . dk   (assigned, as in the reference)
   GemmDesc gw{a.dtype, a.dtype, C, H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.workspace, H, 1,
               a.dW, H, 0};
+  gw.precise = a.gamma ? 1 : 0;
   HB_TRY(gemm(gw, s));
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, H, a.workspace, H, 1, a.W, tr ? C : 1, tr ? 1 : H,
               a.dx, C, 0};
+  gx.precise = a.gamma ? 1 : 0;
   HB_TRY(gemm(gx, s));
   return HASTE_B200_OK;
 }

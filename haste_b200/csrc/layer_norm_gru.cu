@@ -92,6 +92,7 @@ int layer_norm_gru_forward(const LnGruFwd& a, cudaStream_t s) {
   HB_REQUIRE(TN < (1LL << 31), "T*N too large");
   GemmDesc g{a.dtype, a.dtype, (int)TN, 3 * a.H, a.C, a.x, a.C, 1, a.W, 3LL * a.H, 1, a.act_Wx,
              3LL * a.H, 0};
+  g.precise = 1;
   HB_TRY(gemm(g, s));
   HB_TRY(layer_norm_forward(a.dtype, (int)TN, 3 * a.H, a.gamma, nullptr, a.act_Wx, a.tmp_Wx_norm,
                             a.cache_Wx, s));
@@ -144,12 +145,15 @@ int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s) {
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 3 * H, a.dp, 3LL * H, 1, a.W, tr ? C : 1,
               tr ? 1 : 3LL * H, a.dx, C, 0};
+  gx.precise = 1;
   HB_TRY(gemm(gx, s));
   GemmDesc gr{a.dtype, a.dtype, H, 3 * H, (int)TN, a.h, 1, H, a.act_Rh, 3LL * H, 1, a.dR,
               3LL * H, 1};
+  gr.precise = 1;
   HB_TRY(gemm(gr, s));
   GemmDesc gw{a.dtype, a.dtype, C, 3 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.dp, 3LL * H, 1,
               a.dW, 3LL * H, 1};
+  gw.precise = 1;
   HB_TRY(gemm(gw, s));
   return HASTE_B200_OK;
 }

@@ -206,6 +206,7 @@ int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
   HB_REQUIRE(TN < (1LL << 31), "T*N too large");
   GemmDesc g{a.dtype, a.dtype, (int)TN, 4 * a.H, a.C, a.x, a.C, 1, a.W, 4LL * a.H, 1, a.act_Wx,
              4LL * a.H, 0};
+  g.precise = 1;
   HB_TRY(gemm(g, s));
   HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma, nullptr, a.act_Wx, a.act_Wx_norm,
                             a.cache_Wx, s));
@@ -272,12 +273,15 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gw{a.dtype, a.dtype, C, 4 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.act_Wx,
               4LL * H, 1, a.dW, 4LL * H, 1};
+  gw.precise = 1;
   HB_TRY(gemm(gw, s));
   GemmDesc gr{a.dtype, a.dtype, H, 4 * H, (int)TN, a.h, 1, H, a.act_Rh, 4LL * H, 1, a.dR,
               4LL * H, 1};
+  gr.precise = 1;
   HB_TRY(gemm(gr, s));
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 4 * H, a.act_Wx, 4LL * H, 1, a.W, tr ? C : 1,
               tr ? 1 : 4LL * H, a.dx, C, 0};
+  gx.precise = 1;
   HB_TRY(gemm(gx, s));
   return HASTE_B200_OK;
 }

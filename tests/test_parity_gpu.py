@@ -103,3 +103,46 @@ def test_zero_steps_and_error_reporting():
         ops.lstm_forward(True, 0.0, x.double(), h0.double(), h0.double(), W.double(), R.double(),
                          b.double(), torch.empty(0, 0, 0, device="cuda").double())
     assert _C.launch_count() >= 0
+
+
+# shapes that exercise several hidden slices, several batch slices and multi-tile CTAs
+REC_SHAPES = [(12, 40, 32, 80), (20, 64, 64, 512), (6, 130, 48, 512), (9, 3, 16, 200)]
+
+
+@pytest.mark.parametrize("path", ["stepwise", "persistent"])
+@pytest.mark.parametrize("shape", REC_SHAPES, ids=lambda s: "T%d_N%d_C%d_H%d" % s)
+@pytest.mark.parametrize("cell", ["lstm", "gru"])
+def test_both_recurrence_paths_fp32(cell, shape, path):
+    from haste_b200 import _C
+    T, N, C, H = shape
+    d = oracle.make_inputs(cell, T, N, C, H, seed=T + H, zoneout=0.2)
+    ref_out, ref_grads = oracle.forward_backward(cell, d, zoneout=0.2)
+    _C.set_recurrence_path(_C.PATH_STEPWISE if path == "stepwise" else _C.PATH_AUTO)
+    try:
+        n0 = _C.launch_count()
+        out, grads = run_cuda(cell, d, zoneout=0.2)
+        _C.sync_check(torch.cuda.current_stream().cuda_stream)
+        launches = _C.launch_count() - n0
+    finally:
+        _C.set_recurrence_path(_C.PATH_AUTO)
+    _compare(cell, d, out, grads, ref_out, ref_grads, TOL_F32)
+    if path == "persistent":
+        # one launch per pass, not per time step
+        assert launches < 40, launches
+    else:
+        assert launches >= 4 * T
+
+
+@pytest.mark.parametrize("shape", [(20, 64, 64, 512), (8, 128, 64, 1024)],
+                         ids=lambda s: "T%d_N%d_C%d_H%d" % s)
+@pytest.mark.parametrize("cell", ["lstm", "gru"])
+def test_persistent_path_bf16(cell, shape):
+    from haste_b200 import _C
+    T, N, C, H = shape
+    d = oracle.make_inputs(cell, T, N, C, H, seed=H, zoneout=0.1)
+    dq = {k: (v.to(torch.bfloat16).to(torch.float64) if v is not None else None)
+          for k, v in d.items()}
+    ref_out, ref_grads = oracle.forward_backward(cell, dq, zoneout=0.1)
+    out, grads = run_cuda(cell, dq, zoneout=0.1, dtype=torch.bfloat16)
+    _C.sync_check(torch.cuda.current_stream().cuda_stream)
+    _compare(cell, dq, out, grads, ref_out, ref_grads, TOL_BF16)
