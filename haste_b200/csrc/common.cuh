@@ -117,6 +117,11 @@ int gemm_simt(const GemmDesc& g, cudaStream_t stream);
 // layer_norm_backward_scratch_floats(rows, width) floats.  dx may alias dy.
 int layer_norm_forward(int dtype, int rows, int width, const void* gamma, const void* beta,
                        const void* x, void* y, void* cache, cudaStream_t stream);
+// Same, with the input stored as `in_dtype` (fp32 input with bf16 everything else is
+// allowed) and an optional copy of the input, converted to `dtype`, written to x_copy.
+int layer_norm_forward_from(int in_dtype, int dtype, int rows, int width, const void* gamma,
+                            const void* beta, const void* x, void* y, void* cache, void* x_copy,
+                            cudaStream_t stream);
 size_t layer_norm_backward_scratch_floats(int rows, int width);
 int layer_norm_backward(int dtype, int rows, int width, const void* gamma, const void* x,
                         const void* dy, void* dx, int acc_dtype, void* dgamma, void* dbeta,

@@ -173,6 +173,7 @@ int gru_backward_stepwise(const GruBwd& a, float* dh_carry, cudaStream_t s) {
 int gru_forward(const GruFwd& a, cudaStream_t s) {
   HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
+  if (a.T == 0) return HASTE_B200_OK;  // nothing to do; scratch pointers may be null
   HB_REQUIRE(a.W && a.R && a.bx && a.br && a.h && a.tmp_Wx && a.tmp_Rh, "null pointer");
   HB_REQUIRE(!a.training || a.v, "v is required when training");
   if (a.T == 0) return HASTE_B200_OK;
@@ -195,6 +196,7 @@ int gru_forward(const GruFwd& a, cudaStream_t s) {
 int gru_backward(const GruBwd& a, cudaStream_t s) {
   HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
+  if (a.T == 0) return HASTE_B200_OK;  // nothing to do; scratch pointers may be null
   HB_REQUIRE(a.W && a.R && a.h && a.v && a.dh_new && a.dW && a.dR && a.dbx && a.dbr && a.dh &&
                  a.dp && a.dq, "null pointer");
   if (a.T == 0) return HASTE_B200_OK;

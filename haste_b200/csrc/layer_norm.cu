@@ -27,14 +27,20 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return s;
 }
 
-template <typename T>
+// TI is the storage type of the input (fp32 input with bf16 parameters/outputs is used
+// inside the bf16 LayerNorm cells so that a value is rounded once, when it is saved).
+// x_copy, if not null, receives the input converted to T.
+template <typename T, typename TI>
 __global__ void __launch_bounds__(LN_THREADS)
 ln_forward_kernel(int width, const T* __restrict__ gamma, const T* __restrict__ beta,
-                  const T* __restrict__ x, T* __restrict__ y, T* __restrict__ cache) {
+                  const TI* __restrict__ x, T* __restrict__ y, T* __restrict__ cache,
+                  T* __restrict__ x_copy) {
   __shared__ float red[LN_THREADS / 32];
   const long long row = blockIdx.x;
-  const T* xr = x + row * width;
+  const TI* xr = x + row * width;
   T* yr = y + row * width;
+  if (x_copy)
+    for (int i = threadIdx.x; i < width; i += LN_THREADS) st(x_copy + row * width + i, ld(xr + i));
   float s = 0.f;
   for (int i = threadIdx.x; i < width; i += LN_THREADS) s += ld(xr + i);
   const float mean = block_sum(s, red) / width;
@@ -131,14 +137,29 @@ ln_backward_dx_kernel(int width, const T* __restrict__ gamma, const T* __restric
 
 int layer_norm_forward(int dtype, int rows, int width, const void* gamma, const void* beta,
                        const void* x, void* y, void* cache, cudaStream_t stream) {
+  return layer_norm_forward_from(dtype, dtype, rows, width, gamma, beta, x, y, cache, nullptr,
+                                 stream);
+}
+
+int layer_norm_forward_from(int in_dtype, int dtype, int rows, int width, const void* gamma,
+                            const void* beta, const void* x, void* y, void* cache, void* x_copy,
+                            cudaStream_t stream) {
   if (rows <= 0) return HASTE_B200_OK;
-  if (dtype == HASTE_B200_F32)
-    ln_forward_kernel<float><<<rows, LN_THREADS, 0, stream>>>(
-        width, (const float*)gamma, (const float*)beta, (const float*)x, (float*)y, (float*)cache);
-  else
-    ln_forward_kernel<__nv_bfloat16><<<rows, LN_THREADS, 0, stream>>>(
-        width, (const __nv_bfloat16*)gamma, (const __nv_bfloat16*)beta, (const __nv_bfloat16*)x,
-        (__nv_bfloat16*)y, (__nv_bfloat16*)cache);
+  using bf = __nv_bfloat16;
+  if (dtype == HASTE_B200_F32 && in_dtype == HASTE_B200_F32)
+    ln_forward_kernel<float, float><<<rows, LN_THREADS, 0, stream>>>(
+        width, (const float*)gamma, (const float*)beta, (const float*)x, (float*)y, (float*)cache,
+        (float*)x_copy);
+  else if (dtype == HASTE_B200_BF16 && in_dtype == HASTE_B200_BF16)
+    ln_forward_kernel<bf, bf><<<rows, LN_THREADS, 0, stream>>>(
+        width, (const bf*)gamma, (const bf*)beta, (const bf*)x, (bf*)y, (bf*)cache, (bf*)x_copy);
+  else if (dtype == HASTE_B200_BF16 && in_dtype == HASTE_B200_F32)
+    ln_forward_kernel<bf, float><<<rows, LN_THREADS, 0, stream>>>(
+        width, (const bf*)gamma, (const bf*)beta, (const float*)x, (bf*)y, (bf*)cache, (bf*)x_copy);
+  else {
+    set_last_error("layer_norm_forward: unsupported dtype combination %d -> %d", in_dtype, dtype);
+    return HASTE_B200_ERR_INVALID;
+  }
   HB_LAUNCH_OK();
   count_launch(1);
   return HASTE_B200_OK;

@@ -18,7 +18,7 @@ namespace {
 template <typename T, bool Training>
 __global__ void lnlstm_cell_state(int N, int H, T* v, const T* __restrict__ Rh_norm,
                                   const T* __restrict__ b, const T* __restrict__ c_prev,
-                                  T* __restrict__ c_out) {
+                                  T* __restrict__ c_out, float* c_carry) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   const int n = blockIdx.y;
   if (j >= H) return;
@@ -34,7 +34,12 @@ __global__ void lnlstm_cell_state(int N, int H, T* v, const T* __restrict__ Rh_n
     st(v + g0 + 2 * H, f);
   }
   st(v + g0 + 3 * H, o);
-  st(c_out + o0, f * ld(c_prev + o0) + i * g);
+  // bf16 storage: the running cell state is carried in fp32 (c_carry) and only its
+  // saved copy is rounded
+  const float cp = c_carry ? c_carry[o0] : ld(c_prev + o0);
+  const float cn = f * cp + i * g;
+  if (c_carry) c_carry[o0] = cn;
+  st(c_out + o0, cn);
 }
 
 template <typename T, bool Training, bool Zoneout>
@@ -103,7 +108,7 @@ __global__ void lnlstm_gate_grad(int N, int H, const T* __restrict__ c_prev, T* 
 }
 
 template <typename T>
-int forward_steps(const LnLstmFwd& a, cudaStream_t s) {
+int forward_steps(const LnLstmFwd& a, float* rh_f32, float* c_f32, cudaStream_t s) {
   const int N = a.N, H = a.H;
   const long long NH = (long long)N * H;
   const size_t es = sizeof(T);
@@ -118,20 +123,34 @@ int forward_steps(const LnLstmFwd& a, cudaStream_t s) {
   dim3 block(128), grid(ceil_div(H, 128), N);
   for (int t = 0; t < a.T; ++t) {
     T* Rh_t = act_Rh + t * NH * 4;
-    GemmDesc g{a.dtype, a.dtype, N, 4 * H, H, h + t * NH, H, 1, a.R, 4LL * H, 1, Rh_t, 4LL * H, 0};
-    HB_TRY(gemm_small(g, s));
-    HB_TRY(layer_norm_forward(a.dtype, N, 4 * H, gamma1, nullptr, Rh_t, a.tmp_Rh,
-                              (char*)a.cache_Rh + (size_t)t * N * 2 * es, s));
+    if (rh_f32) {
+      // bf16 storage: keep h.R and c' in fp32 between the kernels of one step
+      GemmDesc g{a.dtype, HASTE_B200_F32, N, 4 * H, H, h + t * NH, H, 1, a.R, 4LL * H, 1, rh_f32,
+                 4LL * H, 0};
+      HB_TRY(gemm_small(g, s));
+      HB_TRY(layer_norm_forward_from(HASTE_B200_F32, a.dtype, N, 4 * H, gamma1, nullptr, rh_f32,
+                                     a.tmp_Rh, (char*)a.cache_Rh + (size_t)t * N * 2 * es, Rh_t, s));
+    } else {
+      GemmDesc g{a.dtype, a.dtype, N, 4 * H, H, h + t * NH, H, 1, a.R, 4LL * H, 1, Rh_t, 4LL * H, 0};
+      HB_TRY(gemm_small(g, s));
+      HB_TRY(layer_norm_forward(a.dtype, N, 4 * H, gamma1, nullptr, Rh_t, a.tmp_Rh,
+                                (char*)a.cache_Rh + (size_t)t * N * 2 * es, s));
+    }
     T* vt = v + t * NH * 4;
     if (a.training)
-      lnlstm_cell_state<T, true><<<grid, block, 0, s>>>(N, H, vt, (const T*)a.tmp_Rh,
-                                                        (const T*)a.b, c + t * NH, c + (t + 1) * NH);
+      lnlstm_cell_state<T, true><<<grid, block, 0, s>>>(
+          N, H, vt, (const T*)a.tmp_Rh, (const T*)a.b, c + t * NH, c + (t + 1) * NH, c_f32);
     else
-      lnlstm_cell_state<T, false><<<grid, block, 0, s>>>(N, H, vt, (const T*)a.tmp_Rh,
-                                                         (const T*)a.b, c + t * NH, c + (t + 1) * NH);
+      lnlstm_cell_state<T, false><<<grid, block, 0, s>>>(
+          N, H, vt, (const T*)a.tmp_Rh, (const T*)a.b, c + t * NH, c + (t + 1) * NH, c_f32);
     HB_LAUNCH_OK();
-    HB_TRY(layer_norm_forward(a.dtype, N, H, a.gamma_h, a.beta_h, c + (t + 1) * NH,
-                              c_norm + t * NH, (char*)a.cache_c + (size_t)t * N * 2 * es, s));
+    if (c_f32)
+      HB_TRY(layer_norm_forward_from(HASTE_B200_F32, a.dtype, N, H, a.gamma_h, a.beta_h, c_f32,
+                                     c_norm + t * NH, (char*)a.cache_c + (size_t)t * N * 2 * es,
+                                     nullptr, s));
+    else
+      HB_TRY(layer_norm_forward(a.dtype, N, H, a.gamma_h, a.beta_h, c + (t + 1) * NH,
+                                c_norm + t * NH, (char*)a.cache_c + (size_t)t * N * 2 * es, s));
     const T* mt = zo ? mask + t * NH : nullptr;
 #define HB_ARGS N, H, h + t * NH, c_norm + t * NH, vt, h + (t + 1) * NH, a.zoneout_prob, mt
     if (a.training) {
@@ -210,8 +229,15 @@ int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
   HB_TRY(gemm(g, s));
   HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma, nullptr, a.act_Wx, a.act_Wx_norm,
                             a.cache_Wx, s));
-  if (a.dtype == HASTE_B200_F32) return forward_steps<float>(a, s);
-  return forward_steps<__nv_bfloat16>(a, s);
+  if (a.dtype == HASTE_B200_F32) return forward_steps<float>(a, nullptr, nullptr, s);
+  const size_t NH = (size_t)a.N * a.H;
+  Arena ws;
+  HB_TRY(make_arena(&ws, s, Arena::pad(NH * 4 * 4) + Arena::pad(NH * 4) + 512));
+  float* rh_f32 = ws.take<float>(NH * 4);
+  float* c_f32 = ws.take<float>(NH);
+  HB_REQUIRE(rh_f32 && c_f32, "scratch arena");
+  HB_TRY(to_float(a.dtype, a.c, c_f32, NH, s));
+  return forward_steps<__nv_bfloat16>(a, rh_f32, c_f32, s);
 }
 
 int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {

@@ -150,6 +150,7 @@ int lstm_backward_stepwise(const LstmBwd& a, float* dh_carry, float* dc_carry, c
 int lstm_forward(const LstmFwd& a, cudaStream_t s) {
   HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
+  if (a.T == 0) return HASTE_B200_OK;  // nothing to do; scratch pointers may be null
   HB_REQUIRE(a.W && a.R && a.b && a.h && a.c && a.v && a.tmp_Rh, "null pointer");
   HB_REQUIRE(a.T == 0 || a.x, "x is null");
   if (a.T == 0) return HASTE_B200_OK;
@@ -172,6 +173,7 @@ int lstm_forward(const LstmFwd& a, cudaStream_t s) {
 int lstm_backward(const LstmBwd& a, cudaStream_t s) {
   HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
+  if (a.T == 0) return HASTE_B200_OK;  // nothing to do; scratch pointers may be null
   HB_REQUIRE(a.W && a.R && a.h && a.c && a.dh_new && a.dc_new && a.dW && a.dR && a.db &&
                  a.dh && a.dc && a.v, "null pointer");
   if (a.T == 0) return HASTE_B200_OK;

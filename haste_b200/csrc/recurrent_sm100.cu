@@ -31,6 +31,7 @@
 // Replaces the per-step cuBLAS call + pointwise kernel of the reference
 // (lib/lstm_forward_gpu.cu.cc:210-310, lib/lstm_backward_gpu.cu.cc:246-316,
 //  lib/gru_forward_gpu.cu.cc:214-308, lib/gru_backward_gpu.cu.cc:252-320).
+#include <cstdlib>
 #include <mutex>
 
 #include "cells.cuh"
@@ -137,6 +138,7 @@ struct FwdParams {
   void* v;           // gate cache [T, N, 4H] (may be null when not training, GRU)
   const void* mask;  // [T, N, H]
   Sync sync;
+  int dbg;           // timing experiments only (wrong results): 1 no waits, 2 no MMA, 4 no h load
 };
 
 template <int G, int KSW, int SPLIT, typename T>
@@ -232,50 +234,62 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
     }
 
     // ---- wait until every CTA of this batch slice has published h_t
-    if (t > 0) {
+    if (t > 0 && !(p.dbg & 1)) {
       if (!wait_group(p.sync, bs, (unsigned int)p.nHS * t, &s_flag)) break;
     }
 
-    // ---- h_t rows of this batch slice -> shared memory (bf16 planes)
-    {
+    // ---- h_t rows of this batch slice -> shared memory (bf16 planes).  All loads of an
+    // m-tile are issued before any is consumed, so their L2 latencies overlap.
+    if (!(p.dbg & 4)) {
       const T* hsrc = hbuf + (long long)t * NH;
-      const int chunks_per_row = KPAD / 4;
-      const int total = BNR * chunks_per_row;
-      for (int e = tid; e < total; e += THREADS) {
-        const int r = e / chunks_per_row, kc = (e - r * chunks_per_row) * 4;
-        const int n = n0 + r;
-        float x[4] = {0.f, 0.f, 0.f, 0.f};
-        if (n < N) {
-          const T* src = hsrc + (long long)n * H + kc;
-          if (kc + 3 < H && (H & 3) == 0) {
-            if (sizeof(T) == 4) {
-              const float4 f = __ldcg(reinterpret_cast<const float4*>(src));
-              x[0] = f.x; x[1] = f.y; x[2] = f.z; x[3] = f.w;
-            } else {
-              const uint2 w2 = __ldcg(reinterpret_cast<const uint2*>(src));
-              const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&w2.x);
-              const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&w2.y);
-              x[0] = __low2float(p0); x[1] = __high2float(p0);
-              x[2] = __low2float(p1); x[3] = __high2float(p1);
-            }
-          } else {
+      constexpr int CPR = KPAD / 4;           // 4-element chunks per row
+      constexpr int CPT = 16 * CPR / THREADS; // chunks per thread per m-tile
+      const bool vec_ok = (H & 3) == 0;
+      for (int mt = 0; mt < p.MT; ++mt) {
+        float x[CPT][4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-              if (kc + j < H) x[j] = ldcg(src + j);
+        for (int i = 0; i < CPT; ++i) {
+          const int e = tid + i * THREADS;
+          const int r = mt * 16 + e / CPR, kc = (e % CPR) * 4;
+          const int n = n0 + r;
+          x[i][0] = x[i][1] = x[i][2] = x[i][3] = 0.f;
+          if (n < N && kc < H) {
+            const T* src = hsrc + (long long)n * H + kc;
+            if (vec_ok) {
+              if (sizeof(T) == 4) {
+                const float4 f = __ldcg(reinterpret_cast<const float4*>(src));
+                x[i][0] = f.x; x[i][1] = f.y; x[i][2] = f.z; x[i][3] = f.w;
+              } else {
+                const uint2 w2 = __ldcg(reinterpret_cast<const uint2*>(src));
+                const __nv_bfloat162 p0 = *reinterpret_cast<const __nv_bfloat162*>(&w2.x);
+                const __nv_bfloat162 p1 = *reinterpret_cast<const __nv_bfloat162*>(&w2.y);
+                x[i][0] = __low2float(p0); x[i][1] = __high2float(p0);
+                x[i][2] = __low2float(p1); x[i][3] = __high2float(p1);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (kc + j < H) x[i][j] = ldcg(src + j);
+            }
           }
         }
-        uint2 hi2, lo2;
-        if (SPLIT == 2) {
-          float hi[4], lo[4];
 #pragma unroll
-          for (int j = 0; j < 4; ++j) split_bf16(x[j], hi[j], lo[j]);
-          hi2 = make_uint2(pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]));
-          lo2 = make_uint2(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]));
-          *reinterpret_cast<uint2*>(a_lo + (size_t)r * AROW + kc) = lo2;
-        } else {
-          hi2 = make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+        for (int i = 0; i < CPT; ++i) {
+          const int e = tid + i * THREADS;
+          const int r = mt * 16 + e / CPR, kc = (e % CPR) * 4;
+          uint2 hi2;
+          if (SPLIT == 2) {
+            float hi[4], lo[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) split_bf16(x[i][j], hi[j], lo[j]);
+            hi2 = make_uint2(pack_bf16(hi[0], hi[1]), pack_bf16(hi[2], hi[3]));
+            *reinterpret_cast<uint2*>(a_lo + (size_t)r * AROW + kc) =
+                make_uint2(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]));
+          } else {
+            hi2 = make_uint2(pack_bf16(x[i][0], x[i][1]), pack_bf16(x[i][2], x[i][3]));
+          }
+          *reinterpret_cast<uint2*>(a_hi + (size_t)r * AROW + kc) = hi2;
         }
-        *reinterpret_cast<uint2*>(a_hi + (size_t)r * AROW + kc) = hi2;
       }
     }
     __syncthreads();
@@ -285,6 +299,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
       float acc[NT][4];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+      if (!(p.dbg & 2))
 #pragma unroll
       for (int ks = 0; ks < KSW; ++ks) {
         const int row = mt * 16 + (lane & 15);
@@ -377,7 +392,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
       }
       __syncthreads();  // `part` is reused by the next m-tile / step
     }
-    if (t + 1 < p.T) signal_group(p.sync, bs);
+    if (t + 1 < p.T && !(p.dbg & 1)) signal_group(p.sync, bs);
   }
 }
 
@@ -520,12 +535,13 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
         if (mt < p.MT) {
           float s = 0.f;
           const float* q0 = src + (size_t)(mt * 16 + nl) * U + ul;
-          for (int sidx = 0; sidx < p.nHS; sidx += 4) {
-            float a0 = __ldcg(q0 + (size_t)sidx * blk);
-            float a1 = (sidx + 1 < p.nHS) ? __ldcg(q0 + (size_t)(sidx + 1) * blk) : 0.f;
-            float a2 = (sidx + 2 < p.nHS) ? __ldcg(q0 + (size_t)(sidx + 2) * blk) : 0.f;
-            float a3 = (sidx + 3 < p.nHS) ? __ldcg(q0 + (size_t)(sidx + 3) * blk) : 0.f;
-            s += (a0 + a1) + (a2 + a3);
+          // 8 loads in flight per pass; the summation order is fixed by this code
+          for (int s0 = 0; s0 < p.nHS; s0 += 8) {
+            float a[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+              a[k] = (s0 + k < p.nHS) ? __ldcg(q0 + (size_t)(s0 + k) * blk) : 0.f;
+            s += ((a[0] + a[1]) + (a[2] + a[3])) + ((a[4] + a[5]) + (a[6] + a[7]));
           }
           dh_c[mt] += s;
         }
@@ -772,6 +788,15 @@ int run_bwd(BwdParams& p, const Geometry& g, cudaStream_t s) {
 
 bool path_allowed() { return recurrence_path() != HASTE_B200_PATH_STEPWISE; }
 
+int debug_skip() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HASTE_B200_DEBUG_SKIP");
+    v = e ? atoi(e) : 0;
+  }
+  return v;
+}
+
 }  // namespace
 
 int lstm_forward_persistent(const LstmFwd& a, cudaStream_t s) {
@@ -783,7 +808,7 @@ int lstm_forward_persistent(const LstmFwd& a, cudaStream_t s) {
   HB_TRY(make_sync(g, 0, &sm, s));
   const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
   FwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.b,
-              nullptr, a.v, a.h, a.c, a.v, a.zoneout_mask, sm.sync};
+              nullptr, a.v, a.h, a.c, a.v, a.zoneout_mask, sm.sync, debug_skip()};
   if (a.dtype == HASTE_B200_F32) return run_fwd<4, 2, float>(p, g, s);
   return run_fwd<4, 1, __nv_bfloat16>(p, g, s);
 }
@@ -797,7 +822,7 @@ int gru_forward_persistent(const GruFwd& a, cudaStream_t s) {
   HB_TRY(make_sync(g, 0, &sm, s));
   const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
   FwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.bx,
-              a.br, a.tmp_Wx, a.h, nullptr, a.v, a.zoneout_mask, sm.sync};
+              a.br, a.tmp_Wx, a.h, nullptr, a.v, a.zoneout_mask, sm.sync, debug_skip()};
   if (a.dtype == HASTE_B200_F32) return run_fwd<3, 2, float>(p, g, s);
   return run_fwd<3, 1, __nv_bfloat16>(p, g, s);
 }
