@@ -33,10 +33,11 @@ int haste_b200_profile_read(float* ms, int n) {
 
 int haste_b200_sync_check(void* stream) {
   HB_CUDA_OK(cudaStreamSynchronize((cudaStream_t)stream));
-  const int code = hb::take_error_word();
+  int d[4] = {0, 0, 0, 0};
+  const int code = hb::take_error_word(d);
   if (code != 0) {
-    hb::set_last_error("a kernel gave up on a bounded wait (code %d); results are incomplete",
-                       code);
+    hb::set_last_error("a kernel gave up on a bounded wait (code %d, detail %d %d %d 0x%x); "
+                       "results are incomplete", code, d[0], d[1], d[2], (unsigned)d[3]);
     return HASTE_B200_ERR_TIMEOUT;
   }
   return HASTE_B200_OK;

@@ -100,7 +100,7 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s);
 int layer_norm_gru_forward(const LnGruFwd& a, cudaStream_t s);
 int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s);
 
-// Persistent-kernel implementations of the recurrences (recurrent_sm100.cu).
+// Persistent-kernel implementations of the recurrences (recurrent_kernels.cuh).
 // Each returns HASTE_B200_ERR_UNSUPPORTED (without touching any buffer) when the
 // shape does not fit, in which case the caller runs its step-wise path.
 // Forward: the input projection is already in a.v (LSTM) / a.tmp_Wx (GRU).

@@ -1,7 +1,7 @@
 // LSTM forward / backward drivers and their step-wise kernels.
 //
 // Two implementations of the recurrence sit behind each driver:
-//   * the persistent kernels of recurrent_sm100.cu (one launch per layer pass,
+//   * the persistent kernels of recurrent_kernels.cuh (one launch per layer pass,
 //     recurrent weights resident on chip, tensor-core step product), used
 //     whenever the shape fits; and
 //   * the step-wise path in this file (one contraction + one pointwise launch per

@@ -1,0 +1,9 @@
+// Instantiates the persistent gru fwd recurrence kernels for f32 storage
+// (one translation unit per combination so that they compile in parallel).
+#include "recurrent_kernels.cuh"
+
+namespace hb {
+namespace rec {
+int run_fwd_gru_f32(FwdParams& p, const Geometry& g, cudaStream_t s) { return run_fwd<3, 2, float>(p, g, s); }
+}  // namespace rec
+}  // namespace hb

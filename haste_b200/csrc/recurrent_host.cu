@@ -1,0 +1,139 @@
+// Host side of the persistent recurrence kernels (recurrent_kernels.cuh): tiling choice,
+// exchange-buffer scratch, and the four entry points the cell drivers call.
+#include <cstdlib>
+
+#include "recurrent_kernels.cuh"
+
+namespace hb {
+namespace rec {
+
+int sm_count() {
+  static int n = 0;
+  if (!n) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (n <= 0) n = 148;
+  }
+  return n;
+}
+
+namespace {
+
+constexpr int MAX_MT = 4;
+
+// Picks the batch tiling: as many CTAs as fit on the GPU at once (one CTA per SM).
+bool pick_geometry(int N, int H, Geometry* g) {
+  const int nHS = ceil_div(H, U);
+  const int sms = sm_count();
+  for (int mt = 1; mt <= MAX_MT; ++mt) {
+    const int nBS = ceil_div(N, 16 * mt);
+    if ((long long)nHS * nBS <= sms) {
+      g->nHS = nHS; g->nBS = nBS; g->MT = mt;
+      return true;
+    }
+  }
+  return false;
+}
+
+bool supported(int dtype, int N, int H, Geometry* g) {
+  if (recurrence_path() == HASTE_B200_PATH_STEPWISE) return false;
+  if (dtype == HASTE_B200_F32 && H > 512) return false;   // R slice must fit the register file
+  if (dtype == HASTE_B200_BF16 && H > 1024) return false;
+  return pick_geometry(N, H, g);
+}
+
+int debug_skip() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("HASTE_B200_DEBUG_SKIP");
+    v = e ? atoi(e) : 0;
+  }
+  return v;
+}
+
+// Zeroed scratch: abort flag followed by `words` exchange words.
+int make_scratch(size_t words, Sync* sync, uint32_t** xwords, cudaStream_t s) {
+  Arena ws;
+  const size_t bytes = Arena::pad(4096) + Arena::pad(words * 4);
+  HB_TRY(make_arena(&ws, s, bytes + 512, /*slot=*/2));
+  int* flag = ws.take<int>(1024);
+  uint32_t* x = ws.take<uint32_t>(words);
+  HB_REQUIRE(flag && x, "scratch arena");
+  HB_CUDA_OK(cudaMemsetAsync(flag, 0, bytes, s));
+  sync->abort_flag = flag;
+  sync->err = device_error_word();
+  HB_REQUIRE(sync->err, "error word");
+  *xwords = x;
+  return HASTE_B200_OK;
+}
+
+}  // namespace
+}  // namespace rec
+
+using namespace rec;
+
+int lstm_forward_persistent(const LstmFwd& a, cudaStream_t s) {
+  Geometry g;
+  if (!supported(a.dtype, a.N, a.H, &g)) return HASTE_B200_ERR_UNSUPPORTED;
+  const int Hx = (a.H + 3) & ~3;
+  Sync sync;
+  uint32_t* xbuf = nullptr;
+  HB_TRY(make_scratch((size_t)2 * a.N * Hx, &sync, &xbuf, s));
+  const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
+  FwdParams p{a.T, a.N, a.H, Hx, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.b,
+              nullptr, a.v, a.h, a.c, a.v, a.zoneout_mask, xbuf, sync, debug_skip()};
+  return a.dtype == HASTE_B200_F32 ? run_fwd_lstm_f32(p, g, s) : run_fwd_lstm_bf16(p, g, s);
+}
+
+int gru_forward_persistent(const GruFwd& a, cudaStream_t s) {
+  Geometry g;
+  if (!supported(a.dtype, a.N, a.H, &g)) return HASTE_B200_ERR_UNSUPPORTED;
+  const int Hx = (a.H + 3) & ~3;
+  Sync sync;
+  uint32_t* xbuf = nullptr;
+  HB_TRY(make_scratch((size_t)2 * a.N * Hx, &sync, &xbuf, s));
+  const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
+  FwdParams p{a.T, a.N, a.H, Hx, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.bx,
+              a.br, a.tmp_Wx, a.h, nullptr, a.v, a.zoneout_mask, xbuf, sync, debug_skip()};
+  return a.dtype == HASTE_B200_F32 ? run_fwd_gru_f32(p, g, s) : run_fwd_gru_bf16(p, g, s);
+}
+
+// The persistent backward kernels leave the recurrent contribution of the very last
+// processed step (t = 0) out of dh (nothing inside the kernel consumes it); it is added
+// here with one small contraction: dh += dG_0 . R^T.
+int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry, cudaStream_t s) {
+  Geometry g;
+  if (!supported(a.dtype, a.N, a.H, &g)) return HASTE_B200_ERR_UNSUPPORTED;
+  Sync sync;
+  uint32_t* exch = nullptr;
+  HB_TRY(make_scratch((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U, &sync, &exch, s));
+  BwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R, a.h,
+              a.c, a.v, a.dh_new, a.dc_new, nullptr, nullptr, a.zoneout_mask, dh_carry, dc_carry,
+              exch, sync, debug_skip()};
+  int st_ = a.dtype == HASTE_B200_F32 ? run_bwd_lstm_f32(p, g, s) : run_bwd_lstm_bf16(p, g, s);
+  if (st_ != HASTE_B200_OK) return st_;
+  const int H = a.H;
+  GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 4 * H, a.v, 4LL * H, 1, a.R,
+              a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 4LL * H, dh_carry, H, 1};
+  return gemm_small(gd, s);
+}
+
+int gru_backward_persistent(const GruBwd& a, float* dh_carry, cudaStream_t s) {
+  Geometry g;
+  if (!supported(a.dtype, a.N, a.H, &g)) return HASTE_B200_ERR_UNSUPPORTED;
+  Sync sync;
+  uint32_t* exch = nullptr;
+  HB_TRY(make_scratch((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U, &sync, &exch, s));
+  BwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R, a.h,
+              nullptr, const_cast<void*>(a.v), a.dh_new, nullptr, a.dp, a.dq, a.zoneout_mask,
+              dh_carry, nullptr, exch, sync, debug_skip()};
+  int st_ = a.dtype == HASTE_B200_F32 ? run_bwd_gru_f32(p, g, s) : run_bwd_gru_bf16(p, g, s);
+  if (st_ != HASTE_B200_OK) return st_;
+  const int H = a.H;
+  GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 3 * H, a.dq, 3LL * H, 1, a.R,
+              a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 3LL * H, dh_carry, H, 1};
+  return gemm_small(gd, s);
+}
+
+}  // namespace hb

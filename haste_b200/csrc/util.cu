@@ -49,11 +49,15 @@ int* device_error_word() {
   return g_errw;  // unified addressing: the host pointer is valid on every device
 }
 
-int take_error_word() {
+int take_error_word(int* detail) {
   if (!g_errw) return 0;
   volatile int* w = g_errw;
   const int v = *w;
-  if (v) *w = 0;
+  if (v) {
+    if (detail)
+      for (int i = 0; i < 4; ++i) detail[i] = w[1 + i];
+    *w = 0;
+  }
   return v;
 }
 

@@ -14,7 +14,7 @@ void count_launch(int n);
 // copy anything back.  device_error_word() is the pointer kernels get;
 // take_error_word() returns the current value and clears it.
 int* device_error_word();
-int take_error_word();
+int take_error_word(int* detail = nullptr);  // detail: 4 ints of kernel-specific context
 
 // Library-owned scratch.  One grow-only buffer per (device, stream, slot), so
 // calls issued on different streams never share scratch.  The pointer stays
