@@ -568,43 +568,57 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
       const uint32_t want = (((uint32_t)(ti - 1) >> 1) & 1u) ^ 1u;
       const uint32_t* src =
           p.exch + ((((size_t)((ti - 1) & 1) * nBS + bs) * p.nHS + hs) * p.nHS) * blk;
+      // Thread (row nl, unit ul) sits in a group of 4 adjacent lanes that share
+      // (row, unit quad); lane sg = ul & 3 of the group fetches 16-byte pieces (4 units) from
+      // sources sg*8 .. sg*8+7 of each pass of 32 sources, all loads in flight together,
+      // and a two-step butterfly adds the four lanes.  The summation order is fixed.
+      const int sg = ul & 3, quad = ul >> 2;
 #pragma unroll
       for (int mt = 0; mt < MTMAX; ++mt) {
-        if (mt < p.MT && alive) {
-          float s = 0.f;
-          const uint32_t* q0 = src + (size_t)(mt * 16 + nl) * U + ul;
-          for (int s0 = 0; s0 < p.nHS && alive; s0 += 8) {
-            uint32_t a[8];
+        if (mt < p.MT) {  // uniform: the shuffles below are executed by whole warps
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint32_t* q0 = src + (size_t)(mt * 16 + nl) * U + quad * 4;
+          for (int s0 = 0; s0 < p.nHS && alive; s0 += 32) {
+            uint4 a[8];
             const long long t0 = clock64();
             unsigned int spins = 0;
+            const uint32_t rdy = want << 30;
             for (;;) {
-              // issue every load before looking at any of them
 #pragma unroll
-              for (int k = 0; k < 8; ++k)
-                a[k] = (s0 + k < p.nHS) ? ld_relaxed_u32(q0 + (size_t)(s0 + k) * blk) : (want << 30);
+              for (int k = 0; k < 8; ++k) {
+                const int sidx = s0 + sg * 8 + k;
+                a[k] = (sidx < p.nHS) ? ld_relaxed_u32x4(q0 + (size_t)sidx * blk)
+                                      : make_uint4(rdy, rdy, rdy, rdy);
+              }
               bool ok = true;
 #pragma unroll
-              for (int k = 0; k < 8; ++k) ok = ok && xword_ready(a[k], want);
+              for (int k = 0; k < 8; ++k)
+                ok = ok && xword_ready(a[k].x, want) && xword_ready(a[k].y, want) &&
+                     xword_ready(a[k].z, want) && xword_ready(a[k].w, want);
               if (ok) break;
               if ((++spins & 63u) == 0) {
                 if (*reinterpret_cast<volatile int*>(p.sync.abort_flag) != 0) { alive = false; break; }
                 if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
-                  int bad = 0;
-                  for (int k = 0; k < 8; ++k)
-                    if (s0 + k < p.nHS && !xword_ready(a[k], want)) bad |= 1 << k;
-                  const int srcblk = bs * p.nHS + s0 + __ffs(bad) - 1;
-                  raise_abort(p.sync, &s_abort, 17, blockIdx.x * 1000 + tid, ti * 100 + s0,
-                              bad, *reinterpret_cast<volatile int*>(p.sync.abort_flag + 64 + srcblk));
+                  raise_abort(p.sync, &s_abort, 17, blockIdx.x * 1000 + tid, ti * 100 + s0);
                   alive = false;
                   break;
                 }
               }
             }
-            // fixed summation order
-            s += ((xword_value(a[0]) + xword_value(a[1])) + (xword_value(a[2]) + xword_value(a[3]))) +
-                 ((xword_value(a[4]) + xword_value(a[5])) + (xword_value(a[6]) + xword_value(a[7])));
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              s4[0] += xword_value(a[k].x);
+              s4[1] += xword_value(a[k].y);
+              s4[2] += xword_value(a[k].z);
+              s4[3] += xword_value(a[k].w);
+            }
           }
-          dh_c[mt] += s;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            s4[j] += __shfl_xor_sync(0xffffffffu, s4[j], 1);
+            s4[j] += __shfl_xor_sync(0xffffffffu, s4[j], 2);
+          }
+          dh_c[mt] += sg == 0 ? s4[0] : (sg == 1 ? s4[1] : (sg == 2 ? s4[2] : s4[3]));
         }
       }
     }
