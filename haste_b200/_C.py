@@ -25,10 +25,10 @@ SIGNATURES = {
     "haste_b200_indrnn_backward": [_i] * 6 + [_p] * 14,
     "haste_b200_layer_norm_forward": [_i] * 3 + [_p] * 6,
     "haste_b200_layer_norm_backward": [_i] * 3 + [_p] * 8,
-    "haste_b200_layer_norm_lstm_forward": [_i] * 6 + [_p] * 17 + [_f, _p, _p],
-    "haste_b200_layer_norm_lstm_backward": [_i] * 6 + [_p] * 29,
-    "haste_b200_layer_norm_gru_forward": [_i] * 6 + [_p] * 14 + [_f, _p, _p],
-    "haste_b200_layer_norm_gru_backward": [_i] * 6 + [_p] * 24,
+    "haste_b200_layer_norm_lstm_forward": [_i] * 6 + [_p] * 18 + [_f, _p, _p],
+    "haste_b200_layer_norm_lstm_backward": [_i] * 6 + [_p] * 31,
+    "haste_b200_layer_norm_gru_forward": [_i] * 6 + [_p] * 15 + [_f, _p, _p],
+    "haste_b200_layer_norm_gru_backward": [_i] * 6 + [_p] * 26,
     "haste_b200_layer_norm_indrnn_forward": [_i] * 6 + [_p] * 9 + [_f, _p, _p],
     "haste_b200_layer_norm_indrnn_backward": [_i] * 6 + [_p] * 18,
     "haste_b200_gemm": [_i] * 4 + [_p, _ll, _ll, _p, _ll, _ll, _p, _ll, _i, _p],

@@ -136,11 +136,12 @@ int haste_b200_layer_norm_backward(int dtype, int rows, int width, const void* g
 
 int haste_b200_layer_norm_lstm_forward(
     int dtype, int training, int T, int N, int C, int H, const void* W, const void* R,
-    const void* b, const void* gamma, const void* gamma_h, const void* beta_h, const void* x,
+    const void* b, const void* gamma_Wx, const void* gamma_Rh, const void* gamma_h,
+    const void* beta_h, const void* x,
     void* h, void* c, void* act_Wx, void* act_Wx_norm, void* cache_Wx, void* act_Rh,
     void* cache_Rh, void* act_c_norm, void* cache_c, void* tmp_Rh, float zoneout_prob,
     const void* zoneout_mask, void* stream) {
-  LnLstmFwd a{dtype, training, T, N, C, H, W, R, b, gamma, gamma_h, beta_h, x, h, c, act_Wx,
+  LnLstmFwd a{dtype, training, T, N, C, H, W, R, b, gamma_Wx, gamma_Rh, gamma_h, beta_h, x, h, c, act_Wx,
               act_Wx_norm, cache_Wx, act_Rh, cache_Rh, act_c_norm, cache_c, tmp_Rh, zoneout_prob,
               zoneout_mask};
   return layer_norm_lstm_forward(a, (cudaStream_t)stream);
@@ -148,35 +149,40 @@ int haste_b200_layer_norm_lstm_forward(
 
 int haste_b200_layer_norm_lstm_backward(
     int dtype, int transposed_inputs, int T, int N, int C, int H, const void* W, const void* R,
-    const void* b, const void* gamma, const void* gamma_h, const void* beta_h, const void* x,
+    const void* b, const void* gamma_Wx, const void* gamma_Rh, const void* gamma_h,
+    const void* beta_h, const void* x,
     const void* h, const void* c, const void* dh_new, const void* dc_new, void* dx, void* dW,
-    void* dR, void* db, void* dgamma, void* dgamma_h, void* dbeta_h, void* dh, void* dc,
+    void* dR, void* db, void* dgamma_Wx, void* dgamma_Rh, void* dgamma_h, void* dbeta_h, void* dh,
+    void* dc,
     void* act_Wx, void* act_Wx_norm, const void* cache_Wx, void* act_Rh, const void* cache_Rh,
     void* act_c_norm, const void* cache_c, const void* zoneout_mask, void* stream) {
-  LnLstmBwd a{dtype, transposed_inputs, T, N, C, H, W, R, b, gamma, gamma_h, beta_h, x, h, c,
-              dh_new, dc_new, dx, dW, dR, db, dgamma, dgamma_h, dbeta_h, dh, dc, act_Wx,
+  LnLstmBwd a{dtype, transposed_inputs, T, N, C, H, W, R, b, gamma_Wx, gamma_Rh, gamma_h, beta_h,
+              x, h, c, dh_new, dc_new, dx, dW, dR, db, dgamma_Wx, dgamma_Rh, dgamma_h, dbeta_h, dh,
+              dc, act_Wx,
               act_Wx_norm, cache_Wx, act_Rh, cache_Rh, act_c_norm, cache_c, zoneout_mask};
   return layer_norm_lstm_backward(a, (cudaStream_t)stream);
 }
 
 int haste_b200_layer_norm_gru_forward(
     int dtype, int training, int T, int N, int C, int H, const void* W, const void* R,
-    const void* bx, const void* br, const void* gamma, const void* x, void* h, void* v,
+    const void* bx, const void* br, const void* gamma_Wx, const void* gamma_Rh, const void* x,
+    void* h, void* v,
     void* act_Wx, void* cache_Wx, void* tmp_Wx_norm, void* act_Rh, void* cache_Rh,
     void* tmp_Rh_norm, float zoneout_prob, const void* zoneout_mask, void* stream) {
-  LnGruFwd a{dtype, training, T, N, C, H, W, R, bx, br, gamma, x, h, v, act_Wx, cache_Wx,
+  LnGruFwd a{dtype, training, T, N, C, H, W, R, bx, br, gamma_Wx, gamma_Rh, x, h, v, act_Wx, cache_Wx,
              tmp_Wx_norm, act_Rh, cache_Rh, tmp_Rh_norm, zoneout_prob, zoneout_mask};
   return layer_norm_gru_forward(a, (cudaStream_t)stream);
 }
 
 int haste_b200_layer_norm_gru_backward(
     int dtype, int transposed_inputs, int T, int N, int C, int H, const void* W, const void* R,
-    const void* bx, const void* br, const void* gamma, const void* x, const void* h,
-    const void* v, const void* dh_new, void* dx, void* dW, void* dR, void* dbx, void* dbr,
-    void* dgamma, void* dh, void* dp, void* dq, const void* act_Wx, const void* cache_Wx,
+    const void* bx, const void* br, const void* gamma_Wx, const void* gamma_Rh, const void* x,
+    const void* h, const void* v, const void* dh_new, void* dx, void* dW, void* dR, void* dbx,
+    void* dbr, void* dgamma_Wx, void* dgamma_Rh, void* dh, void* dp, void* dq, const void* act_Wx,
+    const void* cache_Wx,
     void* act_Rh, const void* cache_Rh, const void* zoneout_mask, void* stream) {
-  LnGruBwd a{dtype, transposed_inputs, T, N, C, H, W, R, bx, br, gamma, x, h, v, dh_new, dx, dW,
-             dR, dbx, dbr, dgamma, dh, dp, dq, act_Wx, cache_Wx, act_Rh, cache_Rh, zoneout_mask};
+  LnGruBwd a{dtype, transposed_inputs, T, N, C, H, W, R, bx, br, gamma_Wx, gamma_Rh, x, h, v,
+             dh_new, dx, dW, dR, dbx, dbr, dgamma_Wx, dgamma_Rh, dh, dp, dq, act_Wx, cache_Wx, act_Rh, cache_Rh, zoneout_mask};
   return layer_norm_gru_backward(a, (cudaStream_t)stream);
 }
 

@@ -55,7 +55,7 @@ struct IndrnnBwd {
 };
 struct LnLstmFwd {
   int dtype, training, T, N, C, H;
-  const void *W, *R, *b, *gamma, *gamma_h, *beta_h, *x;
+  const void *W, *R, *b, *gamma_Wx, *gamma_Rh, *gamma_h, *beta_h, *x;
   void *h, *c, *act_Wx, *act_Wx_norm, *cache_Wx, *act_Rh, *cache_Rh, *act_c_norm, *cache_c,
       *tmp_Rh;
   float zoneout_prob;
@@ -63,8 +63,8 @@ struct LnLstmFwd {
 };
 struct LnLstmBwd {
   int dtype, transposed_inputs, T, N, C, H;
-  const void *W, *R, *b, *gamma, *gamma_h, *beta_h, *x, *h, *c, *dh_new, *dc_new;
-  void *dx, *dW, *dR, *db, *dgamma, *dgamma_h, *dbeta_h, *dh, *dc, *act_Wx, *act_Wx_norm;
+  const void *W, *R, *b, *gamma_Wx, *gamma_Rh, *gamma_h, *beta_h, *x, *h, *c, *dh_new, *dc_new;
+  void *dx, *dW, *dR, *db, *dgamma_Wx, *dgamma_Rh, *dgamma_h, *dbeta_h, *dh, *dc, *act_Wx, *act_Wx_norm;
   const void* cache_Wx;
   void* act_Rh;
   const void* cache_Rh;
@@ -74,15 +74,15 @@ struct LnLstmBwd {
 };
 struct LnGruFwd {
   int dtype, training, T, N, C, H;
-  const void *W, *R, *bx, *br, *gamma, *x;
+  const void *W, *R, *bx, *br, *gamma_Wx, *gamma_Rh, *x;
   void *h, *v, *act_Wx, *cache_Wx, *tmp_Wx_norm, *act_Rh, *cache_Rh, *tmp_Rh_norm;
   float zoneout_prob;
   const void* zoneout_mask;
 };
 struct LnGruBwd {
   int dtype, transposed_inputs, T, N, C, H;
-  const void *W, *R, *bx, *br, *gamma, *x, *h, *v, *dh_new;
-  void *dx, *dW, *dR, *dbx, *dbr, *dgamma, *dh, *dp, *dq;
+  const void *W, *R, *bx, *br, *gamma_Wx, *gamma_Rh, *x, *h, *v, *dh_new;
+  void *dx, *dW, *dR, *dbx, *dbr, *dgamma_Wx, *dgamma_Rh, *dh, *dp, *dq;
   const void *act_Wx, *cache_Wx;
   void* act_Rh;  // overwritten with d(h.R)
   const void* cache_Rh;

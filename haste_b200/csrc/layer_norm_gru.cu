@@ -31,7 +31,7 @@ int forward_steps(const LnGruFwd& a, cudaStream_t s) {
   T* v = (T*)a.v;
   T* act_Rh = (T*)a.act_Rh;
   const T* Wx = (const T*)a.tmp_Wx_norm;
-  const T* gamma1 = (const T*)a.gamma + 3 * H;
+  const T* gamma1 = (const T*)a.gamma_Rh;
   const T* mask = (const T*)a.zoneout_mask;
   const bool zo = a.zoneout_prob != 0.0f && mask != nullptr;
   for (int t = 0; t < a.T; ++t) {
@@ -58,7 +58,7 @@ int backward_steps(const LnGruBwd& a, float* dh_carry, void* dgamma1, float* lns
   T* dp = (T*)a.dp;
   T* dq = (T*)a.dq;
   T* act_Rh = (T*)a.act_Rh;
-  const T* gamma1 = (const T*)a.gamma + 3 * H;
+  const T* gamma1 = (const T*)a.gamma_Rh;
   const T* mask = (const T*)a.zoneout_mask;
   const long long r_rs = a.transposed_inputs ? H : 1;
   const long long r_cs = a.transposed_inputs ? 1 : 3LL * H;
@@ -83,7 +83,7 @@ int backward_steps(const LnGruBwd& a, float* dh_carry, void* dgamma1, float* lns
 int layer_norm_gru_forward(const LnGruFwd& a, cudaStream_t s) {
   HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
-  HB_REQUIRE(a.W && a.R && a.bx && a.br && a.gamma && a.h && a.act_Wx && a.cache_Wx &&
+  HB_REQUIRE(a.W && a.R && a.bx && a.br && a.gamma_Wx && a.gamma_Rh && a.h && a.act_Wx && a.cache_Wx &&
                  a.tmp_Wx_norm && a.act_Rh && a.cache_Rh && a.tmp_Rh_norm, "null pointer");
   HB_REQUIRE(!a.training || a.v, "v is required when training");
   if (a.T == 0) return HASTE_B200_OK;
@@ -94,7 +94,7 @@ int layer_norm_gru_forward(const LnGruFwd& a, cudaStream_t s) {
              3LL * a.H, 0};
   g.precise = 1;
   HB_TRY(gemm(g, s));
-  HB_TRY(layer_norm_forward(a.dtype, (int)TN, 3 * a.H, a.gamma, nullptr, a.act_Wx, a.tmp_Wx_norm,
+  HB_TRY(layer_norm_forward(a.dtype, (int)TN, 3 * a.H, a.gamma_Wx, nullptr, a.act_Wx, a.tmp_Wx_norm,
                             a.cache_Wx, s));
   if (a.dtype == HASTE_B200_F32) return forward_steps<float>(a, s);
   return forward_steps<__nv_bfloat16>(a, s);
@@ -103,8 +103,8 @@ int layer_norm_gru_forward(const LnGruFwd& a, cudaStream_t s) {
 int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s) {
   HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
-  HB_REQUIRE(a.W && a.R && a.gamma && a.h && a.v && a.dh_new && a.dW && a.dR && a.dbx && a.dbr &&
-                 a.dgamma && a.dh && a.dp && a.dq && a.act_Wx && a.cache_Wx && a.act_Rh &&
+  HB_REQUIRE(a.W && a.R && a.gamma_Wx && a.gamma_Rh && a.h && a.v && a.dh_new && a.dW && a.dR && a.dbx && a.dbr &&
+                 a.dgamma_Wx && a.dgamma_Rh && a.dh && a.dp && a.dq && a.act_Wx && a.cache_Wx && a.act_Rh &&
                  a.cache_Rh, "null pointer");
   if (a.T == 0) return HASTE_B200_OK;
   HB_REQUIRE(a.x && a.dx, "x/dx is null");
@@ -125,7 +125,7 @@ int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s) {
   float* acc = ws.take<float>(3 * H);
   HB_REQUIRE(dh_carry && cs && lns && acc, "scratch arena");
   HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
-  void* dgamma1 = (char*)a.dgamma + (size_t)3 * H * es;
+  void* dgamma1 = a.dgamma_Rh;
   if (bf) {
     HB_CUDA_OK(cudaMemsetAsync(acc, 0, 3 * H * sizeof(float), s));
     dgamma1 = acc;
@@ -133,15 +133,15 @@ int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s) {
   int st_ = bf ? backward_steps<__nv_bfloat16>(a, dh_carry, dgamma1, lns, s)
                : backward_steps<float>(a, dh_carry, dgamma1, lns, s);
   HB_TRY(st_);
-  if (bf) HB_TRY(add_float_into(a.dtype, acc, (char*)a.dgamma + (size_t)3 * H * es, 3 * H, s));
+  if (bf) HB_TRY(add_float_into(a.dtype, acc, a.dgamma_Rh, 3 * H, s));
   HB_TRY(from_float(a.dtype, dh_carry, a.dh, NH, s));
 
   // dp/dq hold gradients w.r.t. the normalised projections (+ bias).
   HB_TRY(colsum(a.dtype, a.dp, 3LL * H, (int)TN, 3 * H, a.dtype, a.dbx, 1, cs, s));
   HB_TRY(colsum(a.dtype, a.dq, 3LL * H, (int)TN, 3 * H, a.dtype, a.dbr, 1, cs, s));
   // LayerNorm 1 backward over all steps, in place on dp.
-  HB_TRY(layer_norm_backward(a.dtype, (int)TN, 3 * H, a.gamma, a.act_Wx, a.dp, a.dp, a.dtype,
-                             a.dgamma, nullptr, a.cache_Wx, lns, s));
+  HB_TRY(layer_norm_backward(a.dtype, (int)TN, 3 * H, a.gamma_Wx, a.act_Wx, a.dp, a.dp, a.dtype,
+                             a.dgamma_Wx, nullptr, a.cache_Wx, lns, s));
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 3 * H, a.dp, 3LL * H, 1, a.W, tr ? C : 1,
               tr ? 1 : 3LL * H, a.dx, C, 0};

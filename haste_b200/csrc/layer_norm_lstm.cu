@@ -117,7 +117,7 @@ int forward_steps(const LnLstmFwd& a, float* rh_f32, float* c_f32, cudaStream_t 
   T* v = (T*)a.act_Wx_norm;
   T* act_Rh = (T*)a.act_Rh;
   T* c_norm = (T*)a.act_c_norm;
-  const T* gamma1 = (const T*)a.gamma + 4 * H;
+  const T* gamma1 = (const T*)a.gamma_Rh;
   const T* mask = (const T*)a.zoneout_mask;
   const bool zo = a.zoneout_prob != 0.0f && mask != nullptr;
   dim3 block(128), grid(ceil_div(H, 128), N);
@@ -177,7 +177,7 @@ int backward_steps(const LnLstmBwd& a, float* dh_carry, float* dc_carry, void* d
   T* v = (T*)a.act_Wx_norm;
   T* act_Rh = (T*)a.act_Rh;
   T* c_norm = (T*)a.act_c_norm;
-  const T* gamma1 = (const T*)a.gamma + 4 * H;
+  const T* gamma1 = (const T*)a.gamma_Rh;
   const T* mask = (const T*)a.zoneout_mask;
   const long long r_rs = a.transposed_inputs ? H : 1;
   const long long r_cs = a.transposed_inputs ? 1 : 4LL * H;
@@ -216,7 +216,7 @@ int backward_steps(const LnLstmBwd& a, float* dh_carry, float* dc_carry, void* d
 int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
   HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
-  HB_REQUIRE(a.W && a.R && a.b && a.gamma && a.gamma_h && a.beta_h && a.h && a.c && a.act_Wx &&
+  HB_REQUIRE(a.W && a.R && a.b && a.gamma_Wx && a.gamma_Rh && a.gamma_h && a.beta_h && a.h && a.c && a.act_Wx &&
                  a.act_Wx_norm && a.cache_Wx && a.act_Rh && a.cache_Rh && a.act_c_norm &&
                  a.cache_c && a.tmp_Rh, "null pointer");
   if (a.T == 0) return HASTE_B200_OK;
@@ -227,7 +227,7 @@ int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
              4LL * a.H, 0};
   g.precise = 1;
   HB_TRY(gemm(g, s));
-  HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma, nullptr, a.act_Wx, a.act_Wx_norm,
+  HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma_Wx, nullptr, a.act_Wx, a.act_Wx_norm,
                             a.cache_Wx, s));
   if (a.dtype == HASTE_B200_F32) return forward_steps<float>(a, nullptr, nullptr, s);
   const size_t NH = (size_t)a.N * a.H;
@@ -243,8 +243,8 @@ int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
 int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
   HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
-  HB_REQUIRE(a.W && a.R && a.gamma && a.gamma_h && a.h && a.c && a.dh_new && a.dc_new && a.dW &&
-                 a.dR && a.db && a.dgamma && a.dgamma_h && a.dbeta_h && a.dh && a.dc &&
+  HB_REQUIRE(a.W && a.R && a.gamma_Wx && a.gamma_Rh && a.gamma_h && a.h && a.c && a.dh_new && a.dc_new && a.dW &&
+                 a.dR && a.db && a.dgamma_Wx && a.dgamma_Rh && a.dgamma_h && a.dbeta_h && a.dh && a.dc &&
                  a.act_Wx && a.act_Wx_norm && a.cache_Wx && a.act_Rh && a.cache_Rh &&
                  a.act_c_norm && a.cache_c, "null pointer");
   if (a.T == 0) return HASTE_B200_OK;
@@ -269,7 +269,7 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
   HB_TRY(to_float(a.dtype, a.dc, dc_carry, NH, s));
 
   const size_t es = dtype_size(a.dtype);
-  void* dgamma1 = (char*)a.dgamma + (size_t)4 * H * es;
+  void* dgamma1 = a.dgamma_Rh;
   void* dgamma_h = a.dgamma_h;
   void* dbeta_h = a.dbeta_h;
   if (bf) {
@@ -284,7 +284,7 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
                                        HASTE_B200_F32, lns, s);
   HB_TRY(st_);
   if (bf) {
-    HB_TRY(add_float_into(a.dtype, acc, (char*)a.dgamma + (size_t)4 * H * es, 4 * H, s));
+    HB_TRY(add_float_into(a.dtype, acc, a.dgamma_Rh, 4 * H, s));
     HB_TRY(add_float_into(a.dtype, acc + 4 * H, a.dgamma_h, H, s));
     HB_TRY(add_float_into(a.dtype, acc + 5 * H, a.dbeta_h, H, s));
   }
@@ -294,8 +294,8 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
   // act_Wx_norm now holds the gradient w.r.t. (LN1(x.W) + LN2(h.R) + b).
   HB_TRY(colsum(a.dtype, a.act_Wx_norm, 4LL * H, (int)TN, 4 * H, a.dtype, a.db, 1, cs, s));
   // LayerNorm 1 backward over all steps: act_Wx <- d/d(x.W).
-  HB_TRY(layer_norm_backward(a.dtype, (int)TN, 4 * H, a.gamma, a.act_Wx, a.act_Wx_norm, a.act_Wx,
-                             a.dtype, a.dgamma, nullptr, a.cache_Wx, lns, s));
+  HB_TRY(layer_norm_backward(a.dtype, (int)TN, 4 * H, a.gamma_Wx, a.act_Wx, a.act_Wx_norm, a.act_Wx,
+                             a.dtype, a.dgamma_Wx, nullptr, a.cache_Wx, lns, s));
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gw{a.dtype, a.dtype, C, 4 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.act_Wx,
               4LL * H, 1, a.dW, 4LL * H, 1};

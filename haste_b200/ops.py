@@ -187,7 +187,8 @@ def layer_norm_lstm_forward(training, zoneout_prob, x, h0, c0, kernel, recurrent
         tmp_Rh = x.new_empty(N, 4 * H)
         mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
         _C.call("haste_b200_layer_norm_lstm_forward", _dtype(x), int(training), T, N, C, H,
-                _p(kernel), _p(recurrent_kernel), _p(bias), _p(gamma), _p(gamma_h), _p(beta_h),
+                _p(kernel), _p(recurrent_kernel), _p(bias), _p(gamma[0]), _p(gamma[1]), _p(gamma_h),
+                _p(beta_h),
                 _p(x), _p(h), _p(c), _p(act_Wx), _p(act_Wx_norm), _p(cache_Wx), _p(act_Rh),
                 _p(cache_Rh), _p(act_c_norm), _p(cache_c), _p(tmp_Rh), zp, mp, _stream())
     return [h, c, act_Wx, act_Wx_norm, cache_Wx, act_Rh, cache_Rh, act_c_norm, cache_c]
@@ -211,9 +212,10 @@ def layer_norm_lstm_backward(x, kernel, recurrent_kernel, bias, gamma, gamma_h, 
         dh = h.new_zeros(N, H)
         dc = h.new_zeros(N, H)
         _C.call("haste_b200_layer_norm_lstm_backward", _dtype(h), int(transposed), T, N, C, H,
-                _p(kernel), _p(recurrent_kernel), _p(bias), _p(gamma), _p(gamma_h), _p(beta_h),
+                _p(kernel), _p(recurrent_kernel), _p(bias), _p(gamma[0]), _p(gamma[1]), _p(gamma_h),
+                _p(beta_h),
                 _p(x), _p(h), _p(c), _p(dh_new), _p(dc_new), _p(dx), _p(dW), _p(dR), _p(db),
-                _p(dgamma), _p(dgamma_h), _p(dbeta_h), _p(dh), _p(dc), _p(act_Wx),
+                _p(dgamma[0]), _p(dgamma[1]), _p(dgamma_h), _p(dbeta_h), _p(dh), _p(dc), _p(act_Wx),
                 _p(act_Wx_norm), _p(cache_Wx), _p(act_Rh), _p(cache_Rh), _p(act_c_norm),
                 _p(cache_c), _p(zoneout_mask), _stream())
     return [dx, dh, dc, dW, dR, db, dgamma, dgamma_h, dbeta_h]
@@ -236,7 +238,8 @@ def layer_norm_gru_forward(training, zoneout_prob, x, h0, kernel, recurrent_kern
         cache_Rh = x.new_empty(T, N, 2)
         mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
         _C.call("haste_b200_layer_norm_gru_forward", _dtype(x), int(training), T, N, C, H,
-                _p(kernel), _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(gamma), _p(x),
+                _p(kernel), _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(gamma[0]),
+                _p(gamma[1]), _p(x),
                 _p(h), _p(cache), _p(act_Wx), _p(cache_Wx), _p(tmp_Wx_norm), _p(act_Rh),
                 _p(cache_Rh), _p(tmp_Rh_norm), zp, mp, _stream())
     return [h, cache, act_Wx, cache_Wx, act_Rh, cache_Rh]
@@ -260,9 +263,10 @@ def layer_norm_gru_backward(x, kernel, recurrent_kernel, bias, recurrent_bias, g
         dq = h.new_empty(T, N, 3 * H)
         dgamma = torch.zeros_like(gamma)
         _C.call("haste_b200_layer_norm_gru_backward", _dtype(h), int(transposed), T, N, C, H,
-                _p(kernel), _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(gamma), _p(x),
+                _p(kernel), _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(gamma[0]),
+                _p(gamma[1]), _p(x),
                 _p(h), _p(cache), _p(dh_new), _p(dx), _p(dW), _p(dR), _p(dbx), _p(dbr),
-                _p(dgamma), _p(dh), _p(dp), _p(dq), _p(act_Wx), _p(cache_Wx), _p(act_Rh),
+                _p(dgamma[0]), _p(dgamma[1]), _p(dh), _p(dp), _p(dq), _p(act_Wx), _p(cache_Wx), _p(act_Rh),
                 _p(cache_Rh), _p(zoneout_mask), _stream())
     return [dx, dh, dW, dR, dbx, dbr, dgamma]
 

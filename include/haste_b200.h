@@ -144,45 +144,49 @@ int haste_b200_layer_norm_backward(int dtype, int rows, int width, const void* g
 /* ---- LayerNormLSTM ----------------------------------------------------- */
 /* Replaces layer_norm_lstm::ForwardPass<T>::Run  (lib/haste/layer_norm_lstm.h:75-92,
  * lib/layer_norm_lstm_forward_gpu.cu.cc:276-340).
- *   gamma [2,4H] (row 0 normalises x.W, row 1 normalises h.R)  gamma_h, beta_h [H]
+ *   gamma_Wx, gamma_Rh [4H] (the two rows of the module's [2,4H] gamma: the first
+ *   normalises x.W, the second h.R)  gamma_h, beta_h [H]
  *   act_Wx, act_Wx_norm, act_Rh [T,N,4H]  act_c_norm [T,N,H]
  *   cache_Wx, cache_Rh, cache_c [T,N,2]  tmp_Rh [N,4H] */
 int haste_b200_layer_norm_lstm_forward(
     int dtype, int training, int T, int N, int C, int H, const void* W, const void* R,
-    const void* b, const void* gamma, const void* gamma_h, const void* beta_h, const void* x,
+    const void* b, const void* gamma_Wx, const void* gamma_Rh, const void* gamma_h,
+    const void* beta_h, const void* x,
     void* h, void* c, void* act_Wx, void* act_Wx_norm, void* cache_Wx, void* act_Rh,
     void* cache_Rh, void* act_c_norm, void* cache_c, void* tmp_Rh, float zoneout_prob,
     const void* zoneout_mask, void* stream);
 
 /* Replaces layer_norm_lstm::BackwardPass<T>::Run  (lib/haste/layer_norm_lstm.h:160-183,
- * lib/layer_norm_lstm_backward_gpu.cu.cc:255-352).  dgamma [2,4H], dgamma_h,
+ * lib/layer_norm_lstm_backward_gpu.cu.cc:255-352).  dgamma_Wx, dgamma_Rh [4H], dgamma_h,
  * dbeta_h [H] accumulated; act_Wx, act_Wx_norm, act_Rh, act_c_norm are overwritten. */
 int haste_b200_layer_norm_lstm_backward(
     int dtype, int transposed_inputs, int T, int N, int C, int H, const void* W, const void* R,
-    const void* b, const void* gamma, const void* gamma_h, const void* beta_h, const void* x,
+    const void* b, const void* gamma_Wx, const void* gamma_Rh, const void* gamma_h,
+    const void* beta_h, const void* x,
     const void* h, const void* c, const void* dh_new, const void* dc_new, void* dx, void* dW,
-    void* dR, void* db, void* dgamma, void* dgamma_h, void* dbeta_h, void* dh, void* dc,
+    void* dR, void* db, void* dgamma_Wx, void* dgamma_Rh, void* dgamma_h, void* dbeta_h, void* dh,
+    void* dc,
     void* act_Wx, void* act_Wx_norm, const void* cache_Wx, void* act_Rh, const void* cache_Rh,
     void* act_c_norm, const void* cache_c, const void* zoneout_mask, void* stream);
 
 /* ---- LayerNormGRU ------------------------------------------------------ */
 /* Replaces layer_norm_gru::ForwardPass<T>::Run  (lib/haste/layer_norm_gru.h:72-88,
- * lib/layer_norm_gru_forward_gpu.cu.cc:243-305).  gamma [2,3H];
+ * lib/layer_norm_gru_forward_gpu.cu.cc:243-305).  gamma_Wx, gamma_Rh [3H];
  * act_Wx, tmp_Wx_norm [T,N,3H]; act_Rh [T,N,3H]; tmp_Rh_norm [N,3H]. */
 int haste_b200_layer_norm_gru_forward(
     int dtype, int training, int T, int N, int C, int H, const void* W, const void* R,
-    const void* bx, const void* br, const void* gamma, const void* x, void* h, void* v,
-    void* act_Wx, void* cache_Wx, void* tmp_Wx_norm, void* act_Rh, void* cache_Rh,
+    const void* bx, const void* br, const void* gamma_Wx, const void* gamma_Rh, const void* x,
+    void* h, void* v, void* act_Wx, void* cache_Wx, void* tmp_Wx_norm, void* act_Rh, void* cache_Rh,
     void* tmp_Rh_norm, float zoneout_prob, const void* zoneout_mask, void* stream);
 
 /* Replaces layer_norm_gru::BackwardPass<T>::Run  (lib/haste/layer_norm_gru.h:164-184,
- * lib/layer_norm_gru_backward_gpu.cu.cc:246-310).  dgamma [2,3H] accumulated;
+ * lib/layer_norm_gru_backward_gpu.cu.cc:246-310).  dgamma_Wx, dgamma_Rh [3H] accumulated;
  * act_Rh is overwritten (it receives the gradient of h.R). */
 int haste_b200_layer_norm_gru_backward(
     int dtype, int transposed_inputs, int T, int N, int C, int H, const void* W, const void* R,
-    const void* bx, const void* br, const void* gamma, const void* x, const void* h,
-    const void* v, const void* dh_new, void* dx, void* dW, void* dR, void* dbx, void* dbr,
-    void* dgamma, void* dh, void* dp, void* dq, const void* act_Wx, const void* cache_Wx,
+    const void* bx, const void* br, const void* gamma_Wx, const void* gamma_Rh, const void* x,
+    const void* h, const void* v, const void* dh_new, void* dx, void* dW, void* dR, void* dbx,
+    void* dbr, void* dgamma_Wx, void* dgamma_Rh, void* dh, void* dp, void* dq, const void* act_Wx, const void* cache_Wx,
     void* act_Rh, const void* cache_Rh, const void* zoneout_mask, void* stream);
 
 /* ---- LayerNormIndRNN --------------------------------------------------- */
