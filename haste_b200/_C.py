@@ -25,6 +25,7 @@ SIGNATURES = {
     "haste_b200_indrnn_backward": [_i] * 6 + [_p] * 14,
     "haste_b200_layer_norm_forward": [_i] * 3 + [_p] * 6,
     "haste_b200_layer_norm_backward": [_i] * 3 + [_p] * 8,
+    "haste_b200_layer_norm_backward_noalloc": [_i] * 3 + [_p] * 8,
     "haste_b200_layer_norm_lstm_forward": [_i] * 6 + [_p] * 18 + [_f, _p, _p],
     "haste_b200_layer_norm_lstm_backward": [_i] * 6 + [_p] * 31,
     "haste_b200_layer_norm_gru_forward": [_i] * 6 + [_p] * 15 + [_f, _p, _p],

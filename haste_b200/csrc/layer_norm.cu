@@ -6,6 +6,8 @@
 // lib/layer_norm_backward_gpu.cu.cc:44-91), but reductions use warp shuffles and
 // the parameter gradients are a deterministic two-stage column reduction instead
 // of per-element atomics.
+#include <mutex>
+
 #include "common.cuh"
 #include "util.cuh"
 
@@ -206,3 +208,68 @@ int layer_norm_backward(int dtype, int rows, int width, const void* gamma, const
 }
 
 }  // namespace hb
+
+// ---------------------------------------------------------------------------------------
+// LayerNorm backward for callers that must not allocate.
+//
+// haste_b200_layer_norm_backward takes its reduction scratch (the per-chunk partial sums of
+// dgamma/dbeta) from the library's grow-only pool, which calls cudaMalloc the first time and
+// whenever a larger problem arrives.  Some callers cannot afford that: a serving or audio
+// loop that has handed every byte of device memory to its own arena (cudaMalloc then fails
+// or fragments it), code between cudaStreamBeginCapture and EndCapture (allocation is
+// illegal there), and latency-critical loops in which cudaMalloc's implicit device-wide
+// synchronisation would stall every other stream.  For them this entry point keeps the
+// scratch in a fixed array inside the library image: 2 * 64 chunks * 4096 columns of fp32
+// = 2 MiB per GPU that loads the library, held until the process exits.
+// ---------------------------------------------------------------------------------------
+namespace hb {
+namespace {
+
+constexpr int NOALLOC_MAX_WIDTH = 4096;
+static __device__ __align__(256) float g_ln_noalloc_scratch[2 * PG_CHUNKS * NOALLOC_MAX_WIDTH];
+
+// g_ln_noalloc_scratch names a host-side handle here, not device memory: the address a
+// kernel can use is looked up once per device (with that device current) and remembered.
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {};
+std::mutex g_noalloc_mu;
+
+int noalloc_scratch(float** out) {
+  int dev = 0;
+  HB_CUDA_OK(cudaGetDevice(&dev));
+  HB_REQUIRE(dev >= 0 && dev < NOALLOC_MAX_DEVICES, "device ordinal out of range");
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  if (!g_noalloc_ptr[dev]) {
+    float* p = nullptr;
+    HB_CUDA_OK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_ln_noalloc_scratch));
+    g_noalloc_ptr[dev] = p;
+  }
+  *out = g_noalloc_ptr[dev];
+  return HASTE_B200_OK;
+}
+
+}  // namespace
+}  // namespace hb
+
+extern "C" int haste_b200_layer_norm_backward_noalloc(int dtype, int rows, int width,
+                                                      const void* gamma, const void* x,
+                                                      const void* dy, void* dx, void* dgamma,
+                                                      void* dbeta, const void* cache,
+                                                      void* stream) {
+  using namespace hb;
+  HB_REQUIRE(dtype == HASTE_B200_F32 || dtype == HASTE_B200_BF16, "dtype");
+  HB_REQUIRE(rows >= 0 && width > 0, "rows,width");
+  if (width > NOALLOC_MAX_WIDTH) {
+    set_last_error("layer_norm_backward_noalloc: width %d exceeds the built-in scratch (max %d "
+                   "columns); use haste_b200_layer_norm_backward", width, NOALLOC_MAX_WIDTH);
+    return HASTE_B200_ERR_UNSUPPORTED;
+  }
+  HB_REQUIRE(gamma && x && dy && dx && dgamma && cache, "null pointer");
+  if (rows == 0) return HASTE_B200_OK;
+  float* scratch = nullptr;
+  HB_TRY(noalloc_scratch(&scratch));
+  // Stage 1 writes every partial that stage 2 reads, so nothing in the array has to start
+  // at zero; what the previous call left behind is simply overwritten.
+  return layer_norm_backward(dtype, rows, width, gamma, x, dy, dx, dtype, dgamma, dbeta, cache,
+                             scratch, (cudaStream_t)stream);
+}

@@ -141,6 +141,24 @@ int haste_b200_layer_norm_backward(int dtype, int rows, int width, const void* g
                                    const void* x, const void* dy, void* dx, void* dgamma,
                                    void* dbeta, const void* cache, void* stream);
 
+/* No counterpart in the reference.  The same computation as
+ * haste_b200_layer_norm_backward, for callers that cannot let the library allocate: a
+ * process whose own arena already owns all device memory, code inside a stream-capture
+ * region, or a latency-critical loop that must not hit cudaMalloc's device-wide
+ * synchronisation.  The reduction scratch lives in a fixed 2 MiB array inside the library
+ * image (held by every GPU that loads the library until the process exits) instead of the
+ * grow-only pool, so this call never allocates or frees.
+ *   - width must be <= 4096; larger widths return HASTE_B200_ERR_UNSUPPORTED with a message.
+ *   - The first call on each device looks up the array's device address (the device of the
+ *     pointers must be current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array.  Nothing in it needs to start at zero (each
+ *     call overwrites what it later reads), but two calls that overlap on the GPU - different
+ *     streams, no ordering between them - race on it and give wrong gradients. */
+int haste_b200_layer_norm_backward_noalloc(int dtype, int rows, int width, const void* gamma,
+                                           const void* x, const void* dy, void* dx,
+                                           void* dgamma, void* dbeta, const void* cache,
+                                           void* stream);
+
 /* ---- LayerNormLSTM ----------------------------------------------------- */
 /* Replaces layer_norm_lstm::ForwardPass<T>::Run  (lib/haste/layer_norm_lstm.h:75-92,
  * lib/layer_norm_lstm_forward_gpu.cu.cc:276-340).
