@@ -106,9 +106,18 @@ int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s);
 // Forward: the input projection is already in a.v (LSTM) / a.tmp_Wx (GRU).
 // Backward: carries are fp32 [N,H] buffers, read at entry and written at exit.
 int lstm_forward_persistent(const LstmFwd& a, cudaStream_t s);
-int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry, cudaStream_t s);
+// Optional bf16 (hi, lo) planes of the gate gradients, written by the persistent backward
+// kernels in fp32 mode (p: dv / dp, p2: dq; lo plane `stride` elements after hi).
+struct GradPlanes {
+  __nv_bfloat16* p = nullptr;
+  __nv_bfloat16* p2 = nullptr;
+  long long stride = 0;
+};
+int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry,
+                             const GradPlanes& planes, cudaStream_t s);
 int gru_forward_persistent(const GruFwd& a, cudaStream_t s);
-int gru_backward_persistent(const GruBwd& a, float* dh_carry, cudaStream_t s);
+int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& planes,
+                            cudaStream_t s);
 
 // Per-step contraction (M = batch rows): always the CUDA-core kernel.
 inline int gemm_small(const GemmDesc& g, cudaStream_t s) { return gemm_simt(g, s); }

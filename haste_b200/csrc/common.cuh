@@ -107,6 +107,11 @@ struct GemmDesc {
   // (three products); the result is then accurate to fp32 rounding.  The LayerNorm cells
   // ask for it because normalisation amplifies the input projection's error.
   int precise = 0;
+  // fp32 storage only: operand already available as two bf16 planes (hi at *_pl, lo
+  // *_pl_stride elements later), same orientation as the operand, leading dimension *_pl_ld.
+  // The recurrence kernels write gate gradients in this form so that they are split once.
+  const void* a_pl = nullptr; long long a_pl_ld = 0, a_pl_stride = 0;
+  const void* b_pl = nullptr; long long b_pl_ld = 0, b_pl_stride = 0;
 };
 int gemm(const GemmDesc& g, cudaStream_t stream);
 int gemm_simt(const GemmDesc& g, cudaStream_t stream);

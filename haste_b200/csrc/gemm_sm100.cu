@@ -379,22 +379,56 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 
 // x -> `planes` bf16 planes (x = p0 + p1 (+ p2), each the bf16 rounding of what is left),
 // same orientation as the source, leading dimension ld_dst (a multiple of 8), planes
-// `plane_stride` elements apart.
+// `plane_stride` elements apart.  One thread converts 4 consecutive elements of a row:
+// a 16-byte load and one 8-byte store per plane when the source allows it.
+template <int PLANES>
 __global__ void split_planes_kernel(const float* __restrict__ src, long long ld_src, int rows,
                                     int cols, __nv_bfloat16* __restrict__ dst, long long ld_dst,
-                                    long long plane_stride, int planes) {
-  const long long total = (long long)rows * ld_dst;
+                                    long long plane_stride, int vec_ok) {
+  const int quads = (int)(ld_dst / 4);
+  const long long total = (long long)rows * quads;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
-    const long long r = i / ld_dst;
-    const int c = (int)(i - r * ld_dst);
-    float x = (c < cols) ? src[r * ld_src + c] : 0.0f;
-    for (int pl = 0; pl < planes; ++pl) {
-      const __nv_bfloat16 h = __float2bfloat16_rn(x);
-      dst[pl * plane_stride + i] = h;
-      x -= __bfloat162float(h);
+    const long long r = i / quads;
+    const int c = (int)(i - r * quads) * 4;
+    float x[4] = {0.f, 0.f, 0.f, 0.f};
+    const float* sp = src + r * ld_src + c;
+    if (vec_ok && c + 3 < cols) {
+      const float4 f = *reinterpret_cast<const float4*>(sp);
+      x[0] = f.x; x[1] = f.y; x[2] = f.z; x[3] = f.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + j < cols) x[j] = sp[j];
+    }
+    __nv_bfloat16* dp = dst + r * ld_dst + c;
+#pragma unroll
+    for (int pl = 0; pl < PLANES; ++pl) {
+      __nv_bfloat162 a = __floats2bfloat162_rn(x[0], x[1]);
+      __nv_bfloat162 b = __floats2bfloat162_rn(x[2], x[3]);
+      uint2 w;
+      w.x = *reinterpret_cast<uint32_t*>(&a);
+      w.y = *reinterpret_cast<uint32_t*>(&b);
+      *reinterpret_cast<uint2*>(dp + pl * plane_stride) = w;
+      x[0] -= __low2float(a); x[1] -= __high2float(a);
+      x[2] -= __low2float(b); x[3] -= __high2float(b);
     }
   }
+}
+
+int launch_split(const float* src, long long ld_src, int rows, int cols, __nv_bfloat16* dst,
+                 long long ld_dst, long long plane_stride, int planes, int blocks,
+                 cudaStream_t stream) {
+  const int vec_ok = ((ld_src & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
+  if (planes == 3)
+    split_planes_kernel<3><<<blocks, 256, 0, stream>>>(src, ld_src, rows, cols, dst, ld_dst,
+                                                       plane_stride, vec_ok);
+  else
+    split_planes_kernel<2><<<blocks, 256, 0, stream>>>(src, ld_src, rows, cols, dst, ld_dst,
+                                                       plane_stride, vec_ok);
+  HB_LAUNCH_OK();
+  count_launch(1);
+  return HASTE_B200_OK;
 }
 
 template <typename TC>
@@ -503,15 +537,20 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
   int kb_per_split = ceil_div(kb_total, splits);
   splits = ceil_div(kb_total, kb_per_split);
 
-  const long long a_ld = f32 ? ((a_cols + 7) & ~7LL) : a_ld_src;
-  const long long b_ld = f32 ? ((b_cols + 7) & ~7LL) : b_ld_src;
+  auto planes_usable = [&](const void* p, long long ld) {
+    return f32 && !g.precise && p && (ld % 8) == 0 && (reinterpret_cast<uintptr_t>(p) & 15) == 0;
+  };
+  const bool a_pre = planes_usable(g.a_pl, g.a_pl_ld) && (g.a_pl_stride % 8) == 0;
+  const bool b_pre = planes_usable(g.b_pl, g.b_pl_ld) && (g.b_pl_stride % 8) == 0;
+  const long long a_ld = a_pre ? g.a_pl_ld : (f32 ? ((a_cols + 7) & ~7LL) : a_ld_src);
+  const long long b_ld = b_pre ? g.b_pl_ld : (f32 ? ((b_cols + 7) & ~7LL) : b_ld_src);
   if (!f32) {
     if ((a_ld % 8) || (b_ld % 8) || ((uintptr_t)g.a & 15) || ((uintptr_t)g.b & 15))
       return unsupported("bf16 operand not 16-byte aligned for TMA");
   }
   const int planes = f32 ? (g.precise ? 3 : 2) : 1;
-  const size_t a_plane = f32 ? Arena::pad((size_t)a_rows * a_ld * 2) : 0;
-  const size_t b_plane = f32 ? Arena::pad((size_t)b_rows * b_ld * 2) : 0;
+  const size_t a_plane = (f32 && !a_pre) ? Arena::pad((size_t)a_rows * a_ld * 2) : 0;
+  const size_t b_plane = (f32 && !b_pre) ? Arena::pad((size_t)b_rows * b_ld * 2) : 0;
   const size_t part_bytes = splits > 1 ? Arena::pad((size_t)splits * M * N * 4) : 0;
   const size_t bytes = planes * (a_plane + b_plane) + part_bytes + 1024;
   Arena ws;
@@ -522,16 +561,17 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
     __nv_bfloat16* ap = ws.take<__nv_bfloat16>(planes * a_plane / 2);
     __nv_bfloat16* bp = ws.take<__nv_bfloat16>(planes * b_plane / 2);
     if (!ap || !bp) return unsupported("scratch arena");
-    const int blocks = 4 * sms;
-    split_planes_kernel<<<blocks, 256, 0, stream>>>((const float*)g.a, a_ld_src, (int)a_rows,
-                                                    (int)a_cols, ap, a_ld, a_plane / 2, planes);
-    HB_LAUNCH_OK();
-    split_planes_kernel<<<blocks, 256, 0, stream>>>((const float*)g.b, b_ld_src, (int)b_rows,
-                                                    (int)b_cols, bp, b_ld, b_plane / 2, planes);
-    HB_LAUNCH_OK();
-    count_launch(2);
+    const int blocks = 8 * sms;
+    if (!a_pre)
+      HB_TRY(launch_split((const float*)g.a, a_ld_src, (int)a_rows, (int)a_cols, ap, a_ld,
+                          a_plane / 2, planes, blocks, stream));
+    if (!b_pre)
+      HB_TRY(launch_split((const float*)g.b, b_ld_src, (int)b_rows, (int)b_cols, bp, b_ld,
+                          b_plane / 2, planes, blocks, stream));
     A.base = ap; A.plane_stride = a_plane / 2;
     B.base = bp; B.plane_stride = b_plane / 2;
+    if (a_pre) { A.base = g.a_pl; A.plane_stride = g.a_pl_stride; }
+    if (b_pre) { B.base = g.b_pl; B.plane_stride = g.b_pl_stride; }
   } else {
     A.base = g.a; A.plane_stride = 0;
     B.base = g.b; B.plane_stride = 0;

@@ -212,10 +212,22 @@ int gru_backward(const GruBwd& a, cudaStream_t s) {
   float* cs = ws.take<float>(csf);
   HB_REQUIRE(dh_carry && cs, "scratch arena");
   HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
+  GradPlanes planes;
+  bool have_planes = false;
+  if (a.dtype == HASTE_B200_F32 && ((3 * H) % 8) == 0) {
+    const size_t pe = Arena::pad((size_t)TN * 3 * H * 2) / 2;  // elements per plane
+    void* pw = workspace(s, 4 * pe * 2 + 256, /*slot=*/3);
+    if (pw) {
+      planes.p = static_cast<__nv_bfloat16*>(pw);
+      planes.p2 = planes.p + 2 * pe;
+      planes.stride = (long long)pe;
+    }
+  }
   int st_;
   {
     ProfScope p(PH_REC_BWD, s);
-    st_ = gru_backward_persistent(a, dh_carry, s);
+    st_ = gru_backward_persistent(a, dh_carry, planes, s);
+    have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
     if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
     st_ = (a.dtype == HASTE_B200_F32) ? gru_backward_stepwise<float>(a, dh_carry, s)
                                       : gru_backward_stepwise<__nv_bfloat16>(a, dh_carry, s);
@@ -228,17 +240,26 @@ int gru_backward(const GruBwd& a, cudaStream_t s) {
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 3 * H, a.dp, 3LL * H, 1, a.W, tr ? C : 1,
               tr ? 1 : 3LL * H, a.dx, C, 0};
+  if (have_planes) {  // dp was already split into bf16 planes by the recurrence kernel
+    gx.a_pl = planes.p; gx.a_pl_ld = 3LL * H; gx.a_pl_stride = planes.stride;
+  }
   {
     ProfScope p(PH_DGRAD, s);
     HB_TRY(gemm(gx, s));
   }
   GemmDesc gr{a.dtype, a.dtype, H, 3 * H, (int)TN, a.h, 1, H, a.dq, 3LL * H, 1, a.dR, 3LL * H, 1};
+  if (have_planes) {
+    gr.b_pl = planes.p2; gr.b_pl_ld = 3LL * H; gr.b_pl_stride = planes.stride;
+  }
   {
     ProfScope p(PH_WGRAD, s);
     HB_TRY(gemm(gr, s));
   }
   GemmDesc gw{a.dtype, a.dtype, C, 3 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.dp, 3LL * H, 1,
               a.dW, 3LL * H, 1};
+  if (have_planes) {
+    gw.b_pl = planes.p; gw.b_pl_ld = 3LL * H; gw.b_pl_stride = planes.stride;
+  }
   {
     ProfScope p(PH_WGRAD, s);
     HB_TRY(gemm(gw, s));

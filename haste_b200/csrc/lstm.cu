@@ -192,10 +192,22 @@ int lstm_backward(const LstmBwd& a, cudaStream_t s) {
   HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
   HB_TRY(to_float(a.dtype, a.dc, dc_carry, NH, s));
 
+  // fp32: room for the gate gradients as bf16 planes (written by the persistent kernel)
+  GradPlanes planes;
+  bool have_planes = false;
+  if (a.dtype == HASTE_B200_F32 && ((4 * H) % 8) == 0) {
+    const size_t pe = Arena::pad((size_t)TN * 4 * H * 2) / 2;  // elements per plane
+    void* pw = workspace(s, 2 * pe * 2 + 256, /*slot=*/3);
+    if (pw) {
+      planes.p = static_cast<__nv_bfloat16*>(pw);
+      planes.stride = (long long)pe;
+    }
+  }
   int st_;
   {
     ProfScope p(PH_REC_BWD, s);
-    st_ = lstm_backward_persistent(a, dh_carry, dc_carry, s);
+    st_ = lstm_backward_persistent(a, dh_carry, dc_carry, planes, s);
+    have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
     if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
     st_ = (a.dtype == HASTE_B200_F32) ? lstm_backward_stepwise<float>(a, dh_carry, dc_carry, s)
                                       : lstm_backward_stepwise<__nv_bfloat16>(a, dh_carry, dc_carry, s);
@@ -211,19 +223,24 @@ int lstm_backward(const LstmBwd& a, cudaStream_t s) {
   // dW[C,4H] += x^T . dv
   GemmDesc gw{a.dtype, a.dtype, C, 4 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.v, 4LL * H, 1,
               a.dW, 4LL * H, 1};
+  // dR[H,4H] += h[0:T]^T . dv
+  GemmDesc gr{a.dtype, a.dtype, H, 4 * H, (int)TN, a.h, 1, H, a.v, 4LL * H, 1, a.dR, 4LL * H, 1};
+  // dx[T*N,C] = dv . W^T
+  GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 4 * H, a.v, 4LL * H, 1, a.W, tr ? C : 1,
+              tr ? 1 : 4LL * H, a.dx, C, 0};
+  if (have_planes) {  // dv was already split into bf16 planes by the recurrence kernel
+    gw.b_pl = planes.p; gw.b_pl_ld = 4LL * H; gw.b_pl_stride = planes.stride;
+    gr.b_pl = planes.p; gr.b_pl_ld = 4LL * H; gr.b_pl_stride = planes.stride;
+    gx.a_pl = planes.p; gx.a_pl_ld = 4LL * H; gx.a_pl_stride = planes.stride;
+  }
   {
     ProfScope p(PH_WGRAD, s);
     HB_TRY(gemm(gw, s));
   }
-  // dR[H,4H] += h[0:T]^T . dv
-  GemmDesc gr{a.dtype, a.dtype, H, 4 * H, (int)TN, a.h, 1, H, a.v, 4LL * H, 1, a.dR, 4LL * H, 1};
   {
     ProfScope p(PH_WGRAD, s);
     HB_TRY(gemm(gr, s));
   }
-  // dx[T*N,C] = dv . W^T
-  GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 4 * H, a.v, 4LL * H, 1, a.W, tr ? C : 1,
-              tr ? 1 : 4LL * H, a.dx, C, 0};
   {
     ProfScope p(PH_DGRAD, s);
     HB_TRY(gemm(gx, s));

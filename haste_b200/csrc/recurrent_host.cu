@@ -102,7 +102,8 @@ int gru_forward_persistent(const GruFwd& a, cudaStream_t s) {
 // The persistent backward kernels leave the recurrent contribution of the very last
 // processed step (t = 0) out of dh (nothing inside the kernel consumes it); it is added
 // here with one small contraction: dh += dG_0 . R^T.
-int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry, cudaStream_t s) {
+int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry,
+                             const GradPlanes& planes, cudaStream_t s) {
   Geometry g;
   if (!supported(a.dtype, a.N, a.H, &g)) return HASTE_B200_ERR_UNSUPPORTED;
   Sync sync;
@@ -110,7 +111,7 @@ int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry,
   HB_TRY(make_scratch((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U, &sync, &exch, s));
   BwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R, a.h,
               a.c, a.v, a.dh_new, a.dc_new, nullptr, nullptr, a.zoneout_mask, dh_carry, dc_carry,
-              exch, sync, debug_skip()};
+              exch, sync, debug_skip(), planes.p, planes.p2, planes.stride};
   int st_ = a.dtype == HASTE_B200_F32 ? run_bwd_lstm_f32(p, g, s) : run_bwd_lstm_bf16(p, g, s);
   if (st_ != HASTE_B200_OK) return st_;
   const int H = a.H;
@@ -119,7 +120,8 @@ int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry,
   return gemm_small(gd, s);
 }
 
-int gru_backward_persistent(const GruBwd& a, float* dh_carry, cudaStream_t s) {
+int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& planes,
+                            cudaStream_t s) {
   Geometry g;
   if (!supported(a.dtype, a.N, a.H, &g)) return HASTE_B200_ERR_UNSUPPORTED;
   Sync sync;
@@ -127,7 +129,7 @@ int gru_backward_persistent(const GruBwd& a, float* dh_carry, cudaStream_t s) {
   HB_TRY(make_scratch((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U, &sync, &exch, s));
   BwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R, a.h,
               nullptr, const_cast<void*>(a.v), a.dh_new, nullptr, a.dp, a.dq, a.zoneout_mask,
-              dh_carry, nullptr, exch, sync, debug_skip()};
+              dh_carry, nullptr, exch, sync, debug_skip(), planes.p, planes.p2, planes.stride};
   int st_ = a.dtype == HASTE_B200_F32 ? run_bwd_gru_f32(p, g, s) : run_bwd_gru_bf16(p, g, s);
   if (st_ != HASTE_B200_OK) return st_;
   const int H = a.H;

@@ -87,6 +87,12 @@ struct BwdParams {
   uint32_t* exch;       // [2][nBS][nHS(dest)][nHS(src)][16*MT rows][U] tagged partial dh
   Sync sync;
   int dbg;
+  // fp32 storage, optional: the gate gradients also as bf16 (hi, lo) planes, hi at gpl and lo
+  // gpl_stride elements later, laid out like v / dp (gpl) and dq (gpl2), so that the
+  // contractions that follow do not have to split them again.
+  __nv_bfloat16* gpl;
+  __nv_bfloat16* gpl2;
+  long long gpl_stride;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -655,6 +661,16 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
             T* vt = vbuf + ((long long)t * N + n) * 4 * H + u0 + ul;
 #pragma unroll
             for (int g4 = 0; g4 < 4; ++g4) st(vt + g4 * H, dgate[g4 % G]);
+            if (SPLIT == 2 && p.gpl) {
+              __nv_bfloat16* ph = p.gpl + ((long long)t * N + n) * 4 * H + u0 + ul;
+#pragma unroll
+              for (int g4 = 0; g4 < 4; ++g4) {
+                float hi, lo;
+                split_bf16(dgate[g4 % G], hi, lo);
+                ph[g4 * H] = __float2bfloat16_rn(hi);
+                ph[p.gpl_stride + g4 * H] = __float2bfloat16_rn(lo);
+              }
+            }
           }
         } else {
           const float z = gv[mt][0], r = gv[mt][1], g = gv[mt][2], qg = gv[mt][3];
@@ -671,6 +687,19 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
             const long long w0 = ((long long)t * N + n) * 3 * H + u0 + ul;
             st(dpb + w0, dp_z); st(dpb + w0 + H, dp_r); st(dpb + w0 + 2 * H, dp_g);
             st(dqb + w0, dp_z); st(dqb + w0 + H, dp_r); st(dqb + w0 + 2 * H, dgate[2]);
+            if (SPLIT == 2 && p.gpl) {
+              const float pv[3] = {dp_z, dp_r, dp_g};
+#pragma unroll
+              for (int g3 = 0; g3 < 3; ++g3) {
+                float hi, lo;
+                split_bf16(pv[g3], hi, lo);
+                p.gpl[w0 + g3 * H] = __float2bfloat16_rn(hi);
+                p.gpl[p.gpl_stride + w0 + g3 * H] = __float2bfloat16_rn(lo);
+                split_bf16(g3 == 2 ? dgate[2] : pv[g3], hi, lo);
+                p.gpl2[w0 + g3 * H] = __float2bfloat16_rn(hi);
+                p.gpl2[p.gpl_stride + w0 + g3 * H] = __float2bfloat16_rn(lo);
+              }
+            }
           }
         }
         // A operand row (mt*16+nl), columns ul*G .. ul*G+G-1
