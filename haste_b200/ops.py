@@ -96,6 +96,66 @@ def lstm_backward(x, kernel, recurrent_kernel, bias, zoneout_mask, h, c, cache, 
     return [dx, dh, dc, dW, dR, db]
 
 
+_copy_streams = {}
+
+
+def lstm_forward_from_host(training, zoneout_prob, x_host, h0, c0, kernel, recurrent_kernel, bias,
+                           zoneout_mask, chunks=4):
+    """`lstm_forward` for an input that still lives in pinned HOST memory.
+
+    The sequence is cut into `chunks` pieces along time; while the GPU runs the projection and
+    the recurrence of one piece, the next piece is copied host->device on a second stream, so
+    only the first copy is exposed.  Every piece is a C-ABI call on slices of the same
+    `[T+1,N,H]` / `[T,N,4H]` buffers (the state slot a piece ends on is the initial state of
+    the next), so the result equals one call on the whole sequence up to the rounding of the
+    input projection (a short piece may take the CUDA-core contraction path).
+    Returns [h, c, cache, x_device].
+    """
+    _check(h0, c0, kernel, recurrent_kernel, bias, zoneout_mask)
+    if x_host.is_cuda or not x_host.is_pinned():
+        raise RuntimeError("haste_b200: x_host must be a pinned CPU tensor")
+    T, N, C = x_host.shape
+    H = recurrent_kernel.shape[0]
+    dev = h0.device
+    with torch.cuda.device(dev):
+        main = torch.cuda.current_stream()
+        side = _copy_streams.get(dev.index)
+        if side is None:
+            side = _copy_streams[dev.index] = torch.cuda.Stream(device=dev)
+        x = torch.empty(T, N, C, device=dev, dtype=h0.dtype)
+        h = h0.new_empty(T + 1, N, H)
+        c = h0.new_empty(T + 1, N, H)
+        h[0] = h0
+        c[0] = c0
+        cache = h0.new_empty(T, N, 4 * H)
+        tmp_Rh = h0.new_empty(N, 4 * H)
+        mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
+        es = x.element_size()
+        bounds = [round(i * T / chunks) for i in range(chunks + 1)]
+        side.wait_stream(main)
+        x.record_stream(side)
+        events = []
+        with torch.cuda.stream(side):
+            for k in range(chunks):
+                t0, t1 = bounds[k], bounds[k + 1]
+                if t1 > t0:
+                    x[t0:t1].copy_(x_host[t0:t1], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(side)
+                events.append(ev)
+        for k in range(chunks):
+            t0, t1 = bounds[k], bounds[k + 1]
+            if t1 == t0:
+                continue
+            main.wait_event(events[k])
+            _C.call("haste_b200_lstm_forward", _dtype(h0), int(training), t1 - t0, N, C, H,
+                    _p(kernel), _p(recurrent_kernel), _p(bias), x.data_ptr() + t0 * N * C * es,
+                    h.data_ptr() + t0 * N * H * es, c.data_ptr() + t0 * N * H * es,
+                    cache.data_ptr() + t0 * N * 4 * H * es, _p(tmp_Rh), zp,
+                    (mp + t0 * N * H * es) if mp else None, main.cuda_stream)
+    return [h, c, cache, x]
+
+
 # ---------------------------------------------------------------- GRU
 def gru_forward(training, zoneout_prob, x, h0, kernel, recurrent_kernel, bias, recurrent_bias,
                 zoneout_mask):

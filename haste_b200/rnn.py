@@ -195,8 +195,8 @@ class BaseRNN(nn.Module):
         if self.return_state_sequence:
             return self._permute(state[1:]).unsqueeze(0)
         if lengths is not None:
-            cols = range(state.size(1))
-            return state[[lengths, cols]].unsqueeze(0)
+            cols = torch.arange(state.size(1), device=state.device)
+            return state[torch.as_tensor(lengths, device=state.device), cols].unsqueeze(0)
         return state[-1].unsqueeze(0)
 
     def _get_zoneout_mask(self, input, zoneout_mask=None):

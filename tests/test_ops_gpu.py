@@ -198,3 +198,21 @@ def test_bidirectional_stack_matches_oracle_composition():
             for k, v in layer.named_parameters():
                 assert_close(v.grad, leaves[i][k].grad, TOL_F32, f"stack d{k}")
             i += 1
+
+
+def test_streamed_host_input_equals_single_call():
+    from haste_b200 import ops
+    T, N, C, H = 37, 16, 32, 64
+    d = oracle.make_inputs("lstm", T, N, C, H, seed=8, zoneout=0.2)
+    cu = lambda t: t.float().cuda().contiguous()
+    args = [cu(d[k]) for k in ("h0", "c0", "W", "R", "b", "mask")]
+    want = ops.lstm_forward(True, 0.2, cu(d["x"]), *args)
+    x_host = d["x"].float().pin_memory()
+    for chunks in (1, 3, 5):
+        got = ops.lstm_forward_from_host(True, 0.2, x_host, *args, chunks=chunks)
+        torch.cuda.synchronize()
+        # pieces may take a different contraction path than the whole (by size), so the
+        # match is to rounding, not bit-for-bit
+        for a, b in zip(got[:3], want):
+            assert_close(a, b, 2e-5, "streamed vs single call")
+        assert torch.equal(got[3], cu(d["x"]))
