@@ -119,8 +119,12 @@ int gru_forward_persistent(const GruFwd& a, cudaStream_t s);
 int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& planes,
                             cudaStream_t s);
 
-// Per-step contraction (M = batch rows): always the CUDA-core kernel.
-inline int gemm_small(const GemmDesc& g, cudaStream_t s) { return gemm_simt(g, s); }
+// Per-step contraction (M = batch rows).  Small batches are launch-bound and stay on the
+// CUDA-core kernel; from 128 rows up the tensor-core kernel pays for its set-up.
+inline int gemm_small(const GemmDesc& g, cudaStream_t s) {
+  if (g.M >= 128 && (long long)g.M * g.N * g.K >= (1LL << 26)) return gemm(g, s);
+  return gemm_simt(g, s);
+}
 
 // Process-wide knobs (set through the C ABI).
 int recurrence_path();
