@@ -118,6 +118,12 @@ int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry,
 int gru_forward_persistent(const GruFwd& a, cudaStream_t s);
 int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& planes,
                             cudaStream_t s);
+// LayerNormLSTM: forward expects LN(x.W) in a.act_Wx_norm; backward adds the LayerNorm
+// parameter gradients of the recurrence into the fp32 accumulators acc = [dgamma_Rh 4H |
+// dgamma_h H | dbeta_h H]; planes.p / p2 receive the gate gradient and d(h.R).
+int layer_norm_lstm_forward_persistent(const LnLstmFwd& a, cudaStream_t s);
+int layer_norm_lstm_backward_persistent(const LnLstmBwd& a, float* dh_carry, float* dc_carry,
+                                        float* acc, const GradPlanes& planes, cudaStream_t s);
 
 // Per-step contraction (M = batch rows).  Small batches are launch-bound and stay on the
 // CUDA-core kernel; from 128 rows up the tensor-core kernel pays for its set-up.

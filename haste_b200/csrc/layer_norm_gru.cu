@@ -37,6 +37,7 @@ int forward_steps(const LnGruFwd& a, cudaStream_t s) {
   for (int t = 0; t < a.T; ++t) {
     T* Rh_t = act_Rh + t * NH * 3;
     GemmDesc g{a.dtype, a.dtype, N, 3 * H, H, h + t * NH, H, 1, a.R, 3LL * H, 1, Rh_t, 3LL * H, 0};
+    g.precise = 1;  // LayerNorm follows: keep the product at fp32 accuracy
     HB_TRY(gemm_small(g, s));
     HB_TRY(layer_norm_forward(a.dtype, N, 3 * H, gamma1, nullptr, Rh_t, a.tmp_Rh_norm,
                               (char*)a.cache_Rh + (size_t)t * N * 2 * es, s));
@@ -73,6 +74,7 @@ int backward_steps(const LnGruBwd& a, float* dh_carry, void* dgamma1, float* lns
                                (const char*)a.cache_Rh + (size_t)t * N * 2 * es, lns, s));
     GemmDesc g{a.dtype, HASTE_B200_F32, N, H, 3 * H, Rh_t, 3LL * H, 1, a.R, r_rs, r_cs, dh_carry,
                H, 1};
+    g.precise = 1;  // LayerNorm follows: keep the product at fp32 accuracy
     HB_TRY(gemm_small(g, s));
   }
   return HASTE_B200_OK;

@@ -127,11 +127,13 @@ int forward_steps(const LnLstmFwd& a, float* rh_f32, float* c_f32, cudaStream_t 
       // bf16 storage: keep h.R and c' in fp32 between the kernels of one step
       GemmDesc g{a.dtype, HASTE_B200_F32, N, 4 * H, H, h + t * NH, H, 1, a.R, 4LL * H, 1, rh_f32,
                  4LL * H, 0};
+      g.precise = 1;  // LayerNorm follows: keep the product at fp32 accuracy
       HB_TRY(gemm_small(g, s));
       HB_TRY(layer_norm_forward_from(HASTE_B200_F32, a.dtype, N, 4 * H, gamma1, nullptr, rh_f32,
                                      a.tmp_Rh, (char*)a.cache_Rh + (size_t)t * N * 2 * es, Rh_t, s));
     } else {
       GemmDesc g{a.dtype, a.dtype, N, 4 * H, H, h + t * NH, H, 1, a.R, 4LL * H, 1, Rh_t, 4LL * H, 0};
+      g.precise = 1;  // LayerNorm follows: keep the product at fp32 accuracy
       HB_TRY(gemm_small(g, s));
       HB_TRY(layer_norm_forward(a.dtype, N, 4 * H, gamma1, nullptr, Rh_t, a.tmp_Rh,
                                 (char*)a.cache_Rh + (size_t)t * N * 2 * es, s));
@@ -206,6 +208,7 @@ int backward_steps(const LnLstmBwd& a, float* dh_carry, float* dc_carry, void* d
                                nullptr, (const char*)a.cache_Rh + (size_t)t * N * 2 * es, lns, s));
     GemmDesc g{a.dtype, HASTE_B200_F32, N, H, 4 * H, Rh_t, 4LL * H, 1, a.R, r_rs, r_cs, dh_carry,
                H, 1};
+    g.precise = 1;  // LayerNorm follows: keep the product at fp32 accuracy
     HB_TRY(gemm_small(g, s));
   }
   return HASTE_B200_OK;
@@ -229,6 +232,10 @@ int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
   HB_TRY(gemm(g, s));
   HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma_Wx, nullptr, a.act_Wx, a.act_Wx_norm,
                             a.cache_Wx, s));
+  {
+    const int st_ = layer_norm_lstm_forward_persistent(a, s);
+    if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
+  }
   if (a.dtype == HASTE_B200_F32) return forward_steps<float>(a, nullptr, nullptr, s);
   const size_t NH = (size_t)a.N * a.H;
   Arena ws;
@@ -268,22 +275,27 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
   HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
   HB_TRY(to_float(a.dtype, a.dc, dc_carry, NH, s));
 
-  const size_t es = dtype_size(a.dtype);
-  void* dgamma1 = a.dgamma_Rh;
-  void* dgamma_h = a.dgamma_h;
-  void* dbeta_h = a.dbeta_h;
-  if (bf) {
-    HB_CUDA_OK(cudaMemsetAsync(acc, 0, 6 * H * sizeof(float), s));
-    dgamma1 = acc;
-    dgamma_h = acc + 4 * H;
-    dbeta_h = acc + 5 * H;
+  // Persistent recurrence first; it adds its LayerNorm parameter gradients into `acc`.
+  HB_CUDA_OK(cudaMemsetAsync(acc, 0, 6 * H * sizeof(float), s));
+  int st_ = layer_norm_lstm_backward_persistent(a, dh_carry, dc_carry, acc, GradPlanes{}, s);
+  bool use_acc = st_ == HASTE_B200_OK;
+  if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
+    void* dgamma1 = a.dgamma_Rh;
+    void* dgamma_h = a.dgamma_h;
+    void* dbeta_h = a.dbeta_h;
+    if (bf) {
+      dgamma1 = acc;
+      dgamma_h = acc + 4 * H;
+      dbeta_h = acc + 5 * H;
+      use_acc = true;
+    }
+    st_ = bf ? backward_steps<__nv_bfloat16>(a, dh_carry, dc_carry, dgamma1, dgamma_h, dbeta_h,
+                                             HASTE_B200_F32, lns, s)
+             : backward_steps<float>(a, dh_carry, dc_carry, dgamma1, dgamma_h, dbeta_h,
+                                     HASTE_B200_F32, lns, s);
   }
-  int st_ = bf ? backward_steps<__nv_bfloat16>(a, dh_carry, dc_carry, dgamma1, dgamma_h, dbeta_h,
-                                               HASTE_B200_F32, lns, s)
-               : backward_steps<float>(a, dh_carry, dc_carry, dgamma1, dgamma_h, dbeta_h,
-                                       HASTE_B200_F32, lns, s);
   HB_TRY(st_);
-  if (bf) {
+  if (use_acc) {
     HB_TRY(add_float_into(a.dtype, acc, a.dgamma_Rh, 4 * H, s));
     HB_TRY(add_float_into(a.dtype, acc + 4 * H, a.dgamma_h, H, s));
     HB_TRY(add_float_into(a.dtype, acc + 5 * H, a.dbeta_h, H, s));

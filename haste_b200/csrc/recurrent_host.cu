@@ -2,7 +2,7 @@
 // exchange-buffer scratch, and the four entry points the cell drivers call.
 #include <cstdlib>
 
-#include "recurrent_kernels.cuh"
+#include "recurrent_ln_kernels.cuh"
 
 namespace hb {
 namespace rec {
@@ -135,6 +135,62 @@ int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& 
   const int H = a.H;
   GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 3 * H, a.dq, 3LL * H, 1, a.R,
               a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 3LL * H, dh_carry, H, 1};
+  return gemm_small(gd, s);
+}
+
+// ---- LayerNormLSTM (recurrent_ln_kernels.cuh) ------------------------------------------
+// Forward: LN(x.W) is already in a.act_Wx_norm.  Four source slices per thread in the
+// statistic exchange limit the kernels to 64 hidden slices, which `supported` guarantees.
+int layer_norm_lstm_forward_persistent(const LnLstmFwd& a, cudaStream_t s) {
+  Geometry g;
+  if (!supported(a.dtype, a.N, a.H, &g) || g.nHS > 64) return HASTE_B200_ERR_UNSUPPORTED;
+  const int Hx = (a.H + 3) & ~3;
+  const size_t xwords = (size_t)2 * a.N * Hx;
+  const size_t swords = (size_t)2 * 2 * g.nBS * g.MT * 16 * g.nHS * 2;
+  Sync sync;
+  uint32_t* words = nullptr;
+  HB_TRY(make_scratch(xwords + swords + 64, &sync, &words, s));
+  const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
+  LnFwdParams p{a.T, a.N, a.H, Hx, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.b,
+                a.gamma_Rh, a.gamma_h, a.beta_h, a.act_Wx_norm, a.act_Rh, a.cache_Rh,
+                a.act_c_norm, a.cache_c, a.h, a.c, a.zoneout_mask, words,
+                words + ((xwords + 63) & ~size_t(63)), sync};
+  return a.dtype == HASTE_B200_F32 ? run_ln_fwd_f32(p, g, s) : run_ln_fwd_bf16(p, g, s);
+}
+
+// Backward.  `acc` holds fp32 accumulators [dgamma_Rh 4H | dgamma_h H | dbeta_h H] that the
+// per-row-group partial sums of the kernel are added into (fixed order).  As for the plain
+// LSTM, the recurrent contribution of step 0 to dh is added here by one small contraction.
+int layer_norm_lstm_backward_persistent(const LnLstmBwd& a, float* dh_carry, float* dc_carry,
+                                        float* acc, const GradPlanes& planes, cudaStream_t s) {
+  Geometry g;
+  if (!supported(a.dtype, a.N, a.H, &g) || g.nHS > 64) return HASTE_B200_ERR_UNSUPPORTED;
+  const int H = a.H;
+  const size_t ewords = ((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U + 63) & ~size_t(63);
+  const size_t swords = ((size_t)2 * 2 * g.nBS * g.MT * 16 * g.nHS * 2 + 63) & ~size_t(63);
+  const int prow = g.nBS * 16;
+  const size_t pwords = (size_t)prow * 6 * H;
+  const size_t cwords = colsum_scratch_floats(prow, 4 * H);
+  Sync sync;
+  uint32_t* words = nullptr;
+  HB_TRY(make_scratch(ewords + swords + pwords + cwords + 64, &sync, &words, s));
+  float* part = reinterpret_cast<float*>(words + ewords + swords);
+  float* cs = part + pwords;
+  LnBwdParams p{a.T, a.N, H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R,
+                a.gamma_Rh, a.gamma_h, a.c, a.act_Wx_norm, a.act_Rh, a.cache_Rh, a.act_c_norm,
+                a.cache_c, a.dh_new, a.dc_new, a.zoneout_mask, dh_carry, dc_carry, part,
+                part + (size_t)prow * 4 * H, part + (size_t)prow * 5 * H, words, words + ewords,
+                sync, planes.p, planes.p2, planes.stride};
+  int st_ = a.dtype == HASTE_B200_F32 ? run_ln_bwd_f32(p, g, s) : run_ln_bwd_bf16(p, g, s);
+  if (st_ != HASTE_B200_OK) return st_;
+  HB_TRY(colsum(HASTE_B200_F32, part, 4LL * H, prow, 4 * H, HASTE_B200_F32, acc, 1, cs, s));
+  HB_TRY(colsum(HASTE_B200_F32, part + (size_t)prow * 4 * H, H, prow, H, HASTE_B200_F32,
+                acc + 4 * H, 1, cs, s));
+  HB_TRY(colsum(HASTE_B200_F32, part + (size_t)prow * 5 * H, H, prow, H, HASTE_B200_F32,
+                acc + 5 * H, 1, cs, s));
+  GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 4 * H, a.act_Rh, 4LL * H, 1, a.R,
+              a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 4LL * H, dh_carry, H, 1};
+  gd.precise = 1;
   return gemm_small(gd, s);
 }
 

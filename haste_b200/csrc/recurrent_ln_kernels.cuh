@@ -1,0 +1,978 @@
+// Persistent LayerNormLSTM recurrence kernels (forward and backward), sm_100a.
+//
+// Same skeleton as recurrent_kernels.cuh - cooperative grid of (hidden slices) x (batch
+// slices), the CTA's slice of R resident in registers as mma.sync fragments, self-validating
+// tagged words for every inter-CTA hand-off, bounded waits - plus what LayerNorm adds: a
+// normalisation runs over a whole row (all 4H gate columns of h.R, all H units of c'), while a
+// CTA only holds 64 / 16 of those columns.  Each row statistic is therefore built in two
+// levels: the 16 threads that own a row inside a CTA reduce with shuffles, the CTAs of the
+// batch slice then exchange one (a, b) pair per row through a small tagged buffer and every
+// CTA combines the nHS pairs in a fixed order.  Forward: (mean, M2) pairs combined with
+// Chan's formula (no E[x^2]-mean^2 cancellation); backward: the two row sums of the
+// LayerNorm gradient.  Per step that is three exchange rounds forward (h.R statistics, c'
+// statistics, h) and three backward (partial dh, LN(c') sums, LN(h.R) sums).
+//
+// All LayerNorm inputs stay in fp32 registers between the stages of a step (with bf16 storage
+// too: a value is rounded only when it is saved for the backward pass).
+//
+// Math and saved tensors follow the reference (lib/layer_norm_lstm_forward_gpu.cu.cc:26-109,
+// 191-273; lib/layer_norm_lstm_backward_gpu.cu.cc:27-118,207-252; LayerNorm gradient
+// lib/layer_norm_backward_gpu.cu.cc:44-91).  One deliberate difference: the reference's
+// LayerNorm gradient carries a term proportional to sum(x - mean), which is zero in exact
+// arithmetic; it is left out here.
+#pragma once
+
+#include "recurrent_kernels.cuh"
+
+namespace hb {
+namespace rec {
+
+struct LnFwdParams {
+  int T, N, H, Hx, nHS, MT, training, has_zoneout;
+  float zoneout_prob;
+  const void* R;        // [H, 4H]
+  const void* b;        // [4H]
+  const void* gamma_Rh; // [4H]
+  const void* gamma_h;  // [H]
+  const void* beta_h;   // [H]
+  void* v;              // act_Wx_norm [T,N,4H]: LN1(x.W) in, gate activations out
+  void* act_Rh;         // [T,N,4H] pre-norm h.R (saved)
+  void* cache_Rh;       // [T,N,2]
+  void* act_c_norm;     // [T,N,H]
+  void* cache_c;        // [T,N,2]
+  void* h;              // [T+1,N,H]
+  void* c;              // [T+1,N,H] un-normalised cell state
+  const void* mask;
+  uint32_t* xbuf;       // [2][N][Hx] tagged h words
+  uint32_t* sbuf;       // [2 stats][2 parity][nBS][rows][nHS][2] tagged statistic pairs
+  Sync sync;
+};
+
+struct LnBwdParams {
+  int T, N, H, nHS, MT, has_zoneout, r_transposed;
+  const void* R;
+  const void* gamma_Rh;
+  const void* gamma_h;
+  const void* c;          // [T+1,N,H]
+  void* v;                // act_Wx_norm: gate activations in, gate gradients out
+  void* act_Rh;           // pre-norm h.R in, d(h.R) out
+  const void* cache_Rh;
+  void* act_c_norm;       // LN(c') in (left untouched)
+  const void* cache_c;
+  const void* dh_new;
+  const void* dc_new;
+  const void* mask;
+  float* dh_carry;        // [N,H] in/out
+  float* dc_carry;        // [N,H] in/out
+  float* dgRh_part;       // [N,4H] per-row partial sums of dgamma_Rh (reduced by the host)
+  float* dgh_part;        // [N,H]  per-row partial sums of dgamma_h
+  float* dbh_part;        // [N,H]  per-row partial sums of dbeta_h
+  uint32_t* exch;         // tagged partial dh, as in rec_bwd_kernel
+  uint32_t* sbuf;         // [2 stats][2 parity][nBS][rows][nHS][2]
+  Sync sync;
+  __nv_bfloat16* gpl;     // optional bf16 planes of d(x.W-side gate gradient) (dv)
+  __nv_bfloat16* gpl2;    // optional bf16 planes of d(h.R)
+  long long gpl_stride;
+};
+
+// Statistics and partial gradients travel as fp32 words whose lowest mantissa bit is replaced
+// by the tag (22 explicit mantissa bits survive): LayerNorm amplifies a relative error of the
+// exchanged value roughly tenfold, so the 17 bits of the (hi, lo) bf16 pair are not enough
+// here.  Same protocol otherwise: buffers start zeroed and the expected tag alternates.
+__device__ __forceinline__ uint32_t fword_encode(float x, uint32_t tag) {
+  return (__float_as_uint(x) & ~1u) | tag;
+}
+__device__ __forceinline__ float fword_value(uint32_t w) { return __uint_as_float(w & ~1u); }
+__device__ __forceinline__ bool fword_ready(uint32_t w, uint32_t tag) { return (w & 1u) == tag; }
+
+// h words: tagged fp32 with fp32 storage, the (hi, lo) bf16 pair with bf16 storage.
+template <int SPLIT> __device__ __forceinline__ uint32_t hword_encode(float x, uint32_t tag) {
+  return SPLIT == 2 ? fword_encode(x, tag) : xword_encode(x, tag);
+}
+template <int SPLIT> __device__ __forceinline__ bool hword_ready(uint32_t w, uint32_t tag) {
+  return SPLIT == 2 ? fword_ready(w, tag) : xword_ready(w, tag);
+}
+// x = p[0] + p[1] + p[2], each the bf16 rounding of what the previous ones left.
+__device__ __forceinline__ void split3_bf16(float x, float (&p)[3]) {
+  p[0] = __bfloat162float(__float2bfloat16_rn(x));
+  const float r1 = x - p[0];
+  p[1] = __bfloat162float(__float2bfloat16_rn(r1));
+  p[2] = __bfloat162float(__float2bfloat16_rn(r1 - p[1]));
+}
+
+// Sum over the 16 consecutive lanes that own one batch row.
+__device__ __forceinline__ float row16_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  v += __shfl_xor_sync(0xffffffffu, v, 4);
+  v += __shfl_xor_sync(0xffffffffu, v, 8);
+  return v;
+}
+
+// One exchange round of per-row pairs among the CTAs of a batch slice, in two halves.
+//   area : this round's buffer, laid out [rows][nHS][2] tagged words
+// stat_publish: lane ul == 0 of the row's 16-thread group stores this CTA's pair (a, b).
+__device__ __forceinline__ void stat_publish(uint32_t* area, int row, int hs, int nHS,
+                                             uint32_t tag, float a, float b) {
+  __stcg(reinterpret_cast<uint2*>(area + ((size_t)row * nHS + hs) * 2),
+         make_uint2(fword_encode(a, tag), fword_encode(b, tag)));
+}
+// stat_collect: thread ul of the group fetches the pairs of sources ul, ul+16, ul+32, ul+48
+// (zero where there is no such source, or when `active` is false); the caller combines them
+// and finishes with row16_sum.  Returns false if the wait was abandoned.
+__device__ __forceinline__ bool stat_collect(const uint32_t* area, int row, int nHS, int ul,
+                                             uint32_t tag, bool active, float (&out_a)[4],
+                                             float (&out_b)[4], const Sync& sync, int* s_abort,
+                                             int code) {
+  const uint32_t* rowp = area + (size_t)row * nHS * 2;
+  uint2 w[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) w[k] = make_uint2(tag, tag);
+  bool alive = true;
+  if (active) {
+    const long long t0 = clock64();
+    unsigned int spins = 0;
+    for (;;) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const int s = ul + 16 * k;
+        if (s < nHS) {
+          const uint32_t* q = rowp + s * 2;
+          asm volatile("ld.relaxed.gpu.global.v2.u32 {%0,%1}, [%2];"
+                       : "=r"(w[k].x), "=r"(w[k].y) : "l"(q) : "memory");
+        }
+      }
+      bool ok = true;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ok = ok && fword_ready(w[k].x, tag) && fword_ready(w[k].y, tag);
+      if (ok) break;
+      if ((++spins & 63u) == 0) {
+        if (*reinterpret_cast<volatile int*>(sync.abort_flag) != 0) { alive = false; break; }
+        if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
+          raise_abort(sync, s_abort, code, blockIdx.x * 1000 + threadIdx.x, row);
+          alive = false;
+          break;
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const bool have = active && alive && (ul + 16 * k) < nHS;
+    out_a[k] = have ? fword_value(w[k].x) : 0.f;
+    out_b[k] = have ? fword_value(w[k].y) : 0.f;
+  }
+  return alive;
+}
+
+// Combines (mean, M2) pairs of nHS column slices (slice s holds cnt(s) values) into the row's
+// mean and 1/sqrt(var + eps).  Executed by all 16 lanes of the row group.
+__device__ __forceinline__ void chan_combine(const float (&m)[4], const float (&m2)[4], int ul,
+                                             int nHS, int width, int per_slice, float& mean,
+                                             float& invstd) {
+  float cnt[4], s = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int src = ul + 16 * k;
+    const int c = src < nHS ? min(per_slice, width - src * per_slice) : 0;
+    cnt[k] = (float)c;
+    s += cnt[k] * m[k];
+  }
+  mean = row16_sum(s) / (float)width;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const float d = m[k] - mean;
+    q += m2[k] + cnt[k] * d * d;
+  }
+  invstd = rsqrtf(row16_sum(q) / (float)width + kLnEps);
+}
+
+// ---------------------------------------------------------------------------------------
+// Forward
+// ---------------------------------------------------------------------------------------
+template <int KSW, int SPLIT, int MTMAX, typename T>
+__global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p) {
+  constexpr int G = 4;
+  constexpr int COLS = G * U;
+  constexpr int NT = COLS / 8;
+  constexpr int KW = KSW * 16;
+  constexpr int KPAD = WARPS * KW;
+  constexpr int AROW = KPAD + 8;
+  constexpr int PROW = COLS + 8;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int BNR = p.MT * 16;
+  // fp32 storage: h in three bf16 planes (a0 + a1 + a2 carries 24 mantissa bits)
+  constexpr int PA = SPLIT == 2 ? 3 : 1;
+  __nv_bfloat16* a_hi = reinterpret_cast<__nv_bfloat16*>(smem);
+  const size_t a_plane = (size_t)16 * AROW;  // one m-tile; each warp only touches its own K range
+  float* part = reinterpret_cast<float*>(smem + (size_t)PA * a_plane * 2);  // [2][8][16][PROW]
+  // fp32 storage: third plane of R as ready-made B fragments, [warp][nt][ks][half][lane]
+  uint32_t* b2f = reinterpret_cast<uint32_t*>(part + (size_t)2 * WARPS * 16 * PROW);
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, q = lane & 3;
+  const int hs = blockIdx.x % p.nHS, bs = blockIdx.x / p.nHS;
+  const int nBS = gridDim.x / p.nHS;
+  const int u0 = hs * U, n0 = bs * BNR;
+  const int H = p.H, N = p.N, Hx = p.Hx;
+  const long long NH = (long long)N * H;
+  const int GH = G * H;
+  if (tid == 0) s_abort = 0;
+
+  // ---- recurrent weights -> registers (B fragments), once
+  uint32_t rf[SPLIT][NT][KSW][2];
+  {
+    const T* R = reinterpret_cast<const T*>(p.R);
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int cl = nt * 8 + gq;  // local column, unit-major: cl = u*G + gate
+      const int u = cl / G, gate = cl % G;
+      const bool col_ok = (u0 + u) < H;
+      const long long col = (long long)gate * H + u0 + u;
+#pragma unroll
+      for (int ks = 0; ks < KSW; ++ks) {
+        const int kb = warp * KW + ks * 16 + 2 * q;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float x0 = 0.f, x1 = 0.f;
+          const int k = kb + half * 8;
+          if (col_ok && k < H) x0 = ld(R + (long long)k * GH + col);
+          if (col_ok && k + 1 < H) x1 = ld(R + (long long)(k + 1) * GH + col);
+          if (SPLIT == 2) {
+            float p0[3], p1[3];
+            split3_bf16(x0, p0);
+            split3_bf16(x1, p1);
+            rf[0][nt][ks][half] = pack_bf16(p0[0], p1[0]);
+            rf[SPLIT - 1][nt][ks][half] = pack_bf16(p0[1], p1[1]);
+            b2f[((((size_t)warp * NT + nt) * KSW + ks) * 2 + half) * 32 + lane] =
+                pack_bf16(p0[2], p1[2]);
+          } else {
+            rf[0][nt][ks][half] = pack_bf16(x0, x1);
+          }
+        }
+      }
+    }
+  }
+
+  // ---- pointwise ownership: thread -> (row nl of each m-tile, unit ul)
+  const int nl = tid >> 4, ul = tid & 15;
+  const bool unit_ok = (u0 + ul) < H;
+  const bool unit_pad = !unit_ok && (u0 + ul) < Hx;
+  const float cnt_units = (float)min(U, H - u0);  // valid units of this CTA
+  T* hbuf = reinterpret_cast<T*>(p.h);
+  T* cbuf = reinterpret_cast<T*>(p.c);
+  T* vbuf = reinterpret_cast<T*>(p.v);
+  T* rhbuf = reinterpret_cast<T*>(p.act_Rh);
+  T* cnbuf = reinterpret_cast<T*>(p.act_c_norm);
+  T* cache1 = reinterpret_cast<T*>(p.cache_Rh);
+  T* cache3 = reinterpret_cast<T*>(p.cache_c);
+  const T* mask = reinterpret_cast<const T*>(p.mask);
+  float bias[G], g1[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    bias[g] = unit_ok ? ld(reinterpret_cast<const T*>(p.b) + g * H + u0 + ul) : 0.f;
+    g1[g] = unit_ok ? ld(reinterpret_cast<const T*>(p.gamma_Rh) + g * H + u0 + ul) : 0.f;
+  }
+  const float gh = unit_ok ? ld(reinterpret_cast<const T*>(p.gamma_h) + u0 + ul) : 0.f;
+  const float bh = unit_ok ? ld(reinterpret_cast<const T*>(p.beta_h) + u0 + ul) : 0.f;
+  float c_reg[MTMAX], h_reg[MTMAX];
+#pragma unroll
+  for (int mt = 0; mt < MTMAX; ++mt) {
+    const int n = n0 + mt * 16 + nl;
+    const bool ok = mt < p.MT && n < N && unit_ok;
+    h_reg[mt] = ok ? ld(hbuf + (long long)n * H + u0 + ul) : 0.f;
+    c_reg[mt] = ok ? ld(cbuf + (long long)n * H + u0 + ul) : 0.f;
+  }
+
+  __syncthreads();
+
+  const size_t sarea = (size_t)BNR * p.nHS * 2;  // words of one (statistic, parity, slice) area
+  bool alive = true;
+  int pbuf = 0;
+  for (int t = 0; t < p.T && alive; ++t) {
+    const uint32_t tag = (((uint32_t)t >> 1) & 1u) ^ 1u;
+    uint32_t* area1 = p.sbuf + (((size_t)0 * 2 + (t & 1)) * nBS + bs) * sarea;
+    uint32_t* area3 = p.sbuf + (((size_t)1 * 2 + (t & 1)) * nBS + bs) * sarea;
+    // ---- loads that do not depend on the recurrence: LN(x.W) (+ zoneout mask)
+    float wxr[MTMAX][G], mk[MTMAX];
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+      const int n = n0 + mt * 16 + nl;
+      const bool ok = mt < p.MT && n < N && unit_ok;
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+        wxr[mt][g] = ok ? ld(vbuf + ((long long)t * N + n) * GH + g * H + u0 + ul) : 0.f;
+      mk[mt] = (ok && p.has_zoneout && p.training)
+                   ? ld(mask + (long long)t * NH + (long long)n * H + u0 + ul) : 0.f;
+    }
+
+    // ---- stage A: step product, pre-norm h.R saved, its row statistics published
+    float rh[MTMAX][G];
+    bool stop = false;  // CTA-uniform: taken from a barrier-wide OR of the abort flag
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) rh[mt][g] = 0.f;
+      if (mt < p.MT && !stop) {
+        // ---- this warp's K range of h_t for the rows of m-tile mt -> the A planes.  At t = 0
+        // the caller's initial state; afterwards the tagged words the producers wrote.
+        {
+          constexpr int CPR = KW / 4;         // 4-element chunks per row in this warp's range
+          constexpr int CPL = 16 * CPR / 32;  // chunks per lane
+          __syncwarp();                       // the previous m-tile's fragment loads are done
+          if (t == 0) {
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+              const int e = lane + i * 32;
+              const int r = e / CPR, k = warp * KW + (e % CPR) * 4;
+              const int n = n0 + mt * 16 + r;
+              float x[4];
+#pragma unroll
+              for (int j4 = 0; j4 < 4; ++j4)
+                x[j4] = (n < N && k + j4 < H) ? ld(hbuf + (long long)n * H + k + j4) : 0.f;
+              if (SPLIT == 2) {
+                float px[3], py[3], pz[3], pw[3];
+                split3_bf16(x[0], px); split3_bf16(x[1], py);
+                split3_bf16(x[2], pz); split3_bf16(x[3], pw);
+#pragma unroll
+                for (int k3 = 0; k3 < PA; ++k3)
+                  *reinterpret_cast<uint2*>(a_hi + k3 * a_plane + (size_t)r * AROW + k) = make_uint2(
+                      pack_bf16(px[k3 % 3], py[k3 % 3]), pack_bf16(pz[k3 % 3], pw[k3 % 3]));
+              } else {
+                *reinterpret_cast<uint2*>(a_hi + (size_t)r * AROW + k) =
+                    make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+              }
+            }
+          } else if (alive) {
+            const uint32_t want = (((uint32_t)(t - 1) >> 1) & 1u) ^ 1u;
+            const uint32_t* xsrc = p.xbuf + (size_t)((t - 1) & 1) * N * Hx;
+            uint4 w[CPL];
+            const long long t0 = clock64();
+            unsigned int spins = 0;
+            for (;;) {
+              // issue every load before looking at any of them, so their latencies overlap
+#pragma unroll
+              for (int i = 0; i < CPL; ++i) {
+                const int e = lane + i * 32;
+                const int r = e / CPR, k = warp * KW + (e % CPR) * 4;
+                const int n = n0 + mt * 16 + r;
+                if (n < N && k < Hx) w[i] = ld_relaxed_u32x4(xsrc + (size_t)n * Hx + k);
+                else w[i] = SPLIT == 2 ? make_uint4(want, want, want, want)
+                                       : make_uint4(want << 30, want << 30, want << 30, want << 30);
+              }
+              bool ok = true;
+#pragma unroll
+              for (int i = 0; i < CPL; ++i)
+                ok = ok && hword_ready<SPLIT>(w[i].x, want) && hword_ready<SPLIT>(w[i].y, want) &&
+                     hword_ready<SPLIT>(w[i].z, want) && hword_ready<SPLIT>(w[i].w, want);
+              if (__all_sync(0xffffffffu, ok)) break;
+              if ((++spins & 63u) == 0) {
+                bool quit = *reinterpret_cast<volatile int*>(p.sync.abort_flag) != 0;
+                if (!quit && clock64() - t0 > SPIN_LIMIT_CYCLES) {
+                  raise_abort(p.sync, &s_abort, 26, blockIdx.x, t);
+                  quit = true;
+                }
+                if (__any_sync(0xffffffffu, quit)) { alive = false; break; }
+              }
+            }
+            if (!alive) *reinterpret_cast<volatile int*>(&s_abort) = 1;  // the barrier below sees it
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+              const int e = lane + i * 32;
+              const int r = e / CPR, k = warp * KW + (e % CPR) * 4;
+              if (SPLIT == 2) {
+                float px[3], py[3], pz[3], pw[3];
+                split3_bf16(fword_value(w[i].x), px);
+                split3_bf16(fword_value(w[i].y), py);
+                split3_bf16(fword_value(w[i].z), pz);
+                split3_bf16(fword_value(w[i].w), pw);
+#pragma unroll
+                for (int k3 = 0; k3 < PA; ++k3)
+                  *reinterpret_cast<uint2*>(a_hi + k3 * a_plane + (size_t)r * AROW + k) = make_uint2(
+                      pack_bf16(px[k3 % 3], py[k3 % 3]), pack_bf16(pz[k3 % 3], pw[k3 % 3]));
+              } else {
+                *reinterpret_cast<uint2*>(a_hi + (size_t)r * AROW + k) = make_uint2(
+                    __byte_perm(w[i].x, w[i].y, 0x5410), __byte_perm(w[i].z, w[i].w, 0x5410));
+              }
+            }
+          }
+          __syncwarp();
+        }
+        float acc[NT][4];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KSW; ++ks) {
+          const int row = lane & 15;
+          const int kcol = warp * KW + ks * 16 + (lane >> 4) * 8;
+          uint32_t a0[4], a1[4], a2[4];
+          ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), a0);
+          if (SPLIT == 2) {
+            ldmatrix_x4(smem_u32(a_hi + a_plane + (size_t)row * AROW + kcol), a1);
+            ldmatrix_x4(smem_u32(a_hi + (PA - 1) * a_plane + (size_t)row * AROW + kcol), a2);
+          }
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            if (SPLIT == 2) {
+              // six products, smallest first: everything above 2^-24 of the result
+              const uint32_t* bq = b2f + ((((size_t)warp * NT + nt) * KSW + ks) * 2) * 32 + lane;
+              mma_bf16(acc[nt], a0, bq[0], bq[32]);
+              mma_bf16(acc[nt], a2, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+              mma_bf16(acc[nt], a1, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+              mma_bf16(acc[nt], a0, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+              mma_bf16(acc[nt], a1, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+            }
+            mma_bf16(acc[nt], a0, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+          }
+        }
+        float* pb = part + (size_t)pbuf * WARPS * 16 * PROW;
+        float* pw = pb + (size_t)warp * 16 * PROW;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          *reinterpret_cast<float2*>(pw + gq * PROW + nt * 8 + 2 * q) =
+              make_float2(acc[nt][0], acc[nt][1]);
+          *reinterpret_cast<float2*>(pw + (gq + 8) * PROW + nt * 8 + 2 * q) =
+              make_float2(acc[nt][2], acc[nt][3]);
+        }
+        stop = __syncthreads_or(*reinterpret_cast<volatile int*>(&s_abort)) != 0;
+#pragma unroll
+        for (int w = 0; w < WARPS; ++w) {
+          const float4 f =
+              *reinterpret_cast<const float4*>(pb + ((size_t)w * 16 + nl) * PROW + ul * G);
+          rh[mt][0] += f.x; rh[mt][1] += f.y; rh[mt][2] += f.z; rh[mt][3] += f.w;
+        }
+        pbuf ^= 1;
+        const int n = n0 + mt * 16 + nl;
+        const bool ok = n < N && unit_ok;
+        if (ok) {
+          T* rt = rhbuf + ((long long)t * N + n) * GH + u0 + ul;
+#pragma unroll
+          for (int g = 0; g < G; ++g) st(rt + g * H, rh[mt][g]);
+        }
+        const float s = ok ? (rh[mt][0] + rh[mt][1]) + (rh[mt][2] + rh[mt][3]) : 0.f;
+        const float m_loc = row16_sum(s) / (G * cnt_units);
+        float dd = 0.f;
+        if (ok) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) dd += (rh[mt][g] - m_loc) * (rh[mt][g] - m_loc);
+        }
+        dd = row16_sum(dd);
+        if (ul == 0 && n < N) stat_publish(area1, mt * 16 + nl, hs, p.nHS, tag, m_loc, dd);
+      }
+    }
+    if (stop) break;
+
+    // ---- stage B: LayerNorm of h.R, gates, new cell state, its row statistics published
+    float og[MTMAX], cnew[MTMAX];
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+      og[mt] = cnew[mt] = 0.f;
+      if (mt < p.MT) {
+        const int n = n0 + mt * 16 + nl;
+        const bool ok = n < N && unit_ok;
+        float sa[4], sb[4], mean1, inv1;
+        if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 27))
+          *reinterpret_cast<volatile int*>(&s_abort) = 1;
+        chan_combine(sa, sb, ul, p.nHS, GH, COLS, mean1, inv1);
+        float pre[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+          pre[g] = (rh[mt][g] - mean1) * inv1 * g1[g] + wxr[mt][g] + bias[g];
+        const float i = sigmoid_fast(pre[0]);
+        const float gg = tanh_fast(pre[1]);
+        const float f = sigmoid_fast(pre[2]);
+        const float o = sigmoid_fast(pre[3]);
+        const float c_new = f * c_reg[mt] + i * gg;
+        og[mt] = o;
+        cnew[mt] = c_new;
+        const float s = row16_sum(ok ? c_new : 0.f);
+        const float m_loc = s / cnt_units;
+        const float dd = row16_sum(ok ? (c_new - m_loc) * (c_new - m_loc) : 0.f);
+        if (ul == 0 && n < N) stat_publish(area3, mt * 16 + nl, hs, p.nHS, tag, m_loc, dd);
+        if (ok) {
+          st(cbuf + (long long)(t + 1) * NH + (long long)n * H + u0 + ul, c_new);
+          if (p.training) {
+            T* vt = vbuf + ((long long)t * N + n) * GH + u0 + ul;
+            st(vt, i); st(vt + H, gg); st(vt + 2 * H, f); st(vt + 3 * H, o);
+          }
+        }
+        if (hs == 0 && ul == 0 && n < N) {
+          st(cache1 + ((long long)t * N + n) * 2, mean1);
+          st(cache1 + ((long long)t * N + n) * 2 + 1, inv1);
+        }
+      }
+    }
+
+    // ---- stage C: LayerNorm of the cell state, output, h_t published
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+      if (mt < p.MT) {
+        const int n = n0 + mt * 16 + nl;
+        const bool ok = n < N && unit_ok;
+        float sa[4], sb[4], mean3, inv3;
+        if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 28))
+          *reinterpret_cast<volatile int*>(&s_abort) = 1;
+        chan_combine(sa, sb, ul, p.nHS, H, U, mean3, inv3);
+        const float c_norm = (cnew[mt] - mean3) * inv3 * gh + bh;
+        float h_new = og[mt] * tanh_fast(c_norm);
+        if (p.has_zoneout)
+          h_new = p.training ? zoneout<true>(h_new, h_reg[mt], p.zoneout_prob, mk[mt])
+                             : zoneout<false>(h_new, h_reg[mt], p.zoneout_prob, mk[mt]);
+        if (is_bf16<T>::value) h_new = __bfloat162float(__float2bfloat16_rn(h_new));
+        uint32_t* xdst = p.xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul;
+        if (ok) {
+          if (t + 1 < p.T) __stcg(xdst, hword_encode<SPLIT>(h_new, tag));
+          const long long o0 = (long long)n * H + u0 + ul;
+          st(hbuf + (long long)(t + 1) * NH + o0, h_new);
+          st(cnbuf + (long long)t * NH + o0, c_norm);
+          h_reg[mt] = h_new;
+          c_reg[mt] = cnew[mt];
+        } else if (n < N && unit_pad && t + 1 < p.T) {
+          __stcg(xdst, hword_encode<SPLIT>(0.0f, tag));
+        }
+        if (hs == 0 && ul == 0 && n < N) {
+          st(cache3 + ((long long)t * N + n) * 2, mean3);
+          st(cache3 + ((long long)t * N + n) * 2 + 1, inv3);
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward
+// ---------------------------------------------------------------------------------------
+template <int NTW, int SPLIT, int MTMAX, typename T>
+__global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p) {
+  constexpr int G = 4;
+  constexpr int COLS = G * U;
+  constexpr int KS = COLS / 16;
+  constexpr int AROW = COLS + 8;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int BNR = p.MT * 16;
+  constexpr int PA = SPLIT == 2 ? 3 : 1;  // fp32 storage: three bf16 planes per operand
+  __nv_bfloat16* a_base = reinterpret_cast<__nv_bfloat16*>(smem);  // [2][PA][BNR][AROW]
+  const size_t a_plane = (size_t)BNR * AROW;
+  // fp32 storage: third plane of R^T as B fragments, [warp][nt][ks][half][lane]
+  uint32_t* b2f = reinterpret_cast<uint32_t*>(smem + (size_t)2 * PA * a_plane * 2);
+  __shared__ int s_abort;
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gq = lane >> 2, q = lane & 3;
+  const int hs = blockIdx.x % p.nHS, bs = blockIdx.x / p.nHS;
+  const int nBS = gridDim.x / p.nHS;
+  const int u0 = hs * U, n0 = bs * BNR;
+  const int H = p.H, N = p.N;
+  const long long NH = (long long)N * H;
+  const int GH = G * H;
+  if (tid == 0) s_abort = 0;
+  for (int e = tid; e < 2 * PA * (int)a_plane; e += THREADS) a_base[e] = __float2bfloat16_rn(0.f);
+
+  // ---- R[:, slice]^T as B fragments (k = local gate column u*G+gate, n = output unit j)
+  uint32_t rf[SPLIT][NTW][KS][2];
+  {
+    const T* R = reinterpret_cast<const T*>(p.R);
+#pragma unroll
+    for (int nt = 0; nt < NTW; ++nt) {
+      const int j = (warp * NTW + nt) * 8 + gq;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          float x[2];
+#pragma unroll
+          for (int e = 0; e < 2; ++e) {
+            const int cl = ks * 16 + half * 8 + 2 * q + e;
+            const int u = cl / G, gate = cl % G;
+            float val = 0.f;
+            if (j < H && (u0 + u) < H) {
+              const long long col = (long long)gate * H + u0 + u;
+              val = p.r_transposed ? ld(R + col * H + j) : ld(R + (long long)j * GH + col);
+            }
+            x[e] = val;
+          }
+          if (SPLIT == 2) {
+            float p0[3], p1[3];
+            split3_bf16(x[0], p0);
+            split3_bf16(x[1], p1);
+            rf[0][nt][ks][half] = pack_bf16(p0[0], p1[0]);
+            rf[SPLIT - 1][nt][ks][half] = pack_bf16(p0[1], p1[1]);
+            b2f[((((size_t)warp * NTW + nt) * KS + ks) * 2 + half) * 32 + lane] =
+                pack_bf16(p0[2], p1[2]);
+          } else {
+            rf[0][nt][ks][half] = pack_bf16(x[0], x[1]);
+          }
+        }
+      }
+    }
+  }
+
+  const int nl = tid >> 4, ul = tid & 15;
+  const bool unit_ok = (u0 + ul) < H;
+  const T* cbuf = reinterpret_cast<const T*>(p.c);
+  T* vbuf = reinterpret_cast<T*>(p.v);
+  T* rhbuf = reinterpret_cast<T*>(p.act_Rh);
+  const T* cnbuf = reinterpret_cast<const T*>(p.act_c_norm);
+  const T* cache1 = reinterpret_cast<const T*>(p.cache_Rh);
+  const T* cache3 = reinterpret_cast<const T*>(p.cache_c);
+  const T* dhn = reinterpret_cast<const T*>(p.dh_new);
+  const T* dcn = reinterpret_cast<const T*>(p.dc_new);
+  const T* mask = reinterpret_cast<const T*>(p.mask);
+  float g1[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+    g1[g] = unit_ok ? ld(reinterpret_cast<const T*>(p.gamma_Rh) + g * H + u0 + ul) : 0.f;
+  const float gh = unit_ok ? ld(reinterpret_cast<const T*>(p.gamma_h) + u0 + ul) : 0.f;
+  const float inv_H = 1.0f / (float)H, inv_GH = 1.0f / (float)GH;
+
+  float dh_c[MTMAX], dc_c[MTMAX];
+#pragma unroll
+  for (int mt = 0; mt < MTMAX; ++mt) {
+    const int n = n0 + mt * 16 + nl;
+    const bool ok = mt < p.MT && n < N && unit_ok;
+    dh_c[mt] = ok ? p.dh_carry[(long long)n * H + u0 + ul] : 0.f;
+    dc_c[mt] = ok ? p.dc_carry[(long long)n * H + u0 + ul] : 0.f;
+  }
+  float acc_g1[G] = {0.f, 0.f, 0.f, 0.f}, acc_gh = 0.f, acc_bh = 0.f;  // parameter gradients
+  const size_t blk = (size_t)BNR * U;
+  const size_t sarea = (size_t)BNR * p.nHS * 2;
+  bool alive = true;
+  __syncthreads();
+
+  for (int t = p.T - 1; t >= 0 && alive; --t) {
+    const int ti = p.T - 1 - t;
+    const uint32_t tag = (((uint32_t)ti >> 1) & 1u) ^ 1u;
+    uint32_t* area3 = p.sbuf + (((size_t)0 * 2 + (ti & 1)) * nBS + bs) * sarea;
+    uint32_t* area1 = p.sbuf + (((size_t)1 * 2 + (ti & 1)) * nBS + bs) * sarea;
+    // ---- loads independent of the carried gradient
+    float gv[MTMAX][G], rhv[MTMAX][G], cprev[MTMAX], cx3[MTMAX], cnv[MTMAX], dhv[MTMAX],
+        dcv[MTMAX], mk[MTMAX], mean1[MTMAX], inv1[MTMAX], inv3[MTMAX];
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+      const int n = n0 + mt * 16 + nl;
+      const bool rok = mt < p.MT && n < N;
+      const bool ok = rok && unit_ok;
+      const long long o0 = (long long)n * H + u0 + ul;
+      const long long w0 = ((long long)t * N + n) * GH + u0 + ul;
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        gv[mt][g] = ok ? ld(vbuf + w0 + g * H) : 0.f;
+        rhv[mt][g] = ok ? ld(rhbuf + w0 + g * H) : 0.f;
+      }
+      dhv[mt] = ok ? ld(dhn + (long long)(t + 1) * NH + o0) : 0.f;
+      dcv[mt] = ok ? ld(dcn + (long long)(t + 1) * NH + o0) : 0.f;
+      mk[mt] = (ok && p.has_zoneout) ? ld(mask + (long long)t * NH + o0) : 1.f;
+      cprev[mt] = ok ? ld(cbuf + (long long)t * NH + o0) : 0.f;
+      cnv[mt] = ok ? ld(cnbuf + (long long)t * NH + o0) : 0.f;
+      const float mean3 = rok ? ld(cache3 + ((long long)t * N + n) * 2) : 0.f;
+      inv3[mt] = rok ? ld(cache3 + ((long long)t * N + n) * 2 + 1) : 0.f;
+      cx3[mt] = ok ? ld(cbuf + (long long)(t + 1) * NH + o0) - mean3 : 0.f;
+      mean1[mt] = rok ? ld(cache1 + ((long long)t * N + n) * 2) : 0.f;
+      inv1[mt] = rok ? ld(cache1 + ((long long)t * N + n) * 2 + 1) : 0.f;
+    }
+
+    // ---- recurrent part of dh_t: the partials published at the previous step
+    if (ti > 0) {
+      const uint32_t want = (((uint32_t)(ti - 1) >> 1) & 1u) ^ 1u;
+      const uint32_t* src =
+          p.exch + ((((size_t)((ti - 1) & 1) * nBS + bs) * p.nHS + hs) * p.nHS) * blk;
+      const int sg = ul & 3, quad = ul >> 2;
+#pragma unroll
+      for (int mt = 0; mt < MTMAX; ++mt) {
+        if (mt < p.MT) {
+          float s4[4] = {0.f, 0.f, 0.f, 0.f};
+          const uint32_t* q0 = src + (size_t)(mt * 16 + nl) * U + quad * 4;
+          for (int s0 = 0; s0 < p.nHS && alive; s0 += 32) {
+            uint4 a[8];
+            const long long t0 = clock64();
+            unsigned int spins = 0;
+            const uint32_t rdy = want;
+            for (;;) {
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                const int sidx = s0 + sg * 8 + k;
+                a[k] = (sidx < p.nHS) ? ld_relaxed_u32x4(q0 + (size_t)sidx * blk)
+                                      : make_uint4(rdy, rdy, rdy, rdy);
+              }
+              bool ok = true;
+#pragma unroll
+              for (int k = 0; k < 8; ++k)
+                ok = ok && fword_ready(a[k].x, want) && fword_ready(a[k].y, want) &&
+                     fword_ready(a[k].z, want) && fword_ready(a[k].w, want);
+              if (ok) break;
+              if ((++spins & 63u) == 0) {
+                if (*reinterpret_cast<volatile int*>(p.sync.abort_flag) != 0) { alive = false; break; }
+                if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
+                  raise_abort(p.sync, &s_abort, 37, blockIdx.x * 1000 + tid, ti * 100 + s0);
+                  alive = false;
+                  break;
+                }
+              }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              s4[0] += fword_value(a[k].x);
+              s4[1] += fword_value(a[k].y);
+              s4[2] += fword_value(a[k].z);
+              s4[3] += fword_value(a[k].w);
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            s4[j] += __shfl_xor_sync(0xffffffffu, s4[j], 1);
+            s4[j] += __shfl_xor_sync(0xffffffffu, s4[j], 2);
+          }
+          dh_c[mt] += sg == 0 ? s4[0] : (sg == 1 ? s4[1] : (sg == 2 ? s4[2] : s4[3]));
+        }
+      }
+    }
+    if (!alive) *reinterpret_cast<volatile int*>(&s_abort) = 1;
+    alive = true;  // from here on failures only mark s_abort; the barrier below decides
+
+    // ---- stage A: output gate and LayerNorm(c') input gradients; LN(c') row sums published
+    float d_o[MTMAX], db3[MTMAX];
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+      d_o[mt] = db3[mt] = 0.f;
+      if (mt < p.MT) {
+        const int n = n0 + mt * 16 + nl;
+        float dh_total = dhv[mt] + dh_c[mt];
+        float keep = 0.f;
+        if (p.has_zoneout) {
+          keep = (1.0f - mk[mt]) * dh_total;
+          dh_total = mk[mt] * dh_total;
+        }
+        dh_c[mt] = keep;
+        const float o = gv[mt][3];
+        const float c_tanh = tanh_fast(cnv[mt]);
+        d_o[mt] = d_sigmoid(o) * (c_tanh * dh_total);
+        const float dcn_ = d_tanh(c_tanh) * (o * dh_total);  // gradient w.r.t. LayerNorm(c')
+        acc_gh += cx3[mt] * inv3[mt] * dcn_;
+        acc_bh += dcn_;
+        db3[mt] = gh * dcn_;
+        const float s1 = row16_sum(cx3[mt] * db3[mt]);
+        const float s2 = row16_sum(db3[mt]);
+        if (ul == 0 && n < N) stat_publish(area3, mt * 16 + nl, hs, p.nHS, tag, s1, s2);
+      }
+    }
+
+    // ---- stage B: gate gradients; LN(h.R) row sums published
+    float dgate[MTMAX][G];
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) dgate[mt][g] = 0.f;
+      if (mt < p.MT) {
+        const int n = n0 + mt * 16 + nl;
+        const bool ok = n < N && unit_ok;
+        float sa[4], sb[4];
+        if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 38))
+          *reinterpret_cast<volatile int*>(&s_abort) = 1;
+        const float S1 = row16_sum((sa[0] + sa[1]) + (sa[2] + sa[3]));
+        const float S2 = row16_sum((sb[0] + sb[1]) + (sb[2] + sb[3]));
+        const float r = inv3[mt];
+        const float dsigma = -0.5f * S1 * r * r * r;
+        const float dmu = -S2 * r;
+        const float dcl = 2.0f * cx3[mt] * dsigma * inv_H + r * db3[mt] + dmu * inv_H;
+        const float i = gv[mt][0], gg = gv[mt][1], f = gv[mt][2];
+        const float dc_total = ok ? dcv[mt] + dc_c[mt] + dcl : 0.f;
+        dgate[mt][0] = d_sigmoid(i) * (gg * dc_total);
+        dgate[mt][1] = d_tanh(gg) * (i * dc_total);
+        dgate[mt][2] = d_sigmoid(f) * (cprev[mt] * dc_total);
+        dgate[mt][3] = d_o[mt];
+        dc_c[mt] = f * dc_total;
+        float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float cx = rhv[mt][g] - mean1[mt];
+          const float db = g1[g] * dgate[mt][g];
+          if (ok) {
+            s1 += cx * db;
+            s2 += db;
+            acc_g1[g] += cx * inv1[mt] * dgate[mt][g];
+          }
+        }
+        s1 = row16_sum(s1);
+        s2 = row16_sum(s2);
+        if (ul == 0 && n < N) stat_publish(area1, mt * 16 + nl, hs, p.nHS, tag, s1, s2);
+        if (ok) {
+          const long long w0 = ((long long)t * N + n) * GH + u0 + ul;
+#pragma unroll
+          for (int g = 0; g < G; ++g) st(vbuf + w0 + g * H, dgate[mt][g]);
+          if (SPLIT == 2 && p.gpl) {
+#pragma unroll
+            for (int g = 0; g < G; ++g) {
+              float hi, lo;
+              split_bf16(dgate[mt][g], hi, lo);
+              p.gpl[w0 + g * H] = __float2bfloat16_rn(hi);
+              p.gpl[p.gpl_stride + w0 + g * H] = __float2bfloat16_rn(lo);
+            }
+          }
+        }
+      }
+    }
+
+    // ---- stage C: gradient w.r.t. the pre-norm h.R -> global and -> smem (A operand)
+    __nv_bfloat16* a_hi = a_base + (size_t)(ti & 1) * PA * a_plane;
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+      if (mt < p.MT) {
+        const int n = n0 + mt * 16 + nl;
+        const bool ok = n < N && unit_ok;
+        float sa[4], sb[4];
+        if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 39))
+          *reinterpret_cast<volatile int*>(&s_abort) = 1;
+        const float S1 = row16_sum((sa[0] + sa[1]) + (sa[2] + sa[3]));
+        const float S2 = row16_sum((sb[0] + sb[1]) + (sb[2] + sb[3]));
+        const float r = inv1[mt];
+        const float dsigma = -0.5f * S1 * r * r * r;
+        const float dmu = -S2 * r;
+        __nv_bfloat16* rowh = a_hi + (size_t)(mt * 16 + nl) * AROW + ul * G;
+        const long long w0 = ((long long)t * N + n) * GH + u0 + ul;
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float cx = rhv[mt][g] - mean1[mt];
+          const float x = ok ? 2.0f * cx * dsigma * inv_GH + r * (g1[g] * dgate[mt][g]) + dmu * inv_GH
+                             : 0.f;
+          float pl[3] = {x, 0.f, 0.f};
+          if (SPLIT == 2) split3_bf16(x, pl);
+#pragma unroll
+          for (int k3 = 0; k3 < PA; ++k3) rowh[k3 * a_plane + g] = __float2bfloat16_rn(pl[k3 % 3]);
+          if (ok) {
+            st(rhbuf + w0 + g * H, x);
+            if (SPLIT == 2 && p.gpl2) {
+              p.gpl2[w0 + g * H] = __float2bfloat16_rn(pl[0]);
+              p.gpl2[p.gpl_stride + w0 + g * H] = __float2bfloat16_rn(pl[1]);
+            }
+          }
+        }
+      }
+    }
+    if (t == 0) break;
+    if (__syncthreads_or(*reinterpret_cast<volatile int*>(&s_abort))) { alive = false; break; }
+
+    // ---- partial dh_{t-1}[rows, all units] = d(h.R) . R[:, slice]^T
+    {
+      uint32_t* dstbase = p.exch + ((size_t)(ti & 1) * nBS + bs) * p.nHS * p.nHS * blk;
+      for (int mt = 0; mt < p.MT; ++mt) {
+        float acc[NTW][4];
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+          const int row = mt * 16 + (lane & 15);
+          const int kcol = ks * 16 + (lane >> 4) * 8;
+          uint32_t a0[4], a1[4], a2[4];
+          ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), a0);
+          if (SPLIT == 2) {
+            ldmatrix_x4(smem_u32(a_hi + a_plane + (size_t)row * AROW + kcol), a1);
+            ldmatrix_x4(smem_u32(a_hi + (PA - 1) * a_plane + (size_t)row * AROW + kcol), a2);
+          }
+#pragma unroll
+          for (int nt = 0; nt < NTW; ++nt) {
+            if (SPLIT == 2) {
+              const uint32_t* bq = b2f + ((((size_t)warp * NTW + nt) * KS + ks) * 2) * 32 + lane;
+              mma_bf16(acc[nt], a0, bq[0], bq[32]);
+              mma_bf16(acc[nt], a2, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+              mma_bf16(acc[nt], a1, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+              mma_bf16(acc[nt], a0, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+              mma_bf16(acc[nt], a1, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+            }
+            mma_bf16(acc[nt], a0, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+          }
+        }
+#pragma unroll
+        for (int nt = 0; nt < NTW; ++nt) {
+          const int j = (warp * NTW + nt) * 8 + 2 * q;
+          if (j < p.nHS * U) {
+            const int dest = j / U, uj = j % U;
+            uint32_t* d = dstbase + ((size_t)dest * p.nHS + hs) * blk + (size_t)(mt * 16) * U + uj;
+            __stcg(reinterpret_cast<uint2*>(d + (size_t)gq * U),
+                   make_uint2(fword_encode(acc[nt][0], tag), fword_encode(acc[nt][1], tag)));
+            __stcg(reinterpret_cast<uint2*>(d + (size_t)(gq + 8) * U),
+                   make_uint2(fword_encode(acc[nt][2], tag), fword_encode(acc[nt][3], tag)));
+          }
+        }
+      }
+    }
+  }
+
+  // ---- carries and per-row-group parameter-gradient partials out
+  if (alive && !*reinterpret_cast<volatile int*>(&s_abort)) {
+#pragma unroll
+    for (int mt = 0; mt < MTMAX; ++mt) {
+      const int n = n0 + mt * 16 + nl;
+      if (mt < p.MT && n < N && unit_ok) {
+        p.dh_carry[(long long)n * H + u0 + ul] = dh_c[mt];
+        p.dc_carry[(long long)n * H + u0 + ul] = dc_c[mt];
+      }
+    }
+  }
+  if (unit_ok) {
+    const long long r = (long long)bs * 16 + nl;
+#pragma unroll
+    for (int g = 0; g < G; ++g) p.dgRh_part[r * GH + g * H + u0 + ul] = acc_g1[g];
+    p.dgh_part[r * H + u0 + ul] = acc_gh;
+    p.dbh_part[r * H + u0 + ul] = acc_bh;
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host-side dispatch (instantiated one storage type per translation unit)
+// ---------------------------------------------------------------------------------------
+template <int SPLIT, typename T>
+int run_ln_fwd(LnFwdParams& p, const Geometry& g, cudaStream_t s) {
+  const int ksw = ceil_div(ceil_div(p.H, 16), WARPS);
+  auto smem_for = [&](int KSW) {
+    const size_t arow = (size_t)WARPS * KSW * 16 + 8;
+    return (size_t)(SPLIT == 2 ? 3 : 1) * 16 * arow * 2 +
+           (size_t)2 * WARPS * 16 * (4 * U + 8) * 4 + (SPLIT == 2 ? (size_t)KSW * 16384 : 0);
+  };
+  const int grid = g.nHS * g.nBS;
+#define HB_FWD(KSW)                                                                       \
+  if (ksw <= KSW) {                                                                       \
+    if (smem_for(KSW) > 220 * 1024) return HASTE_B200_ERR_UNSUPPORTED;                    \
+    if (g.MT == 1)                                                                        \
+      return launch_coop(ln_fwd_kernel<KSW, SPLIT, 1, T>, grid, smem_for(KSW), &p, s);    \
+    return launch_coop(ln_fwd_kernel<KSW, SPLIT, 4, T>, grid, smem_for(KSW), &p, s);      \
+  }
+  HB_FWD(1)
+  HB_FWD(2)
+  HB_FWD(4)
+  if constexpr (SPLIT == 1) { HB_FWD(8) }
+#undef HB_FWD
+  return HASTE_B200_ERR_UNSUPPORTED;
+}
+
+inline int ntw_pad(int ntw) { return ntw <= 1 ? 1 : ntw <= 2 ? 2 : ntw <= 4 ? 4 : ntw <= 8 ? 8 : 16; }
+
+template <int SPLIT, typename T>
+int run_ln_bwd(LnBwdParams& p, const Geometry& g, cudaStream_t s) {
+  const int ntw = ceil_div(ceil_div(p.H, 8), WARPS);
+  const size_t smem = (size_t)2 * (SPLIT == 2 ? 3 : 1) * g.MT * 16 * (4 * U + 8) * 2 +
+                      (SPLIT == 2 ? (size_t)ntw_pad(ntw) * 8192 : 0);  // + third plane of R^T
+  const int grid = g.nHS * g.nBS;
+#define HB_BWD(NTW)                                                                \
+  if (ntw <= NTW) {                                                                \
+    if (g.MT == 1)                                                                 \
+      return launch_coop(ln_bwd_kernel<NTW, SPLIT, 1, T>, grid, smem, &p, s);      \
+    return launch_coop(ln_bwd_kernel<NTW, SPLIT, 4, T>, grid, smem, &p, s);        \
+  }
+  HB_BWD(1)
+  HB_BWD(2)
+  HB_BWD(4)
+  HB_BWD(8)
+  if constexpr (SPLIT == 1) { HB_BWD(16) }
+#undef HB_BWD
+  return HASTE_B200_ERR_UNSUPPORTED;
+}
+
+int run_ln_fwd_f32(LnFwdParams& p, const Geometry& g, cudaStream_t s);
+int run_ln_fwd_bf16(LnFwdParams& p, const Geometry& g, cudaStream_t s);
+int run_ln_bwd_f32(LnBwdParams& p, const Geometry& g, cudaStream_t s);
+int run_ln_bwd_bf16(LnBwdParams& p, const Geometry& g, cudaStream_t s);
+
+}  // namespace rec
+}  // namespace hb
