@@ -62,6 +62,25 @@ class ClockSampler:
         self.thread = threading.Thread(target=self._run, daemon=True)
 
     def _run(self):
+        # NVML (read-only queries) gives a sample every few milliseconds; nvidia-smi, at one
+        # process per sample, is the fallback.
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.index)
+            bits = [("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown),
+                    ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
+                    ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown),
+                    ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap)]
+            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+            while not self.stop.is_set():
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+                self.samples.append([str(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), str(mx)] +
+                                    ["Active" if r & b else "Not Active" for _, b in bits])
+                self.stop.wait(0.005)
+            return
+        except Exception:
+            pass
         while not self.stop.is_set():
             try:
                 out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
@@ -257,11 +276,21 @@ def main():
         "weight_grad": 2.0 * T * N * 4 * H * (C + H),
         "input_grad": 2.0 * T * N * C * 4 * H,
     }
+    # DRAM bytes per time step of the fp32 N=64 H=512 recurrence launches, from one ncu
+    # --set full capture at T=200 (dram__bytes_read.sum + dram__bytes_write.sum over 200
+    # steps; the summary is profiles/rec_kernels_and_gemm_T200_full_capture.md).  Every
+    # step touches its own slice of the activations once, so a launch's traffic is this
+    # times T.
+    ncu_bytes_per_step = {"recurrence_fwd": (109.374208e6 + 104.630528e6) / 200,
+                          "recurrence_bwd": (188.176896e6 + 167.613184e6) / 200}
     dom = max(phases, key=phases.get)
     if dom in alg_bytes:
         ach = alg_bytes[dom] / (phases[dom] * 1e-3) / 1e9
+        captured = args.dtype == "f32" and (N, H) == (64, 512)
         roof = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"],
-                "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
+                "traffic": ncu_bytes_per_step[dom] * T if captured else None,
+                "algorithmic_bytes": alg_bytes[dom],
                 "peak_source": peak_src,
                 "us_per_timestep": phases[dom] * 1e3 / T}
     else:

@@ -125,10 +125,11 @@ int layer_norm_lstm_forward_persistent(const LnLstmFwd& a, cudaStream_t s);
 int layer_norm_lstm_backward_persistent(const LnLstmBwd& a, float* dh_carry, float* dc_carry,
                                         float* acc, const GradPlanes& planes, cudaStream_t s);
 
-// Per-step contraction (M = batch rows).  Small batches are launch-bound and stay on the
-// CUDA-core kernel; from 128 rows up the tensor-core kernel pays for its set-up.
+// Per-step contraction (M = batch rows).  Small products are launch-bound and stay on the
+// CUDA-core kernel; from 2^26 multiply-adds up the tensor-core kernel pays for its set-up
+// (operand split and tensor maps) even with a partly empty 128-row tile.
 inline int gemm_small(const GemmDesc& g, cudaStream_t s) {
-  if (g.M >= 128 && (long long)g.M * g.N * g.K >= (1LL << 26)) return gemm(g, s);
+  if (g.M >= 32 && (long long)g.M * g.N * g.K >= (1LL << 26)) return gemm(g, s);
   return gemm_simt(g, s);
 }
 

@@ -15,9 +15,9 @@ TOL_BF16 = 2e-2
 # LayerNormLSTM with bf16 storage: the tensors the interface stores in bf16 (x.W, LN(x.W), h)
 # are rounded whatever the arithmetic, and the three LayerNorms amplify that rounding.  An
 # exact float64 evaluation that only rounds those stored tensors is already 2e-2 .. 4.5e-2
-# away from the unrounded oracle (test_bf16_storage_floor.py), so the bar for this cell is
-# set above that floor.
-TOL_BF16_LN_LSTM = 6e-2
+# (outputs) and up to 6e-2 (parameter gradients) away from the unrounded oracle
+# (test_bf16_storage_floor.py), so the bar for this cell is set above that floor.
+TOL_BF16_LN_LSTM = 1e-1
 
 
 def golden_files(cell=None):
