@@ -124,6 +124,11 @@ int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& 
 int layer_norm_lstm_forward_persistent(const LnLstmFwd& a, cudaStream_t s);
 int layer_norm_lstm_backward_persistent(const LnLstmBwd& a, float* dh_carry, float* dc_carry,
                                         float* acc, const GradPlanes& planes, cudaStream_t s);
+// LayerNormGRU: forward expects LN(x.W) in a.tmp_Wx_norm; backward adds dgamma_Rh into the
+// fp32 accumulator acc [3H] and leaves d(h.R) in a.act_Rh.
+int layer_norm_gru_forward_persistent(const LnGruFwd& a, cudaStream_t s);
+int layer_norm_gru_backward_persistent(const LnGruBwd& a, float* dh_carry, float* acc,
+                                       const GradPlanes& planes, cudaStream_t s);
 
 // Per-step contraction (M = batch rows).  Small products are launch-bound and stay on the
 // CUDA-core kernel; from 2^26 multiply-adds up the tensor-core kernel pays for its set-up

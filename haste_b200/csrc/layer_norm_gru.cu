@@ -98,6 +98,10 @@ int layer_norm_gru_forward(const LnGruFwd& a, cudaStream_t s) {
   HB_TRY(gemm(g, s));
   HB_TRY(layer_norm_forward(a.dtype, (int)TN, 3 * a.H, a.gamma_Wx, nullptr, a.act_Wx, a.tmp_Wx_norm,
                             a.cache_Wx, s));
+  {
+    const int st_ = layer_norm_gru_forward_persistent(a, s);
+    if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
+  }
   if (a.dtype == HASTE_B200_F32) return forward_steps<float>(a, s);
   return forward_steps<__nv_bfloat16>(a, s);
 }
@@ -127,15 +131,21 @@ int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s) {
   float* acc = ws.take<float>(3 * H);
   HB_REQUIRE(dh_carry && cs && lns && acc, "scratch arena");
   HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
-  void* dgamma1 = a.dgamma_Rh;
-  if (bf) {
-    HB_CUDA_OK(cudaMemsetAsync(acc, 0, 3 * H * sizeof(float), s));
-    dgamma1 = acc;
+  // Persistent recurrence first; it adds dgamma_Rh into `acc`.
+  HB_CUDA_OK(cudaMemsetAsync(acc, 0, 3 * H * sizeof(float), s));
+  int st_ = layer_norm_gru_backward_persistent(a, dh_carry, acc, GradPlanes{}, s);
+  bool use_acc = st_ == HASTE_B200_OK;
+  if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
+    void* dgamma1 = a.dgamma_Rh;
+    if (bf) {
+      dgamma1 = acc;
+      use_acc = true;
+    }
+    st_ = bf ? backward_steps<__nv_bfloat16>(a, dh_carry, dgamma1, lns, s)
+             : backward_steps<float>(a, dh_carry, dgamma1, lns, s);
   }
-  int st_ = bf ? backward_steps<__nv_bfloat16>(a, dh_carry, dgamma1, lns, s)
-               : backward_steps<float>(a, dh_carry, dgamma1, lns, s);
   HB_TRY(st_);
-  if (bf) HB_TRY(add_float_into(a.dtype, acc, a.dgamma_Rh, 3 * H, s));
+  if (use_acc) HB_TRY(add_float_into(a.dtype, acc, a.dgamma_Rh, 3 * H, s));
   HB_TRY(from_float(a.dtype, dh_carry, a.dh, NH, s));
 
   // dp/dq hold gradients w.r.t. the normalised projections (+ bias).

@@ -1,0 +1,9 @@
+// Instantiates the persistent LayerNormGRU fwd recurrence kernels for bf16 storage
+// (one translation unit per combination so that they compile in parallel).
+#include "recurrent_ln_kernels.cuh"
+
+namespace hb {
+namespace rec {
+int run_lngru_fwd_bf16(LnFwdParams& p, const Geometry& g, cudaStream_t s) { return run_ln_fwd<3, 1, __nv_bfloat16>(p, g, s); }
+}  // namespace rec
+}  // namespace hb

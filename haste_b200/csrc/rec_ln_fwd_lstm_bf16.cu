@@ -4,6 +4,6 @@
 
 namespace hb {
 namespace rec {
-int run_ln_fwd_bf16(LnFwdParams& p, const Geometry& g, cudaStream_t s) { return run_ln_fwd<1, __nv_bfloat16>(p, g, s); }
+int run_ln_fwd_bf16(LnFwdParams& p, const Geometry& g, cudaStream_t s) { return run_ln_fwd<4, 1, __nv_bfloat16>(p, g, s); }
 }  // namespace rec
 }  // namespace hb

@@ -4,6 +4,6 @@
 
 namespace hb {
 namespace rec {
-int run_ln_fwd_f32(LnFwdParams& p, const Geometry& g, cudaStream_t s) { return run_ln_fwd<2, float>(p, g, s); }
+int run_ln_fwd_f32(LnFwdParams& p, const Geometry& g, cudaStream_t s) { return run_ln_fwd<4, 2, float>(p, g, s); }
 }  // namespace rec
 }  // namespace hb

@@ -152,7 +152,7 @@ int layer_norm_lstm_forward_persistent(const LnLstmFwd& a, cudaStream_t s) {
   HB_TRY(make_scratch(xwords + swords + 64, &sync, &words, s));
   const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
   LnFwdParams p{a.T, a.N, a.H, Hx, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.b,
-                a.gamma_Rh, a.gamma_h, a.beta_h, a.act_Wx_norm, a.act_Rh, a.cache_Rh,
+                nullptr, a.act_Wx_norm, a.gamma_Rh, a.gamma_h, a.beta_h, a.act_Wx_norm, a.act_Rh, a.cache_Rh,
                 a.act_c_norm, a.cache_c, a.h, a.c, a.zoneout_mask, words,
                 words + ((xwords + 63) & ~size_t(63)), sync};
   return a.dtype == HASTE_B200_F32 ? run_ln_fwd_f32(p, g, s) : run_ln_fwd_bf16(p, g, s);
@@ -177,7 +177,8 @@ int layer_norm_lstm_backward_persistent(const LnLstmBwd& a, float* dh_carry, flo
   float* part = reinterpret_cast<float*>(words + ewords + swords);
   float* cs = part + pwords;
   LnBwdParams p{a.T, a.N, H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R,
-                a.gamma_Rh, a.gamma_h, a.c, a.act_Wx_norm, a.act_Rh, a.cache_Rh, a.act_c_norm,
+                a.gamma_Rh, a.gamma_h, a.c, nullptr, nullptr, nullptr, a.act_Wx_norm, a.act_Rh,
+                a.cache_Rh, a.act_c_norm,
                 a.cache_c, a.dh_new, a.dc_new, a.zoneout_mask, dh_carry, dc_carry, part,
                 part + (size_t)prow * 4 * H, part + (size_t)prow * 5 * H, words, words + ewords,
                 sync, planes.p, planes.p2, planes.stride};
@@ -190,6 +191,56 @@ int layer_norm_lstm_backward_persistent(const LnLstmBwd& a, float* dh_carry, flo
                 acc + 5 * H, 1, cs, s));
   GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 4 * H, a.act_Rh, 4LL * H, 1, a.R,
               a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 4LL * H, dh_carry, H, 1};
+  gd.precise = 1;
+  return gemm_small(gd, s);
+}
+
+// ---- LayerNormGRU (the G = 3 instantiation of the same kernels) ---------------------------
+// Forward: LN(x.W) is already in a.tmp_Wx_norm.
+int layer_norm_gru_forward_persistent(const LnGruFwd& a, cudaStream_t s) {
+  Geometry g;
+  if (!supported(a.dtype, a.N, a.H, &g) || g.nHS > 64) return HASTE_B200_ERR_UNSUPPORTED;
+  const int Hx = (a.H + 3) & ~3;
+  const size_t xwords = (size_t)2 * a.N * Hx;
+  const size_t swords = (size_t)2 * 2 * g.nBS * g.MT * 16 * g.nHS * 2;
+  Sync sync;
+  uint32_t* words = nullptr;
+  HB_TRY(make_scratch(xwords + swords + 64, &sync, &words, s));
+  const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
+  LnFwdParams p{a.T, a.N, a.H, Hx, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.bx,
+                a.br, a.tmp_Wx_norm, a.gamma_Rh, nullptr, nullptr, a.v, a.act_Rh, a.cache_Rh,
+                nullptr, nullptr, a.h, nullptr, a.zoneout_mask, words,
+                words + ((xwords + 63) & ~size_t(63)), sync};
+  return a.dtype == HASTE_B200_F32 ? run_lngru_fwd_f32(p, g, s) : run_lngru_fwd_bf16(p, g, s);
+}
+
+// Backward.  `acc` is the fp32 accumulator [3H] for dgamma_Rh.  a.act_Rh is overwritten with
+// d(h.R); a.dp / a.dq receive the gradients w.r.t. the normalised projections (+ biases).
+int layer_norm_gru_backward_persistent(const LnGruBwd& a, float* dh_carry, float* acc,
+                                       const GradPlanes& planes, cudaStream_t s) {
+  Geometry g;
+  if (!supported(a.dtype, a.N, a.H, &g) || g.nHS > 64) return HASTE_B200_ERR_UNSUPPORTED;
+  const int H = a.H;
+  const size_t ewords = ((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U + 63) & ~size_t(63);
+  const size_t swords = ((size_t)2 * 2 * g.nBS * g.MT * 16 * g.nHS * 2 + 63) & ~size_t(63);
+  const int prow = g.nBS * 16;
+  const size_t pwords = (size_t)prow * 3 * H;
+  const size_t cwords = colsum_scratch_floats(prow, 3 * H);
+  Sync sync;
+  uint32_t* words = nullptr;
+  HB_TRY(make_scratch(ewords + swords + pwords + cwords + 64, &sync, &words, s));
+  float* part = reinterpret_cast<float*>(words + ewords + swords);
+  float* cs = part + pwords;
+  LnBwdParams p{a.T, a.N, H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R,
+                a.gamma_Rh, nullptr, nullptr, a.h, a.dp, a.dq, const_cast<void*>(a.v), a.act_Rh,
+                a.cache_Rh, nullptr, nullptr, a.dh_new, nullptr, a.zoneout_mask, dh_carry, nullptr,
+                part, nullptr, nullptr, words, words + ewords, sync, planes.p, planes.p2,
+                planes.stride};
+  int st_ = a.dtype == HASTE_B200_F32 ? run_lngru_bwd_f32(p, g, s) : run_lngru_bwd_bf16(p, g, s);
+  if (st_ != HASTE_B200_OK) return st_;
+  HB_TRY(colsum(HASTE_B200_F32, part, 3LL * H, prow, 3 * H, HASTE_B200_F32, acc, 1, cs, s));
+  GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 3 * H, a.act_Rh, 3LL * H, 1, a.R,
+              a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 3LL * H, dh_carry, H, 1};
   gd.precise = 1;
   return gemm_small(gd, s);
 }

@@ -31,12 +31,15 @@ struct LnFwdParams {
   int T, N, H, Hx, nHS, MT, training, has_zoneout;
   float zoneout_prob;
   const void* R;        // [H, 4H]
-  const void* b;        // [4H]
-  const void* gamma_Rh; // [4H]
+  const void* b;        // LSTM: b [4H];  GRU: bx [3H]
+  const void* b2;       // GRU: br [3H]
+  const void* Wx;       // LN(x.W) [T,N,G*H] (LSTM: aliases v)
+  const void* gamma_Rh; // [G*H]
   const void* gamma_h;  // [H]
   const void* beta_h;   // [H]
-  void* v;              // act_Wx_norm [T,N,4H]: LN1(x.W) in, gate activations out
-  void* act_Rh;         // [T,N,4H] pre-norm h.R (saved)
+  void* v;              // LSTM: act_Wx_norm [T,N,4H], LN(x.W) in, gate activations out
+                        // GRU: cache [T,N,4H] = (z, r, g, LN(h.R)_g + br_g), may be null in inference
+  void* act_Rh;         // [T,N,G*H] pre-norm h.R (saved)
   void* cache_Rh;       // [T,N,2]
   void* act_c_norm;     // [T,N,H]
   void* cache_c;        // [T,N,2]
@@ -53,8 +56,12 @@ struct LnBwdParams {
   const void* R;
   const void* gamma_Rh;
   const void* gamma_h;
-  const void* c;          // [T+1,N,H]
-  void* v;                // act_Wx_norm: gate activations in, gate gradients out
+  const void* c;          // LSTM [T+1,N,H]
+  const void* h;          // GRU [T+1,N,H]
+  void* dp;               // GRU out [T,N,3H]: gradient w.r.t. LN(x.W)+bx
+  void* dq;               // GRU out [T,N,3H]: gradient w.r.t. LN(h.R)+br
+  void* v;                // LSTM: act_Wx_norm, gate activations in, gate gradients out.
+                          // GRU: cache [T,N,4H] in (untouched)
   void* act_Rh;           // pre-norm h.R in, d(h.R) out
   const void* cache_Rh;
   void* act_c_norm;       // LN(c') in (left untouched)
@@ -191,9 +198,9 @@ __device__ __forceinline__ void chan_combine(const float (&m)[4], const float (&
 // ---------------------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------------------
-template <int KSW, int SPLIT, int MTMAX, typename T>
+template <int G, int KSW, int SPLIT, int MTMAX, typename T>
 __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p) {
-  constexpr int G = 4;
+  static_assert(G == 4 || G == 3, "G = 4: LayerNormLSTM, G = 3: LayerNormGRU");
   constexpr int COLS = G * U;
   constexpr int NT = COLS / 8;
   constexpr int KW = KSW * 16;
@@ -269,21 +276,24 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
   T* cache1 = reinterpret_cast<T*>(p.cache_Rh);
   T* cache3 = reinterpret_cast<T*>(p.cache_c);
   const T* mask = reinterpret_cast<const T*>(p.mask);
-  float bias[G], g1[G];
+  const T* wx = reinterpret_cast<const T*>(p.Wx);
+  float bias[G], bias2[G], g1[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     bias[g] = unit_ok ? ld(reinterpret_cast<const T*>(p.b) + g * H + u0 + ul) : 0.f;
+    bias2[g] = (G == 3 && unit_ok) ? ld(reinterpret_cast<const T*>(p.b2) + g * H + u0 + ul) : 0.f;
     g1[g] = unit_ok ? ld(reinterpret_cast<const T*>(p.gamma_Rh) + g * H + u0 + ul) : 0.f;
   }
-  const float gh = unit_ok ? ld(reinterpret_cast<const T*>(p.gamma_h) + u0 + ul) : 0.f;
-  const float bh = unit_ok ? ld(reinterpret_cast<const T*>(p.beta_h) + u0 + ul) : 0.f;
+  const float gh = (G == 4 && unit_ok) ? ld(reinterpret_cast<const T*>(p.gamma_h) + u0 + ul) : 0.f;
+  const float bh = (G == 4 && unit_ok) ? ld(reinterpret_cast<const T*>(p.beta_h) + u0 + ul) : 0.f;
   float c_reg[MTMAX], h_reg[MTMAX];
+  (void)gh; (void)bh; (void)cbuf; (void)cnbuf; (void)cache3; (void)cnt_units;
 #pragma unroll
   for (int mt = 0; mt < MTMAX; ++mt) {
     const int n = n0 + mt * 16 + nl;
     const bool ok = mt < p.MT && n < N && unit_ok;
     h_reg[mt] = ok ? ld(hbuf + (long long)n * H + u0 + ul) : 0.f;
-    c_reg[mt] = ok ? ld(cbuf + (long long)n * H + u0 + ul) : 0.f;
+    c_reg[mt] = (G == 4 && ok) ? ld(cbuf + (long long)n * H + u0 + ul) : 0.f;
   }
 
   __syncthreads();
@@ -303,7 +313,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
       const bool ok = mt < p.MT && n < N && unit_ok;
 #pragma unroll
       for (int g = 0; g < G; ++g)
-        wxr[mt][g] = ok ? ld(vbuf + ((long long)t * N + n) * GH + g * H + u0 + ul) : 0.f;
+        wxr[mt][g] = ok ? ld(wx + ((long long)t * N + n) * GH + g * H + u0 + ul) : 0.f;
       mk[mt] = (ok && p.has_zoneout && p.training)
                    ? ld(mask + (long long)t * NH + (long long)n * H + u0 + ul) : 0.f;
     }
@@ -439,9 +449,14 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
         stop = __syncthreads_or(*reinterpret_cast<volatile int*>(&s_abort)) != 0;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) {
-          const float4 f =
-              *reinterpret_cast<const float4*>(pb + ((size_t)w * 16 + nl) * PROW + ul * G);
-          rh[mt][0] += f.x; rh[mt][1] += f.y; rh[mt][2] += f.z; rh[mt][3] += f.w;
+          const float* src = pb + ((size_t)w * 16 + nl) * PROW + ul * G;
+          if (G == 4) {
+            const float4 f = *reinterpret_cast<const float4*>(src);
+            rh[mt][0] += f.x; rh[mt][1] += f.y; rh[mt][2] += f.z; rh[mt][G - 1] += f.w;
+          } else {
+#pragma unroll
+            for (int g = 0; g < G; ++g) rh[mt][g] += src[g];
+          }
         }
         pbuf ^= 1;
         const int n = n0 + mt * 16 + nl;
@@ -451,7 +466,11 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
 #pragma unroll
           for (int g = 0; g < G; ++g) st(rt + g * H, rh[mt][g]);
         }
-        const float s = ok ? (rh[mt][0] + rh[mt][1]) + (rh[mt][2] + rh[mt][3]) : 0.f;
+        float s = 0.f;
+        if (ok) {
+#pragma unroll
+          for (int g = 0; g < G; ++g) s += rh[mt][g];
+        }
         const float m_loc = row16_sum(s) / (G * cnt_units);
         float dd = 0.f;
         if (ok) {
@@ -464,77 +483,120 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
     }
     if (stop) break;
 
-    // ---- stage B: LayerNorm of h.R, gates, new cell state, its row statistics published
-    float og[MTMAX], cnew[MTMAX];
-#pragma unroll
-    for (int mt = 0; mt < MTMAX; ++mt) {
-      og[mt] = cnew[mt] = 0.f;
-      if (mt < p.MT) {
-        const int n = n0 + mt * 16 + nl;
-        const bool ok = n < N && unit_ok;
-        float sa[4], sb[4], mean1, inv1;
-        if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 27))
-          *reinterpret_cast<volatile int*>(&s_abort) = 1;
-        chan_combine(sa, sb, ul, p.nHS, GH, COLS, mean1, inv1);
-        float pre[G];
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-          pre[g] = (rh[mt][g] - mean1) * inv1 * g1[g] + wxr[mt][g] + bias[g];
-        const float i = sigmoid_fast(pre[0]);
-        const float gg = tanh_fast(pre[1]);
-        const float f = sigmoid_fast(pre[2]);
-        const float o = sigmoid_fast(pre[3]);
-        const float c_new = f * c_reg[mt] + i * gg;
-        og[mt] = o;
-        cnew[mt] = c_new;
-        const float s = row16_sum(ok ? c_new : 0.f);
-        const float m_loc = s / cnt_units;
-        const float dd = row16_sum(ok ? (c_new - m_loc) * (c_new - m_loc) : 0.f);
-        if (ul == 0 && n < N) stat_publish(area3, mt * 16 + nl, hs, p.nHS, tag, m_loc, dd);
-        if (ok) {
-          st(cbuf + (long long)(t + 1) * NH + (long long)n * H + u0 + ul, c_new);
-          if (p.training) {
-            T* vt = vbuf + ((long long)t * N + n) * GH + u0 + ul;
-            st(vt, i); st(vt + H, gg); st(vt + 2 * H, f); st(vt + 3 * H, o);
+    if constexpr (G == 4) {
+      // ---- stage B: LayerNorm of h.R, gates, new cell state, its row statistics published
+      float og[MTMAX], cnew[MTMAX];
+  #pragma unroll
+      for (int mt = 0; mt < MTMAX; ++mt) {
+        og[mt] = cnew[mt] = 0.f;
+        if (mt < p.MT) {
+          const int n = n0 + mt * 16 + nl;
+          const bool ok = n < N && unit_ok;
+          float sa[4], sb[4], mean1, inv1;
+          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 27))
+            *reinterpret_cast<volatile int*>(&s_abort) = 1;
+          chan_combine(sa, sb, ul, p.nHS, GH, COLS, mean1, inv1);
+          float pre[G];
+  #pragma unroll
+          for (int g = 0; g < G; ++g)
+            pre[g] = (rh[mt][g] - mean1) * inv1 * g1[g] + wxr[mt][g] + bias[g];
+          const float i = sigmoid_fast(pre[0]);
+          const float gg = tanh_fast(pre[1]);
+          const float f = sigmoid_fast(pre[2]);
+          const float o = sigmoid_fast(pre[G - 1]);
+          const float c_new = f * c_reg[mt] + i * gg;
+          og[mt] = o;
+          cnew[mt] = c_new;
+          const float s = row16_sum(ok ? c_new : 0.f);
+          const float m_loc = s / cnt_units;
+          const float dd = row16_sum(ok ? (c_new - m_loc) * (c_new - m_loc) : 0.f);
+          if (ul == 0 && n < N) stat_publish(area3, mt * 16 + nl, hs, p.nHS, tag, m_loc, dd);
+          if (ok) {
+            st(cbuf + (long long)(t + 1) * NH + (long long)n * H + u0 + ul, c_new);
+            if (p.training) {
+              T* vt = vbuf + ((long long)t * N + n) * GH + u0 + ul;
+              st(vt, i); st(vt + H, gg); st(vt + 2 * H, f); st(vt + 3 * H, o);
+            }
+          }
+          if (hs == 0 && ul == 0 && n < N) {
+            st(cache1 + ((long long)t * N + n) * 2, mean1);
+            st(cache1 + ((long long)t * N + n) * 2 + 1, inv1);
           }
         }
-        if (hs == 0 && ul == 0 && n < N) {
-          st(cache1 + ((long long)t * N + n) * 2, mean1);
-          st(cache1 + ((long long)t * N + n) * 2 + 1, inv1);
+      }
+
+      // ---- stage C: LayerNorm of the cell state, output, h_t published
+  #pragma unroll
+      for (int mt = 0; mt < MTMAX; ++mt) {
+        if (mt < p.MT) {
+          const int n = n0 + mt * 16 + nl;
+          const bool ok = n < N && unit_ok;
+          float sa[4], sb[4], mean3, inv3;
+          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 28))
+            *reinterpret_cast<volatile int*>(&s_abort) = 1;
+          chan_combine(sa, sb, ul, p.nHS, H, U, mean3, inv3);
+          const float c_norm = (cnew[mt] - mean3) * inv3 * gh + bh;
+          float h_new = og[mt] * tanh_fast(c_norm);
+          if (p.has_zoneout)
+            h_new = p.training ? zoneout<true>(h_new, h_reg[mt], p.zoneout_prob, mk[mt])
+                               : zoneout<false>(h_new, h_reg[mt], p.zoneout_prob, mk[mt]);
+          if (is_bf16<T>::value) h_new = __bfloat162float(__float2bfloat16_rn(h_new));
+          uint32_t* xdst = p.xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul;
+          if (ok) {
+            if (t + 1 < p.T) __stcg(xdst, hword_encode<SPLIT>(h_new, tag));
+            const long long o0 = (long long)n * H + u0 + ul;
+            st(hbuf + (long long)(t + 1) * NH + o0, h_new);
+            st(cnbuf + (long long)t * NH + o0, c_norm);
+            h_reg[mt] = h_new;
+            c_reg[mt] = cnew[mt];
+          } else if (n < N && unit_pad && t + 1 < p.T) {
+            __stcg(xdst, hword_encode<SPLIT>(0.0f, tag));
+          }
+          if (hs == 0 && ul == 0 && n < N) {
+            st(cache3 + ((long long)t * N + n) * 2, mean3);
+            st(cache3 + ((long long)t * N + n) * 2 + 1, inv3);
+          }
         }
       }
-    }
-
-    // ---- stage C: LayerNorm of the cell state, output, h_t published
-#pragma unroll
-    for (int mt = 0; mt < MTMAX; ++mt) {
-      if (mt < p.MT) {
-        const int n = n0 + mt * 16 + nl;
-        const bool ok = n < N && unit_ok;
-        float sa[4], sb[4], mean3, inv3;
-        if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 28))
-          *reinterpret_cast<volatile int*>(&s_abort) = 1;
-        chan_combine(sa, sb, ul, p.nHS, H, U, mean3, inv3);
-        const float c_norm = (cnew[mt] - mean3) * inv3 * gh + bh;
-        float h_new = og[mt] * tanh_fast(c_norm);
-        if (p.has_zoneout)
-          h_new = p.training ? zoneout<true>(h_new, h_reg[mt], p.zoneout_prob, mk[mt])
-                             : zoneout<false>(h_new, h_reg[mt], p.zoneout_prob, mk[mt]);
-        if (is_bf16<T>::value) h_new = __bfloat162float(__float2bfloat16_rn(h_new));
-        uint32_t* xdst = p.xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul;
-        if (ok) {
-          if (t + 1 < p.T) __stcg(xdst, hword_encode<SPLIT>(h_new, tag));
-          const long long o0 = (long long)n * H + u0 + ul;
-          st(hbuf + (long long)(t + 1) * NH + o0, h_new);
-          st(cnbuf + (long long)t * NH + o0, c_norm);
-          h_reg[mt] = h_new;
-          c_reg[mt] = cnew[mt];
-        } else if (n < N && unit_pad && t + 1 < p.T) {
-          __stcg(xdst, hword_encode<SPLIT>(0.0f, tag));
-        }
-        if (hs == 0 && ul == 0 && n < N) {
-          st(cache3 + ((long long)t * N + n) * 2, mean3);
-          st(cache3 + ((long long)t * N + n) * 2 + 1, inv3);
+    } else {
+      // ---- stage B: LayerNorm of h.R, gates, output, h_t published
+  #pragma unroll
+      for (int mt = 0; mt < MTMAX; ++mt) {
+        if (mt < p.MT) {
+          const int n = n0 + mt * 16 + nl;
+          const bool ok = n < N && unit_ok;
+          float sa[4], sb[4], mean1, inv1;
+          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 27))
+            *reinterpret_cast<volatile int*>(&s_abort) = 1;
+          chan_combine(sa, sb, ul, p.nHS, GH, COLS, mean1, inv1);
+          float rn[G];
+  #pragma unroll
+          for (int g = 0; g < G; ++g) rn[g] = (rh[mt][g] - mean1) * inv1 * g1[g] + bias2[g];
+          const float z = sigmoid_fast(wxr[mt][0] + bias[0] + rn[0]);
+          const float r = sigmoid_fast(wxr[mt][1] + bias[1] + rn[1]);
+          const float qg = rn[2];
+          const float gg = tanh_fast(wxr[mt][2] + bias[2] + r * qg);
+          float h_new = z * h_reg[mt] + (1.0f - z) * gg;
+          if (p.has_zoneout)
+            h_new = p.training ? zoneout<true>(h_new, h_reg[mt], p.zoneout_prob, mk[mt])
+                               : zoneout<false>(h_new, h_reg[mt], p.zoneout_prob, mk[mt]);
+          if (is_bf16<T>::value) h_new = __bfloat162float(__float2bfloat16_rn(h_new));
+          uint32_t* xdst = p.xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul;
+          if (ok) {
+            if (t + 1 < p.T) __stcg(xdst, hword_encode<SPLIT>(h_new, tag));
+            st(hbuf + (long long)(t + 1) * NH + (long long)n * H + u0 + ul, h_new);
+            if (p.training && vbuf) {
+              T* vt = vbuf + ((long long)t * N + n) * 4 * H + u0 + ul;
+              st(vt, z); st(vt + H, r); st(vt + 2 * H, gg); st(vt + 3 * H, qg);
+            }
+            h_reg[mt] = h_new;
+          } else if (n < N && unit_pad && t + 1 < p.T) {
+            __stcg(xdst, hword_encode<SPLIT>(0.0f, tag));
+          }
+          if (hs == 0 && ul == 0 && n < N) {
+            st(cache1 + ((long long)t * N + n) * 2, mean1);
+            st(cache1 + ((long long)t * N + n) * 2 + 1, inv1);
+          }
         }
       }
     }
@@ -544,11 +606,11 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
 // ---------------------------------------------------------------------------------------
 // Backward
 // ---------------------------------------------------------------------------------------
-template <int NTW, int SPLIT, int MTMAX, typename T>
+template <int G, int NTW, int SPLIT, int MTMAX, typename T>
 __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p) {
-  constexpr int G = 4;
+  static_assert(G == 4 || G == 3, "G = 4: LayerNormLSTM, G = 3: LayerNormGRU");
   constexpr int COLS = G * U;
-  constexpr int KS = COLS / 16;
+  constexpr int KS = COLS / 16;  // 64 or 48 gate columns: no padding
   constexpr int AROW = COLS + 8;
   extern __shared__ __align__(16) uint8_t smem[];
   const int BNR = p.MT * 16;
@@ -612,6 +674,9 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
   const int nl = tid >> 4, ul = tid & 15;
   const bool unit_ok = (u0 + ul) < H;
   const T* cbuf = reinterpret_cast<const T*>(p.c);
+  const T* hbuf = reinterpret_cast<const T*>(p.h);
+  T* dpb = reinterpret_cast<T*>(p.dp);
+  T* dqb = reinterpret_cast<T*>(p.dq);
   T* vbuf = reinterpret_cast<T*>(p.v);
   T* rhbuf = reinterpret_cast<T*>(p.act_Rh);
   const T* cnbuf = reinterpret_cast<const T*>(p.act_c_norm);
@@ -624,7 +689,8 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
 #pragma unroll
   for (int g = 0; g < G; ++g)
     g1[g] = unit_ok ? ld(reinterpret_cast<const T*>(p.gamma_Rh) + g * H + u0 + ul) : 0.f;
-  const float gh = unit_ok ? ld(reinterpret_cast<const T*>(p.gamma_h) + u0 + ul) : 0.f;
+  const float gh = (G == 4 && unit_ok) ? ld(reinterpret_cast<const T*>(p.gamma_h) + u0 + ul) : 0.f;
+  (void)gh; (void)cbuf; (void)hbuf; (void)dpb; (void)dqb; (void)cnbuf; (void)cache3; (void)dcn;
   const float inv_H = 1.0f / (float)H, inv_GH = 1.0f / (float)GH;
 
   float dh_c[MTMAX], dc_c[MTMAX];
@@ -633,9 +699,11 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
     const int n = n0 + mt * 16 + nl;
     const bool ok = mt < p.MT && n < N && unit_ok;
     dh_c[mt] = ok ? p.dh_carry[(long long)n * H + u0 + ul] : 0.f;
-    dc_c[mt] = ok ? p.dc_carry[(long long)n * H + u0 + ul] : 0.f;
+    dc_c[mt] = (G == 4 && ok) ? p.dc_carry[(long long)n * H + u0 + ul] : 0.f;
   }
-  float acc_g1[G] = {0.f, 0.f, 0.f, 0.f}, acc_gh = 0.f, acc_bh = 0.f;  // parameter gradients
+  float acc_g1[G], acc_gh = 0.f, acc_bh = 0.f;  // parameter gradients
+#pragma unroll
+  for (int g = 0; g < G; ++g) acc_g1[g] = 0.f;
   const size_t blk = (size_t)BNR * U;
   const size_t sarea = (size_t)BNR * p.nHS * 2;
   bool alive = true;
@@ -647,8 +715,9 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
     uint32_t* area3 = p.sbuf + (((size_t)0 * 2 + (ti & 1)) * nBS + bs) * sarea;
     uint32_t* area1 = p.sbuf + (((size_t)1 * 2 + (ti & 1)) * nBS + bs) * sarea;
     // ---- loads independent of the carried gradient
-    float gv[MTMAX][G], rhv[MTMAX][G], cprev[MTMAX], cx3[MTMAX], cnv[MTMAX], dhv[MTMAX],
-        dcv[MTMAX], mk[MTMAX], mean1[MTMAX], inv1[MTMAX], inv3[MTMAX];
+    // gv: saved activations (LSTM i,g,f,o; GRU z,r,g,q); rhv: pre-norm h.R
+    float gv[MTMAX][4], rhv[MTMAX][G], cprev[MTMAX], cx3[MTMAX], cnv[MTMAX], dhv[MTMAX],
+        dcv[MTMAX], mk[MTMAX], mean1[MTMAX], inv1[MTMAX], inv3[MTMAX], hprev[MTMAX];
 #pragma unroll
     for (int mt = 0; mt < MTMAX; ++mt) {
       const int n = n0 + mt * 16 + nl;
@@ -656,21 +725,26 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
       const bool ok = rok && unit_ok;
       const long long o0 = (long long)n * H + u0 + ul;
       const long long w0 = ((long long)t * N + n) * GH + u0 + ul;
+      const long long v0 = ((long long)t * N + n) * 4 * H + u0 + ul;
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        gv[mt][g] = ok ? ld(vbuf + w0 + g * H) : 0.f;
-        rhv[mt][g] = ok ? ld(rhbuf + w0 + g * H) : 0.f;
-      }
+      for (int g = 0; g < 4; ++g) gv[mt][g] = ok ? ld(vbuf + v0 + g * H) : 0.f;
+#pragma unroll
+      for (int g = 0; g < G; ++g) rhv[mt][g] = ok ? ld(rhbuf + w0 + g * H) : 0.f;
       dhv[mt] = ok ? ld(dhn + (long long)(t + 1) * NH + o0) : 0.f;
-      dcv[mt] = ok ? ld(dcn + (long long)(t + 1) * NH + o0) : 0.f;
       mk[mt] = (ok && p.has_zoneout) ? ld(mask + (long long)t * NH + o0) : 1.f;
-      cprev[mt] = ok ? ld(cbuf + (long long)t * NH + o0) : 0.f;
-      cnv[mt] = ok ? ld(cnbuf + (long long)t * NH + o0) : 0.f;
-      const float mean3 = rok ? ld(cache3 + ((long long)t * N + n) * 2) : 0.f;
-      inv3[mt] = rok ? ld(cache3 + ((long long)t * N + n) * 2 + 1) : 0.f;
-      cx3[mt] = ok ? ld(cbuf + (long long)(t + 1) * NH + o0) - mean3 : 0.f;
       mean1[mt] = rok ? ld(cache1 + ((long long)t * N + n) * 2) : 0.f;
       inv1[mt] = rok ? ld(cache1 + ((long long)t * N + n) * 2 + 1) : 0.f;
+      cprev[mt] = cx3[mt] = cnv[mt] = dcv[mt] = inv3[mt] = hprev[mt] = 0.f;
+      if constexpr (G == 4) {
+        dcv[mt] = ok ? ld(dcn + (long long)(t + 1) * NH + o0) : 0.f;
+        cprev[mt] = ok ? ld(cbuf + (long long)t * NH + o0) : 0.f;
+        cnv[mt] = ok ? ld(cnbuf + (long long)t * NH + o0) : 0.f;
+        const float mean3 = rok ? ld(cache3 + ((long long)t * N + n) * 2) : 0.f;
+        inv3[mt] = rok ? ld(cache3 + ((long long)t * N + n) * 2 + 1) : 0.f;
+        cx3[mt] = ok ? ld(cbuf + (long long)(t + 1) * NH + o0) - mean3 : 0.f;
+      } else {
+        hprev[mt] = ok ? ld(hbuf + (long long)t * NH + o0) : 0.f;
+      }
     }
 
     // ---- recurrent part of dh_t: the partials published at the previous step
@@ -731,89 +805,139 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
     if (!alive) *reinterpret_cast<volatile int*>(&s_abort) = 1;
     alive = true;  // from here on failures only mark s_abort; the barrier below decides
 
-    // ---- stage A: output gate and LayerNorm(c') input gradients; LN(c') row sums published
-    float d_o[MTMAX], db3[MTMAX];
-#pragma unroll
-    for (int mt = 0; mt < MTMAX; ++mt) {
-      d_o[mt] = db3[mt] = 0.f;
-      if (mt < p.MT) {
-        const int n = n0 + mt * 16 + nl;
-        float dh_total = dhv[mt] + dh_c[mt];
-        float keep = 0.f;
-        if (p.has_zoneout) {
-          keep = (1.0f - mk[mt]) * dh_total;
-          dh_total = mk[mt] * dh_total;
-        }
-        dh_c[mt] = keep;
-        const float o = gv[mt][3];
-        const float c_tanh = tanh_fast(cnv[mt]);
-        d_o[mt] = d_sigmoid(o) * (c_tanh * dh_total);
-        const float dcn_ = d_tanh(c_tanh) * (o * dh_total);  // gradient w.r.t. LayerNorm(c')
-        acc_gh += cx3[mt] * inv3[mt] * dcn_;
-        acc_bh += dcn_;
-        db3[mt] = gh * dcn_;
-        const float s1 = row16_sum(cx3[mt] * db3[mt]);
-        const float s2 = row16_sum(db3[mt]);
-        if (ul == 0 && n < N) stat_publish(area3, mt * 16 + nl, hs, p.nHS, tag, s1, s2);
-      }
-    }
-
-    // ---- stage B: gate gradients; LN(h.R) row sums published
     float dgate[MTMAX][G];
-#pragma unroll
-    for (int mt = 0; mt < MTMAX; ++mt) {
-#pragma unroll
-      for (int g = 0; g < G; ++g) dgate[mt][g] = 0.f;
-      if (mt < p.MT) {
-        const int n = n0 + mt * 16 + nl;
-        const bool ok = n < N && unit_ok;
-        float sa[4], sb[4];
-        if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 38))
-          *reinterpret_cast<volatile int*>(&s_abort) = 1;
-        const float S1 = row16_sum((sa[0] + sa[1]) + (sa[2] + sa[3]));
-        const float S2 = row16_sum((sb[0] + sb[1]) + (sb[2] + sb[3]));
-        const float r = inv3[mt];
-        const float dsigma = -0.5f * S1 * r * r * r;
-        const float dmu = -S2 * r;
-        const float dcl = 2.0f * cx3[mt] * dsigma * inv_H + r * db3[mt] + dmu * inv_H;
-        const float i = gv[mt][0], gg = gv[mt][1], f = gv[mt][2];
-        const float dc_total = ok ? dcv[mt] + dc_c[mt] + dcl : 0.f;
-        dgate[mt][0] = d_sigmoid(i) * (gg * dc_total);
-        dgate[mt][1] = d_tanh(gg) * (i * dc_total);
-        dgate[mt][2] = d_sigmoid(f) * (cprev[mt] * dc_total);
-        dgate[mt][3] = d_o[mt];
-        dc_c[mt] = f * dc_total;
-        float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float cx = rhv[mt][g] - mean1[mt];
-          const float db = g1[g] * dgate[mt][g];
-          if (ok) {
-            s1 += cx * db;
-            s2 += db;
-            acc_g1[g] += cx * inv1[mt] * dgate[mt][g];
+    if constexpr (G == 4) {
+      // ---- stage A: output gate and LayerNorm(c') input gradients; LN(c') row sums published
+      float d_o[MTMAX], db3[MTMAX];
+  #pragma unroll
+      for (int mt = 0; mt < MTMAX; ++mt) {
+        d_o[mt] = db3[mt] = 0.f;
+        if (mt < p.MT) {
+          const int n = n0 + mt * 16 + nl;
+          float dh_total = dhv[mt] + dh_c[mt];
+          float keep = 0.f;
+          if (p.has_zoneout) {
+            keep = (1.0f - mk[mt]) * dh_total;
+            dh_total = mk[mt] * dh_total;
           }
+          dh_c[mt] = keep;
+          const float o = gv[mt][3];
+          const float c_tanh = tanh_fast(cnv[mt]);
+          d_o[mt] = d_sigmoid(o) * (c_tanh * dh_total);
+          const float dcn_ = d_tanh(c_tanh) * (o * dh_total);  // gradient w.r.t. LayerNorm(c')
+          acc_gh += cx3[mt] * inv3[mt] * dcn_;
+          acc_bh += dcn_;
+          db3[mt] = gh * dcn_;
+          const float s1 = row16_sum(cx3[mt] * db3[mt]);
+          const float s2 = row16_sum(db3[mt]);
+          if (ul == 0 && n < N) stat_publish(area3, mt * 16 + nl, hs, p.nHS, tag, s1, s2);
         }
-        s1 = row16_sum(s1);
-        s2 = row16_sum(s2);
-        if (ul == 0 && n < N) stat_publish(area1, mt * 16 + nl, hs, p.nHS, tag, s1, s2);
-        if (ok) {
-          const long long w0 = ((long long)t * N + n) * GH + u0 + ul;
-#pragma unroll
-          for (int g = 0; g < G; ++g) st(vbuf + w0 + g * H, dgate[mt][g]);
-          if (SPLIT == 2 && p.gpl) {
-#pragma unroll
-            for (int g = 0; g < G; ++g) {
-              float hi, lo;
-              split_bf16(dgate[mt][g], hi, lo);
-              p.gpl[w0 + g * H] = __float2bfloat16_rn(hi);
-              p.gpl[p.gpl_stride + w0 + g * H] = __float2bfloat16_rn(lo);
+      }
+
+      // ---- stage B: gate gradients; LN(h.R) row sums published
+  #pragma unroll
+      for (int mt = 0; mt < MTMAX; ++mt) {
+  #pragma unroll
+        for (int g = 0; g < G; ++g) dgate[mt][g] = 0.f;
+        if (mt < p.MT) {
+          const int n = n0 + mt * 16 + nl;
+          const bool ok = n < N && unit_ok;
+          float sa[4], sb[4];
+          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 38))
+            *reinterpret_cast<volatile int*>(&s_abort) = 1;
+          const float S1 = row16_sum((sa[0] + sa[1]) + (sa[2] + sa[3]));
+          const float S2 = row16_sum((sb[0] + sb[1]) + (sb[2] + sb[3]));
+          const float r = inv3[mt];
+          const float dsigma = -0.5f * S1 * r * r * r;
+          const float dmu = -S2 * r;
+          const float dcl = 2.0f * cx3[mt] * dsigma * inv_H + r * db3[mt] + dmu * inv_H;
+          const float i = gv[mt][0], gg = gv[mt][1], f = gv[mt][2];
+          const float dc_total = ok ? dcv[mt] + dc_c[mt] + dcl : 0.f;
+          dgate[mt][0] = d_sigmoid(i) * (gg * dc_total);
+          dgate[mt][1] = d_tanh(gg) * (i * dc_total);
+          dgate[mt][2] = d_sigmoid(f) * (cprev[mt] * dc_total);
+          dgate[mt][G - 1] = d_o[mt];
+          dc_c[mt] = f * dc_total;
+          float s1 = 0.f, s2 = 0.f;
+  #pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float cx = rhv[mt][g] - mean1[mt];
+            const float db = g1[g] * dgate[mt][g];
+            if (ok) {
+              s1 += cx * db;
+              s2 += db;
+              acc_g1[g] += cx * inv1[mt] * dgate[mt][g];
+            }
+          }
+          s1 = row16_sum(s1);
+          s2 = row16_sum(s2);
+          if (ul == 0 && n < N) stat_publish(area1, mt * 16 + nl, hs, p.nHS, tag, s1, s2);
+          if (ok) {
+            const long long w0 = ((long long)t * N + n) * GH + u0 + ul;
+  #pragma unroll
+            for (int g = 0; g < G; ++g) st(vbuf + w0 + g * H, dgate[mt][g]);
+            if (SPLIT == 2 && p.gpl) {
+  #pragma unroll
+              for (int g = 0; g < G; ++g) {
+                float hi, lo;
+                split_bf16(dgate[mt][g], hi, lo);
+                p.gpl[w0 + g * H] = __float2bfloat16_rn(hi);
+                p.gpl[p.gpl_stride + w0 + g * H] = __float2bfloat16_rn(lo);
+              }
             }
           }
         }
       }
-    }
 
+    } else {
+      // ---- stage A: gate gradients (dp: w.r.t. LN(x.W)+bx, dq: w.r.t. LN(h.R)+br); LN(h.R)
+      // row sums published
+  #pragma unroll
+      for (int mt = 0; mt < MTMAX; ++mt) {
+  #pragma unroll
+        for (int g = 0; g < G; ++g) dgate[mt][g] = 0.f;
+        if (mt < p.MT) {
+          const int n = n0 + mt * 16 + nl;
+          const bool ok = n < N && unit_ok;
+          float dh_total = dhv[mt] + dh_c[mt];
+          float keep = 0.f;
+          if (p.has_zoneout) {
+            keep = (1.0f - mk[mt]) * dh_total;
+            dh_total = mk[mt] * dh_total;
+          }
+          const float z = gv[mt][0], r = gv[mt][1], gg = gv[mt][2], qg = gv[mt][3];
+          const float dg = (1.0f - z) * dh_total;
+          const float dz = (hprev[mt] - gg) * dh_total;
+          const float dp_g = d_tanh(gg) * dg;
+          const float dp_r = d_sigmoid(r) * (dp_g * qg);
+          const float dp_z = d_sigmoid(z) * dz;
+          dgate[mt][0] = dp_z;
+          dgate[mt][1] = dp_r;
+          dgate[mt][2] = dp_g * r;
+          dh_c[mt] = keep + z * dh_total;
+          float s1 = 0.f, s2 = 0.f;
+  #pragma unroll
+          for (int g = 0; g < G; ++g) {
+            const float cx = rhv[mt][g] - mean1[mt];
+            const float db = g1[g] * dgate[mt][g];
+            if (ok) {
+              s1 += cx * db;
+              s2 += db;
+              acc_g1[g] += cx * inv1[mt] * dgate[mt][g];
+            }
+          }
+          s1 = row16_sum(s1);
+          s2 = row16_sum(s2);
+          if (ul == 0 && n < N) stat_publish(area1, mt * 16 + nl, hs, p.nHS, tag, s1, s2);
+          if (ok) {
+            const long long w0 = ((long long)t * N + n) * GH + u0 + ul;
+            st(dpb + w0, dp_z); st(dpb + w0 + H, dp_r); st(dpb + w0 + 2 * H, dp_g);
+            st(dqb + w0, dp_z); st(dqb + w0 + H, dp_r); st(dqb + w0 + 2 * H, dgate[mt][2]);
+          }
+        }
+      }
+
+    }
     // ---- stage C: gradient w.r.t. the pre-norm h.R -> global and -> smem (A operand)
     __nv_bfloat16* a_hi = a_base + (size_t)(ti & 1) * PA * a_plane;
 #pragma unroll
@@ -906,7 +1030,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
       const int n = n0 + mt * 16 + nl;
       if (mt < p.MT && n < N && unit_ok) {
         p.dh_carry[(long long)n * H + u0 + ul] = dh_c[mt];
-        p.dc_carry[(long long)n * H + u0 + ul] = dc_c[mt];
+        if (G == 4) p.dc_carry[(long long)n * H + u0 + ul] = dc_c[mt];
       }
     }
   }
@@ -914,29 +1038,32 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
     const long long r = (long long)bs * 16 + nl;
 #pragma unroll
     for (int g = 0; g < G; ++g) p.dgRh_part[r * GH + g * H + u0 + ul] = acc_g1[g];
-    p.dgh_part[r * H + u0 + ul] = acc_gh;
-    p.dbh_part[r * H + u0 + ul] = acc_bh;
+    if (G == 4) {
+      p.dgh_part[r * H + u0 + ul] = acc_gh;
+      p.dbh_part[r * H + u0 + ul] = acc_bh;
+    }
   }
 }
 
 // ---------------------------------------------------------------------------------------
 // Host-side dispatch (instantiated one storage type per translation unit)
 // ---------------------------------------------------------------------------------------
-template <int SPLIT, typename T>
+template <int G, int SPLIT, typename T>
 int run_ln_fwd(LnFwdParams& p, const Geometry& g, cudaStream_t s) {
   const int ksw = ceil_div(ceil_div(p.H, 16), WARPS);
   auto smem_for = [&](int KSW) {
     const size_t arow = (size_t)WARPS * KSW * 16 + 8;
     return (size_t)(SPLIT == 2 ? 3 : 1) * 16 * arow * 2 +
-           (size_t)2 * WARPS * 16 * (4 * U + 8) * 4 + (SPLIT == 2 ? (size_t)KSW * 16384 : 0);
+           (size_t)2 * WARPS * 16 * (G * U + 8) * 4 +
+           (SPLIT == 2 ? (size_t)KSW * WARPS * (G * U / 8) * 256 : 0);
   };
   const int grid = g.nHS * g.nBS;
 #define HB_FWD(KSW)                                                                       \
   if (ksw <= KSW) {                                                                       \
     if (smem_for(KSW) > 220 * 1024) return HASTE_B200_ERR_UNSUPPORTED;                    \
     if (g.MT == 1)                                                                        \
-      return launch_coop(ln_fwd_kernel<KSW, SPLIT, 1, T>, grid, smem_for(KSW), &p, s);    \
-    return launch_coop(ln_fwd_kernel<KSW, SPLIT, 4, T>, grid, smem_for(KSW), &p, s);      \
+      return launch_coop(ln_fwd_kernel<G, KSW, SPLIT, 1, T>, grid, smem_for(KSW), &p, s);    \
+    return launch_coop(ln_fwd_kernel<G, KSW, SPLIT, 4, T>, grid, smem_for(KSW), &p, s);      \
   }
   HB_FWD(1)
   HB_FWD(2)
@@ -948,17 +1075,17 @@ int run_ln_fwd(LnFwdParams& p, const Geometry& g, cudaStream_t s) {
 
 inline int ntw_pad(int ntw) { return ntw <= 1 ? 1 : ntw <= 2 ? 2 : ntw <= 4 ? 4 : ntw <= 8 ? 8 : 16; }
 
-template <int SPLIT, typename T>
+template <int G, int SPLIT, typename T>
 int run_ln_bwd(LnBwdParams& p, const Geometry& g, cudaStream_t s) {
   const int ntw = ceil_div(ceil_div(p.H, 8), WARPS);
-  const size_t smem = (size_t)2 * (SPLIT == 2 ? 3 : 1) * g.MT * 16 * (4 * U + 8) * 2 +
-                      (SPLIT == 2 ? (size_t)ntw_pad(ntw) * 8192 : 0);  // + third plane of R^T
+  const size_t smem = (size_t)2 * (SPLIT == 2 ? 3 : 1) * g.MT * 16 * (G * U + 8) * 2 +
+                      (SPLIT == 2 ? (size_t)ntw_pad(ntw) * WARPS * (G * U / 16) * 256 : 0);  // + third plane of R^T
   const int grid = g.nHS * g.nBS;
 #define HB_BWD(NTW)                                                                \
   if (ntw <= NTW) {                                                                \
     if (g.MT == 1)                                                                 \
-      return launch_coop(ln_bwd_kernel<NTW, SPLIT, 1, T>, grid, smem, &p, s);      \
-    return launch_coop(ln_bwd_kernel<NTW, SPLIT, 4, T>, grid, smem, &p, s);        \
+      return launch_coop(ln_bwd_kernel<G, NTW, SPLIT, 1, T>, grid, smem, &p, s);      \
+    return launch_coop(ln_bwd_kernel<G, NTW, SPLIT, 4, T>, grid, smem, &p, s);        \
   }
   HB_BWD(1)
   HB_BWD(2)
@@ -973,6 +1100,10 @@ int run_ln_fwd_f32(LnFwdParams& p, const Geometry& g, cudaStream_t s);
 int run_ln_fwd_bf16(LnFwdParams& p, const Geometry& g, cudaStream_t s);
 int run_ln_bwd_f32(LnBwdParams& p, const Geometry& g, cudaStream_t s);
 int run_ln_bwd_bf16(LnBwdParams& p, const Geometry& g, cudaStream_t s);
+int run_lngru_fwd_f32(LnFwdParams& p, const Geometry& g, cudaStream_t s);
+int run_lngru_fwd_bf16(LnFwdParams& p, const Geometry& g, cudaStream_t s);
+int run_lngru_bwd_f32(LnBwdParams& p, const Geometry& g, cudaStream_t s);
+int run_lngru_bwd_bf16(LnBwdParams& p, const Geometry& g, cudaStream_t s);
 
 }  // namespace rec
 }  // namespace hb

@@ -112,7 +112,7 @@ REC_SHAPES = [(12, 40, 32, 80), (20, 64, 64, 512), (6, 130, 48, 512), (9, 3, 16,
 
 @pytest.mark.parametrize("path", ["stepwise", "persistent"])
 @pytest.mark.parametrize("shape", REC_SHAPES, ids=lambda s: "T%d_N%d_C%d_H%d" % s)
-@pytest.mark.parametrize("cell", ["lstm", "gru", "layer_norm_lstm"])
+@pytest.mark.parametrize("cell", ["lstm", "gru", "layer_norm_lstm", "layer_norm_gru"])
 def test_both_recurrence_paths_fp32(cell, shape, path):
     from haste_b200 import _C
     T, N, C, H = shape
@@ -136,7 +136,7 @@ def test_both_recurrence_paths_fp32(cell, shape, path):
 
 @pytest.mark.parametrize("shape", [(20, 64, 64, 512), (8, 128, 64, 1024)],
                          ids=lambda s: "T%d_N%d_C%d_H%d" % s)
-@pytest.mark.parametrize("cell", ["lstm", "gru", "layer_norm_lstm"])
+@pytest.mark.parametrize("cell", ["lstm", "gru", "layer_norm_lstm", "layer_norm_gru"])
 def test_persistent_path_bf16(cell, shape):
     from haste_b200 import _C
     T, N, C, H = shape
