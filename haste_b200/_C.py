@@ -19,6 +19,10 @@ _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlo
 SIGNATURES = {
     "haste_b200_lstm_forward": [_i] * 6 + [_p] * 8 + [_f, _p, _p],
     "haste_b200_lstm_backward": [_i] * 6 + [_p] * 17,
+    "haste_b200_lstm_forward_iterate": [_i] * 5 + [_p] * 10 + [_f, _p, _p],
+    "haste_b200_lstm_backward_iterate": [_i] * 5 + [_p] * 18,
+    "haste_b200_gru_forward_iterate": [_i] * 5 + [_p] * 10 + [_f, _p, _p],
+    "haste_b200_gru_backward_iterate": [_i] * 5 + [_p] * 18,
     "haste_b200_gru_forward": [_i] * 6 + [_p] * 9 + [_f, _p, _p],
     "haste_b200_gru_backward": [_i] * 6 + [_p] * 18,
     "haste_b200_indrnn_forward": [_i] * 6 + [_p] * 6 + [_f, _p, _p],

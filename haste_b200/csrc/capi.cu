@@ -72,6 +72,51 @@ int haste_b200_lstm_backward(int dtype, int transposed_inputs, int T, int N, int
   return lstm_backward(a, (cudaStream_t)stream);
 }
 
+int haste_b200_lstm_forward_iterate(int dtype, int training, int N, int C, int H, const void* W,
+                                    const void* R, const void* b, const void* x, const void* h,
+                                    const void* c, void* h_out, void* c_out, void* v,
+                                    void* tmp_Rh, float zoneout_prob, const void* zoneout_mask,
+                                    void* stream) {
+  HB_REQUIRE(h_out && c_out, "h_out/c_out is null");
+  LstmFwd a{dtype, training, 1, N, C, H, W, R, b, x, const_cast<void*>(h), const_cast<void*>(c),
+            v, tmp_Rh, zoneout_prob, zoneout_mask, h_out, c_out};
+  return lstm_forward(a, (cudaStream_t)stream);
+}
+
+int haste_b200_lstm_backward_iterate(int dtype, int transposed_inputs, int N, int C, int H,
+                                     const void* W, const void* R, const void* b, const void* x,
+                                     const void* h, const void* c, const void* c_new,
+                                     const void* dh_new, const void* dc_new, void* dx, void* dW,
+                                     void* dR, void* db, void* dh, void* dc, void* v,
+                                     const void* zoneout_mask, void* stream) {
+  HB_REQUIRE(c_new, "c_new is null");
+  LstmBwd a{dtype, transposed_inputs, 1, N, C, H, W, R, b, x, h, c, dh_new, dc_new,
+            dx, dW, dR, db, dh, dc, v, zoneout_mask, 1, c_new};
+  return lstm_backward(a, (cudaStream_t)stream);
+}
+
+int haste_b200_gru_forward_iterate(int dtype, int training, int N, int C, int H, const void* W,
+                                   const void* R, const void* bx, const void* br, const void* x,
+                                   const void* h, void* h_out, void* v, void* tmp_Wx,
+                                   void* tmp_Rh, float zoneout_prob, const void* zoneout_mask,
+                                   void* stream) {
+  HB_REQUIRE(h_out, "h_out is null");
+  GruFwd a{dtype, training, 1, N, C, H, W, R, bx, br, x, const_cast<void*>(h), v, tmp_Wx, tmp_Rh,
+           zoneout_prob, zoneout_mask, h_out};
+  return gru_forward(a, (cudaStream_t)stream);
+}
+
+int haste_b200_gru_backward_iterate(int dtype, int transposed_inputs, int N, int C, int H,
+                                    const void* W, const void* R, const void* bx, const void* br,
+                                    const void* x, const void* h, const void* v,
+                                    const void* dh_new, void* dx, void* dW, void* dR, void* dbx,
+                                    void* dbr, void* dh, void* dp, void* dq,
+                                    const void* zoneout_mask, void* stream) {
+  GruBwd a{dtype, transposed_inputs, 1, N, C, H, W, R, bx, br, x, h, v, dh_new,
+           dx, dW, dR, dbx, dbr, dh, dp, dq, zoneout_mask, 1};
+  return gru_backward(a, (cudaStream_t)stream);
+}
+
 int haste_b200_gru_forward(int dtype, int training, int T, int N, int C, int H, const void* W,
                            const void* R, const void* bx, const void* br, const void* x, void* h,
                            void* v, void* tmp_Wx, void* tmp_Rh, float zoneout_prob,

@@ -14,12 +14,19 @@ struct LstmFwd {
   void *h, *c, *v, *tmp_Rh;
   float zoneout_prob;
   const void* zoneout_mask;
+  // Single-step form (T == 1, the reference's Iterate): new state goes to separate [N,H]
+  // buffers instead of slot 1 of h / c.
+  void *h_out = nullptr, *c_out = nullptr;
 };
 struct LstmBwd {
   int dtype, transposed_inputs, T, N, C, H;
   const void *W, *R, *b, *x, *h, *c, *dh_new, *dc_new;
   void *dx, *dW, *dR, *db, *dh, *dc, *v;
   const void* zoneout_mask;
+  // Single-step form (T == 1): h, c, dh_new, dc_new are the step's own [N,H] buffers and
+  // c_new is the cell state the forward step produced.
+  int iterate = 0;
+  const void* c_new = nullptr;
 };
 struct GruFwd {
   int dtype, training, T, N, C, H;
@@ -27,12 +34,14 @@ struct GruFwd {
   void *h, *v, *tmp_Wx, *tmp_Rh;
   float zoneout_prob;
   const void* zoneout_mask;
+  void* h_out = nullptr;  // single-step form (T == 1): new state, [N,H]
 };
 struct GruBwd {
   int dtype, transposed_inputs, T, N, C, H;
   const void *W, *R, *bx, *br, *x, *h, *v, *dh_new;
   void *dx, *dW, *dR, *dbx, *dbr, *dh, *dp, *dq;
   const void* zoneout_mask;
+  int iterate = 0;  // single-step form (T == 1): dh_new is the step's own [N,H] buffer
 };
 struct IndrnnFwd {
   int dtype, training, T, N, C, H;

@@ -339,19 +339,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
             }
           } else if (p.c_is_bf16) {
             __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)m * p.ldc + nb;
-            for (int j = 0; j < 32 && nb + j < p.N; ++j) {
-              float v = __uint_as_float(r[j]);
-              if (p.accumulate) v += __bfloat162float(dst[j]);
-              dst[j] = __float2bfloat16_rn(v);
+            if (nb + 32 <= p.N && (p.ldc & 7) == 0 &&
+                (reinterpret_cast<uintptr_t>(p.c) & 15) == 0) {
+              // 16-byte stores: eight bf16 per store, four per 32-column chunk
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                float v[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+                if (p.accumulate) {
+                  const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
+                  const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    v[2 * e] += __uint_as_float(ow[e] << 16);
+                    v[2 * e + 1] += __uint_as_float(ow[e] & 0xFFFF0000u);
+                  }
+                }
+                uint32_t w[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                  w[e] = *reinterpret_cast<uint32_t*>(&t2);
+                }
+                *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+              }
+            } else {
+              for (int j = 0; j < 32 && nb + j < p.N; ++j) {
+                float v = __uint_as_float(r[j]);
+                if (p.accumulate) v += __bfloat162float(dst[j]);
+                dst[j] = __float2bfloat16_rn(v);
+              }
             }
           } else {
             float* dst = reinterpret_cast<float*>(p.c) + (long long)m * p.ldc + nb;
-            if (nb + 32 <= p.N && (p.ldc & 3) == 0 && !p.accumulate) {
+            if (nb + 32 <= p.N && (p.ldc & 3) == 0 &&
+                (reinterpret_cast<uintptr_t>(p.c) & 15) == 0) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) =
-                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (p.accumulate) {
+                  const float4 c0 = *reinterpret_cast<const float4*>(dst + j);
+                  o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w;
+                }
+                *reinterpret_cast<float4*>(dst + j) = o;
+              }
             } else {
               for (int j = 0; j < 32 && nb + j < p.N; ++j) {
                 float v = __uint_as_float(r[j]);

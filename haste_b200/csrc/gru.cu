@@ -139,7 +139,8 @@ int gru_forward_stepwise(const GruFwd& a, cudaStream_t s) {
     HB_TRY(gemm_small(g, s));
     HB_TRY(gru_launch_pointwise_fwd<T>(a.training != 0, zo, N, H, Wx + t * NH * 3,
                                        (const T*)a.tmp_Rh, (const T*)a.bx, (const T*)a.br,
-                                       h + t * NH, h + (t + 1) * NH, v ? v + t * NH * 4 : nullptr,
+                                       h + t * NH, a.h_out ? (T*)a.h_out : h + (t + 1) * NH,
+                                       v ? v + t * NH * 4 : nullptr,
                                        a.zoneout_prob, zo ? mask + t * NH : nullptr, s));
   }
   return HASTE_B200_OK;
@@ -158,8 +159,8 @@ int gru_backward_stepwise(const GruBwd& a, float* dh_carry, cudaStream_t s) {
   const long long r_cs = a.transposed_inputs ? 1 : 3LL * H;
   for (int t = a.T - 1; t >= 0; --t) {
     HB_TRY(gru_launch_pointwise_bwd<T>(N, H, h + t * NH, v + t * NH * 4,
-                                       (const T*)a.dh_new + (t + 1) * NH, dh_carry,
-                                       dp + t * NH * 3, dq + t * NH * 3,
+                                       (const T*)a.dh_new + (a.iterate ? 0 : (t + 1) * NH),
+                                       dh_carry, dp + t * NH * 3, dq + t * NH * 3,
                                        mask ? mask + t * NH : nullptr, s));
     GemmDesc g{a.dtype, HASTE_B200_F32, N, H, 3 * H, dq + t * NH * 3, 3LL * H, 1, a.R, r_rs, r_cs,
                dh_carry, H, 1};
@@ -187,7 +188,7 @@ int gru_forward(const GruFwd& a, cudaStream_t s) {
     HB_TRY(gemm(g, s));
   }
   ProfScope p(PH_REC_FWD, s);
-  int st_ = gru_forward_persistent(a, s);
+  int st_ = a.h_out ? HASTE_B200_ERR_UNSUPPORTED : gru_forward_persistent(a, s);
   if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
   if (a.dtype == HASTE_B200_F32) return gru_forward_stepwise<float>(a, s);
   return gru_forward_stepwise<__nv_bfloat16>(a, s);
@@ -226,7 +227,8 @@ int gru_backward(const GruBwd& a, cudaStream_t s) {
   int st_;
   {
     ProfScope p(PH_REC_BWD, s);
-    st_ = gru_backward_persistent(a, dh_carry, planes, s);
+    st_ = a.iterate ? HASTE_B200_ERR_UNSUPPORTED
+                    : gru_backward_persistent(a, dh_carry, planes, s);
     have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
     if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
     st_ = (a.dtype == HASTE_B200_F32) ? gru_backward_stepwise<float>(a, dh_carry, s)

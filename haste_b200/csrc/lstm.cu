@@ -97,8 +97,10 @@ int lstm_forward_stepwise(const LstmFwd& a, cudaStream_t s) {
     HB_TRY(gemm_small(g, s));
     T* vt = v + t * NH * 4;
     const T* mt = zo ? mask + t * NH : nullptr;
+    T* h_next = a.h_out ? (T*)a.h_out : h + (t + 1) * NH;
+    T* c_next = a.c_out ? (T*)a.c_out : c + (t + 1) * NH;
 #define HB_ARGS N, H, vt, (const T*)a.tmp_Rh, (const T*)a.b, h + t * NH, c + t * NH, \
-                h + (t + 1) * NH, c + (t + 1) * NH, vt, a.zoneout_prob, mt
+                h_next, c_next, vt, a.zoneout_prob, mt
     if (a.training) {
       if (zo) lstm_pointwise_fwd<T, true, true><<<grid, block, 0, s>>>(HB_ARGS);
       else    lstm_pointwise_fwd<T, true, false><<<grid, block, 0, s>>>(HB_ARGS);
@@ -126,14 +128,15 @@ int lstm_backward_stepwise(const LstmBwd& a, float* dh_carry, float* dc_carry, c
   const long long r_cs = a.transposed_inputs ? 1 : 4LL * H;
   for (int t = a.T - 1; t >= 0; --t) {
     T* vt = v + t * NH * 4;
-    const T* dh_new = (const T*)a.dh_new + (t + 1) * NH;
-    const T* dc_new = (const T*)a.dc_new + (t + 1) * NH;
+    const T* dh_new = (const T*)a.dh_new + (a.iterate ? 0 : (t + 1) * NH);
+    const T* dc_new = (const T*)a.dc_new + (a.iterate ? 0 : (t + 1) * NH);
+    const T* c_new = a.iterate ? (const T*)a.c_new : c + (t + 1) * NH;
     if (mask)
-      lstm_pointwise_bwd<T, true><<<grid, block, 0, s>>>(N, H, c + t * NH, vt, c + (t + 1) * NH,
+      lstm_pointwise_bwd<T, true><<<grid, block, 0, s>>>(N, H, c + t * NH, vt, c_new,
                                                          dh_new, dc_new, dh_carry, dc_carry,
                                                          mask + t * NH);
     else
-      lstm_pointwise_bwd<T, false><<<grid, block, 0, s>>>(N, H, c + t * NH, vt, c + (t + 1) * NH,
+      lstm_pointwise_bwd<T, false><<<grid, block, 0, s>>>(N, H, c + t * NH, vt, c_new,
                                                           dh_new, dc_new, dh_carry, dc_carry,
                                                           nullptr);
     HB_LAUNCH_OK();
@@ -164,7 +167,7 @@ int lstm_forward(const LstmFwd& a, cudaStream_t s) {
     HB_TRY(gemm(g, s));
   }
   ProfScope p(PH_REC_FWD, s);
-  int st_ = lstm_forward_persistent(a, s);
+  int st_ = (a.h_out || a.c_out) ? HASTE_B200_ERR_UNSUPPORTED : lstm_forward_persistent(a, s);
   if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
   if (a.dtype == HASTE_B200_F32) return lstm_forward_stepwise<float>(a, s);
   return lstm_forward_stepwise<__nv_bfloat16>(a, s);
@@ -206,7 +209,8 @@ int lstm_backward(const LstmBwd& a, cudaStream_t s) {
   int st_;
   {
     ProfScope p(PH_REC_BWD, s);
-    st_ = lstm_backward_persistent(a, dh_carry, dc_carry, planes, s);
+    st_ = a.iterate ? HASTE_B200_ERR_UNSUPPORTED
+                    : lstm_backward_persistent(a, dh_carry, dc_carry, planes, s);
     have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
     if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
     st_ = (a.dtype == HASTE_B200_F32) ? lstm_backward_stepwise<float>(a, dh_carry, dc_carry, s)

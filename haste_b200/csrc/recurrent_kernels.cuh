@@ -722,11 +722,9 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
     if (t == 0) break;  // nobody consumes partials of the last step
     __syncthreads();    // the only CTA-wide barrier of the step (A planes are double-buffered)
     if (*reinterpret_cast<volatile int*>(&s_abort)) {
-      if (tid == 0) p.sync.abort_flag[64 + blockIdx.x] = 0x7000000 + ti;
       alive = false;
       break;
     }
-    if (tid == 0) p.sync.abort_flag[64 + blockIdx.x] = 0x1000000 + ti;
 
     // ---- partial dh_{t-1}[rows, all units] = dG . R[:, slice]^T, warp owns NTW*8 units
     {
@@ -767,8 +765,6 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
           }
         }
       }
-      __syncwarp();
-      if (lane == 0) atomicAdd(p.sync.abort_flag + 320 + blockIdx.x, 1);
     }
   }
 

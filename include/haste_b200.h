@@ -109,6 +109,44 @@ int haste_b200_gru_backward(int dtype, int transposed_inputs, int T, int N, int 
                             void* dx, void* dW, void* dR, void* dbx, void* dbr, void* dh,
                             void* dp, void* dq, const void* zoneout_mask, void* stream);
 
+/* ---- single-step forms (the reference's Iterate, for autoregressive use) -- */
+/* One time step with the state in separate [N,H] buffers; same arithmetic as T == 1 of the
+ * sequence entry points, no scratch beyond the arguments.  x [N,C]; v, tmp_* sized for one step.
+ * Replaces lstm::ForwardPass<T>::Iterate (lib/haste/lstm.h:73-86,
+ * lib/lstm_forward_gpu.cu.cc:141-208). */
+int haste_b200_lstm_forward_iterate(int dtype, int training, int N, int C, int H,
+                                    const void* W, const void* R, const void* b, const void* x,
+                                    const void* h, const void* c, void* h_out, void* c_out,
+                                    void* v, void* tmp_Rh, float zoneout_prob,
+                                    const void* zoneout_mask, void* stream);
+/* Replaces lstm::BackwardPass<T>::Iterate (lib/haste/lstm.h:201-219,
+ * lib/lstm_backward_gpu.cu.cc:144-243).  h, c: state before the step; c_new: cell state the
+ * step produced; dh_new, dc_new [N,H]: gradient arriving at the step's outputs; dh, dc [N,H]
+ * in/out carries; dW, dR, db accumulate; dx [N,C] assigned; v [N,4H] is overwritten.
+ * With transposed_inputs, x is [C,N] and W, R are [4H,C], [4H,H]. */
+int haste_b200_lstm_backward_iterate(int dtype, int transposed_inputs, int N, int C, int H,
+                                     const void* W, const void* R, const void* b, const void* x,
+                                     const void* h, const void* c, const void* c_new,
+                                     const void* dh_new, const void* dc_new, void* dx, void* dW,
+                                     void* dR, void* db, void* dh, void* dc, void* v,
+                                     const void* zoneout_mask, void* stream);
+/* Replaces gru::ForwardPass<T>::Iterate (lib/haste/gru.h:72-84,
+ * lib/gru_forward_gpu.cu.cc:160-212).  v [N,4H] (may be null when not training),
+ * tmp_Wx, tmp_Rh [N,3H]. */
+int haste_b200_gru_forward_iterate(int dtype, int training, int N, int C, int H, const void* W,
+                                   const void* R, const void* bx, const void* br, const void* x,
+                                   const void* h, void* h_out, void* v, void* tmp_Wx,
+                                   void* tmp_Rh, float zoneout_prob, const void* zoneout_mask,
+                                   void* stream);
+/* Replaces gru::BackwardPass<T>::Iterate (lib/haste/gru.h:172-189,
+ * lib/gru_backward_gpu.cu.cc:168-250).  dp, dq [N,3H] scratch (written). */
+int haste_b200_gru_backward_iterate(int dtype, int transposed_inputs, int N, int C, int H,
+                                    const void* W, const void* R, const void* bx, const void* br,
+                                    const void* x, const void* h, const void* v,
+                                    const void* dh_new, void* dx, void* dW, void* dR, void* dbx,
+                                    void* dbr, void* dh, void* dp, void* dq,
+                                    const void* zoneout_mask, void* stream);
+
 /* ---- IndRNN ------------------------------------------------------------ */
 /* Replaces indrnn::ForwardPass<T>::Run  (lib/haste/indrnn.h:38-47,
  * lib/indrnn_forward_gpu.cu.cc:126-210).  W [C,H] u,b [H] workspace [T,N,H]. */

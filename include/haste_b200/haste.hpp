@@ -118,6 +118,17 @@ class ForwardPass {
                                           W, R, b, x, h, c, v, tmp_Rh, zoneout_prob, zoneout_mask,
                                           stream_));
   }
+  // One step (lib/haste/lstm.h:73-86).  x [N,C], h, c, h_out, c_out [N,H], v, tmp_Rh [N,4H].
+  // The work runs on `stream` when one is given (the reference orders its private streams
+  // against it), else on the stream the object was built with.
+  void Iterate(const cudaStream_t& stream, const T* W, const T* R, const T* b, const T* x,
+               const T* h, const T* c, T* h_out, T* c_out, T* v, T* tmp_Rh,
+               const float zoneout_prob, const T* zoneout_mask) {
+    detail::check(haste_b200_lstm_forward_iterate(detail::dtype_of<T>::value, training_, N_, C_, H_,
+                                                  W, R, b, x, h, c, h_out, c_out, v, tmp_Rh,
+                                                  zoneout_prob, zoneout_mask,
+                                                  stream ? stream : stream_));
+  }
 
  private:
   bool training_;
@@ -138,6 +149,16 @@ class BackwardPass {
     detail::check(haste_b200_lstm_backward(detail::dtype_of<T>::value, 1, steps, N_, C_, H_, W_t,
                                            R_t, b, x_t, h, c, dh_new, dc_new, dx, dW, dR, db, dh,
                                            dc, v, zoneout_mask, stream_));
+  }
+  // One step (lib/haste/lstm.h:201-219).  x_t [C,N]; h, c: state before the step; c_new: cell
+  // state after it; dh_new, dc_new, dh, dc [N,H]; v [N,4H] from the matching forward step.
+  void Iterate(const cudaStream_t& stream, const T* W_t, const T* R_t, const T* b, const T* x_t,
+               const T* h, const T* c, const T* c_new, const T* dh_new, const T* dc_new, T* dx,
+               T* dW, T* dR, T* db, T* dh, T* dc, T* v, const T* zoneout_mask) {
+    detail::check(haste_b200_lstm_backward_iterate(detail::dtype_of<T>::value, 1, N_, C_, H_, W_t,
+                                                   R_t, b, x_t, h, c, c_new, dh_new, dc_new, dx, dW,
+                                                   dR, db, dh, dc, v, zoneout_mask,
+                                                   stream ? stream : stream_));
   }
 
  private:
@@ -162,6 +183,13 @@ class ForwardPass {
                                          W, R, bx, br, x, h, v, tmp_Wx, tmp_Rh, zoneout_prob,
                                          zoneout_mask, stream_));
   }
+  // One step (lib/haste/gru.h:72-84).  x [N,C], h, h_out [N,H], v [N,4H], tmp_Wx, tmp_Rh [N,3H].
+  void Iterate(const T* W, const T* R, const T* bx, const T* br, const T* x, const T* h, T* h_out,
+               T* v, T* tmp_Wx, T* tmp_Rh, const float zoneout_prob, const T* zoneout_mask) {
+    detail::check(haste_b200_gru_forward_iterate(detail::dtype_of<T>::value, training_, N_, C_, H_,
+                                                 W, R, bx, br, x, h, h_out, v, tmp_Wx, tmp_Rh,
+                                                 zoneout_prob, zoneout_mask, stream_));
+  }
 
  private:
   bool training_;
@@ -181,6 +209,14 @@ class BackwardPass {
     detail::check(haste_b200_gru_backward(detail::dtype_of<T>::value, 1, steps, N_, C_, H_, W_t,
                                           R_t, bx, br, x_t, h, v, dh_new, dx, dW, dR, dbx, dbr, dh,
                                           dp, dq, zoneout_mask, stream_));
+  }
+  // One step (lib/haste/gru.h:172-189).  x_t [C,N]; h: state before the step; dh_new, dh [N,H].
+  void Iterate(const T* W_t, const T* R_t, const T* bx, const T* br, const T* x_t, const T* h,
+               const T* v, const T* dh_new, T* dx, T* dW, T* dR, T* dbx, T* dbr, T* dh, T* dp,
+               T* dq, const T* zoneout_mask) {
+    detail::check(haste_b200_gru_backward_iterate(detail::dtype_of<T>::value, 1, N_, C_, H_, W_t,
+                                                  R_t, bx, br, x_t, h, v, dh_new, dx, dW, dR, dbx,
+                                                  dbr, dh, dp, dq, zoneout_mask, stream_));
   }
 
  private:

@@ -31,6 +31,11 @@ void instantiate_all() {
   auto f8 = &gru::BackwardPass<T>::Run;
   auto f9 = &indrnn::ForwardPass<T>::Run;
   auto f10 = &indrnn::BackwardPass<T>::Run;
+  auto i1 = &lstm::ForwardPass<T>::Iterate;
+  auto i2 = &lstm::BackwardPass<T>::Iterate;
+  auto i3 = &gru::ForwardPass<T>::Iterate;
+  auto i4 = &gru::BackwardPass<T>::Iterate;
+  (void)i1; (void)i2; (void)i3; (void)i4;
   (void)f1; (void)f2; (void)f3; (void)f4; (void)f5; (void)f6; (void)f7; (void)f8; (void)f9; (void)f10;
   (void)lf; (void)lb;
 }
