@@ -23,10 +23,11 @@
 // ~1e-5 of fp32 arithmetic.  bf16 storage: one product.
 //
 // Step-to-step data flow carries its own readiness: everything a CTA hands to another
-// CTA (h_t in the forward pass, partial dh in the backward pass) is written as 32-bit
-// words holding the value as a bf16 (hi, lo) pair, and bit 14 of the lo half - always
-// zero for a genuine lo, whose magnitude is below 2^-8 of the value - carries a tag that
-// alternates every time a buffer is reused.  A consumer simply re-reads a word until the
+// CTA is written as 32-bit words that hold the value and a tag that alternates every time
+// a buffer is reused.  h_t (forward) travels as a bf16 (hi, lo) pair - the consumer copies the
+// halves straight into its operand planes - with the tag in bit 14 of the lo half, always
+// zero for a genuine lo, whose magnitude is below 2^-8 of the value; partial dh (backward)
+// travels as fp32 with the tag in the lowest mantissa bit.  A consumer simply re-reads a word until the
 // tag is the one it expects.  There is no counter, no fence and no grid-wide barrier on
 // the critical path, and 32-bit stores cannot tear.  CTAs of different batch slices never
 // touch each other's data.
@@ -156,6 +157,15 @@ __device__ __forceinline__ bool xword_ready(uint32_t w, uint32_t tag) {
   return ((w >> 30) & 1u) == tag;
 }
 
+// Tagged fp32 word: the value with its lowest mantissa bit replaced by the tag (22 explicit
+// mantissa bits survive).  One logic instruction to encode or decode; used wherever the
+// consumer wants the number itself rather than ready-made bf16 planes.
+__device__ __forceinline__ uint32_t fword_encode(float x, uint32_t tag) {
+  return (__float_as_uint(x) & ~1u) | tag;
+}
+__device__ __forceinline__ float fword_value(uint32_t w) { return __uint_as_float(w & ~1u); }
+__device__ __forceinline__ bool fword_ready(uint32_t w, uint32_t tag) { return (w & 1u) == tag; }
+
 // Fast gate functions (ex2.approx based): error ~1e-6 absolute, far inside the parity bar.
 __device__ __forceinline__ float sigmoid_fast(float x) {
   return __fdividef(1.0f, 1.0f + __expf(-x));
@@ -192,9 +202,11 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
   constexpr int PROW = COLS + 8;          // floats per partial row
   extern __shared__ __align__(16) uint8_t smem[];
   const int BNR = p.MT * 16;
+  // A planes hold ONE m-tile (16 rows): a warp only ever reads its own K range of them, so it
+  // restages them per m-tile without any CTA-wide synchronisation.
   __nv_bfloat16* a_hi = reinterpret_cast<__nv_bfloat16*>(smem);
-  __nv_bfloat16* a_lo = a_hi + (SPLIT == 2 ? (size_t)BNR * AROW : 0);
-  float* part = reinterpret_cast<float*>(smem + (size_t)SPLIT * BNR * AROW * 2);  // [2][8][16][PROW]
+  __nv_bfloat16* a_lo = a_hi + (SPLIT == 2 ? (size_t)16 * AROW : 0);
+  float* part = reinterpret_cast<float*>(smem + (size_t)SPLIT * 16 * AROW * 2);  // [2][8][16][PROW]
   __shared__ int s_abort;
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -263,16 +275,6 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
     c_reg[mt] = (G == 4 && ok) ? ld(cbuf + (long long)n * H + u0 + ul) : 0.f;
   }
 
-  // ---- h_0 (caller's initial state) -> shared memory, cooperatively
-  for (int e = tid; e < BNR * KPAD; e += THREADS) {
-    const int r = e / KPAD, k = e - r * KPAD;
-    const int n = n0 + r;
-    const float x = (n < N && k < H) ? ld(hbuf + (long long)n * H + k) : 0.f;
-    float hi = x, lo = 0.f;
-    if (SPLIT == 2) split_bf16(x, hi, lo);
-    a_hi[(size_t)r * AROW + k] = __float2bfloat16_rn(hi);
-    if (SPLIT == 2) a_lo[(size_t)r * AROW + k] = __float2bfloat16_rn(lo);
-  }
   __syncthreads();
 
   bool alive = true;
@@ -291,59 +293,81 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
                    ? ld(mask + (long long)t * NH + (long long)n * H + u0 + ul) : 0.f;
     }
 
-    // ---- this warp's K range of h_t: poll the tagged words the producers wrote
-    if (t > 0 && !(p.dbg & 1)) {
-      constexpr int CPR = KW / 4;             // 16-byte chunks per row in this warp's range
-      constexpr int CPL = 16 * CPR / 32;      // chunks per lane per m-tile
-      const uint32_t want = (((uint32_t)(t - 1) >> 1) & 1u) ^ 1u;
-      const uint32_t* xsrc = p.xbuf + (size_t)((t - 1) & 1) * N * Hx;
-      for (int mt = 0; mt < p.MT && alive; ++mt) {
-        uint4 w[CPL];
-        const long long t0 = clock64();
-        unsigned int spins = 0;
-        for (;;) {
-          // issue every load before looking at any of them, so their latencies overlap
+    for (int mt = 0; mt < p.MT; ++mt) {
+      // ---- this warp's K range of h_t for the rows of m-tile mt -> the A planes.  At t = 0
+      // the caller's initial state; afterwards the tagged words the producers wrote.  Staging
+      // per m-tile lets the wait for one m-tile hide behind the work on the others.
+      {
+        constexpr int CPR = KW / 4;         // 4-element chunks per row in this warp's range
+        constexpr int CPL = 16 * CPR / 32;  // chunks per lane
+        __syncwarp();                       // the previous m-tile's fragment loads are done
+        if (t == 0) {
 #pragma unroll
           for (int i = 0; i < CPL; ++i) {
             const int e = lane + i * 32;
-            const int r = mt * 16 + e / CPR, k = warp * KW + (e % CPR) * 4;
-            const int n = n0 + r;
-            if (n < N && k < Hx) w[i] = ld_relaxed_u32x4(xsrc + (size_t)n * Hx + k);
-            else w[i] = make_uint4(want << 30, want << 30, want << 30, want << 30);
-          }
-          bool ok = true;
+            const int r = e / CPR, k = warp * KW + (e % CPR) * 4;
+            const int n = n0 + mt * 16 + r;
+            float x[4], lo[4];
 #pragma unroll
-          for (int i = 0; i < CPL; ++i)
-            ok = ok && xword_ready(w[i].x, want) && xword_ready(w[i].y, want) &&
-                 xword_ready(w[i].z, want) && xword_ready(w[i].w, want);
-          if (__all_sync(0xffffffffu, ok)) break;
-          if ((++spins & 63u) == 0) {
-            bool stop = *reinterpret_cast<volatile int*>(p.sync.abort_flag) != 0;
-            if (!stop && clock64() - t0 > SPIN_LIMIT_CYCLES) {
-              raise_abort(p.sync, &s_abort, 16);
-              stop = true;
+            for (int j4 = 0; j4 < 4; ++j4) {
+              x[j4] = (n < N && k + j4 < H) ? ld(hbuf + (long long)n * H + k + j4) : 0.f;
+              lo[j4] = 0.f;
+              if (SPLIT == 2) split_bf16(x[j4], x[j4], lo[j4]);
             }
-            if (__any_sync(0xffffffffu, stop)) { alive = false; break; }
+            *reinterpret_cast<uint2*>(a_hi + (size_t)r * AROW + k) =
+                make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
+            if (SPLIT == 2)
+              *reinterpret_cast<uint2*>(a_lo + (size_t)r * AROW + k) =
+                  make_uint2(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]));
+          }
+        } else if (alive && !(p.dbg & 1)) {
+          const uint32_t want = (((uint32_t)(t - 1) >> 1) & 1u) ^ 1u;
+          const uint32_t wtag = want << 30;
+          const uint32_t* xsrc = p.xbuf + (size_t)((t - 1) & 1) * N * Hx;
+          uint4 w[CPL];
+          const long long t0 = clock64();
+          unsigned int spins = 0;
+          for (;;) {
+            // issue every load before looking at any of them, so their latencies overlap
+#pragma unroll
+            for (int i = 0; i < CPL; ++i) {
+              const int e = lane + i * 32;
+              const int r = e / CPR, k = warp * KW + (e % CPR) * 4;
+              const int n = n0 + mt * 16 + r;
+              if (n < N && k < Hx) w[i] = ld_relaxed_u32x4(xsrc + (size_t)n * Hx + k);
+              else w[i] = make_uint4(wtag, wtag, wtag, wtag);
+            }
+            // one logic instruction per word: bit 30 of `bad` ends up set if any tag is stale
+            uint32_t bad = 0;
+#pragma unroll
+            for (int i = 0; i < CPL; ++i)
+              bad |= (w[i].x ^ wtag) | (w[i].y ^ wtag) | (w[i].z ^ wtag) | (w[i].w ^ wtag);
+            const bool ok = (bad & 0x40000000u) == 0;
+            if (__all_sync(0xffffffffu, ok)) break;
+            if ((++spins & 63u) == 0) {
+              bool stop = *reinterpret_cast<volatile int*>(p.sync.abort_flag) != 0;
+              if (!stop && clock64() - t0 > SPIN_LIMIT_CYCLES) {
+                raise_abort(p.sync, &s_abort, 16);
+                stop = true;
+              }
+              if (__any_sync(0xffffffffu, stop)) { alive = false; break; }
+            }
+          }
+          if (!alive) *reinterpret_cast<volatile int*>(&s_abort) = 1;  // the barrier below sees it
+#pragma unroll
+          for (int i = 0; i < CPL; ++i) {
+            const int e = lane + i * 32;
+            const int r = e / CPR, k = warp * KW + (e % CPR) * 4;
+            *reinterpret_cast<uint2*>(a_hi + (size_t)r * AROW + k) =
+                make_uint2(__byte_perm(w[i].x, w[i].y, 0x5410), __byte_perm(w[i].z, w[i].w, 0x5410));
+            if (SPLIT == 2)
+              *reinterpret_cast<uint2*>(a_lo + (size_t)r * AROW + k) =
+                  make_uint2(__byte_perm(w[i].x, w[i].y, 0x7632) & 0xBFFFBFFFu,
+                             __byte_perm(w[i].z, w[i].w, 0x7632) & 0xBFFFBFFFu);
           }
         }
-        if (!alive) break;
-#pragma unroll
-        for (int i = 0; i < CPL; ++i) {
-          const int e = lane + i * 32;
-          const int r = mt * 16 + e / CPR, k = warp * KW + (e % CPR) * 4;
-          *reinterpret_cast<uint2*>(a_hi + (size_t)r * AROW + k) =
-              make_uint2(__byte_perm(w[i].x, w[i].y, 0x5410), __byte_perm(w[i].z, w[i].w, 0x5410));
-          if (SPLIT == 2)
-            *reinterpret_cast<uint2*>(a_lo + (size_t)r * AROW + k) =
-                make_uint2(__byte_perm(w[i].x, w[i].y, 0x7632) & 0xBFFFBFFFu,
-                           __byte_perm(w[i].z, w[i].w, 0x7632) & 0xBFFFBFFFu);
-        }
+        __syncwarp();
       }
-      __syncwarp();
-    }
-    if (!alive) *reinterpret_cast<volatile int*>(&s_abort) = 1;
-
-    for (int mt = 0; mt < p.MT; ++mt) {
       // ---- this warp's K range of the step product
       float acc[NT][4];
 #pragma unroll
@@ -351,7 +375,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
       if (!(p.dbg & 2)) {
 #pragma unroll
         for (int ks = 0; ks < KSW; ++ks) {
-          const int row = mt * 16 + (lane & 15);
+          const int row = lane & 15;
           const int kcol = warp * KW + ks * 16 + (lane >> 4) * 8;
           uint32_t ah[4], al[4];
           ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), ah);
@@ -375,8 +399,9 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
         *reinterpret_cast<float2*>(pw + (gq + 8) * PROW + nt * 8 + 2 * q) =
             make_float2(acc[nt][2], acc[nt][3]);
       }
-      __syncthreads();  // the only CTA-wide barrier of the step (partials are double-buffered)
-      if (*reinterpret_cast<volatile int*>(&s_abort)) { alive = false; break; }
+      // the only CTA-wide barrier per m-tile (partials are double-buffered); the OR makes the
+      // decision to stop the same for every thread
+      if (__syncthreads_or(*reinterpret_cast<volatile int*>(&s_abort))) { alive = false; break; }
 
       // ---- pointwise stage for (row nl of m-tile mt, unit ul)
       float rh[G];
@@ -588,7 +613,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
             uint4 a[8];
             const long long t0 = clock64();
             unsigned int spins = 0;
-            const uint32_t rdy = want << 30;
+            const uint32_t rdy = want;
             for (;;) {
 #pragma unroll
               for (int k = 0; k < 8; ++k) {
@@ -596,12 +621,11 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
                 a[k] = (sidx < p.nHS) ? ld_relaxed_u32x4(q0 + (size_t)sidx * blk)
                                       : make_uint4(rdy, rdy, rdy, rdy);
               }
-              bool ok = true;
+              uint32_t bad = 0;  // bit 0 ends up set if any tag is stale
 #pragma unroll
               for (int k = 0; k < 8; ++k)
-                ok = ok && xword_ready(a[k].x, want) && xword_ready(a[k].y, want) &&
-                     xword_ready(a[k].z, want) && xword_ready(a[k].w, want);
-              if (ok) break;
+                bad |= (a[k].x ^ want) | (a[k].y ^ want) | (a[k].z ^ want) | (a[k].w ^ want);
+              if ((bad & 1u) == 0) break;
               if ((++spins & 63u) == 0) {
                 if (*reinterpret_cast<volatile int*>(p.sync.abort_flag) != 0) { alive = false; break; }
                 if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
@@ -613,10 +637,10 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
             }
 #pragma unroll
             for (int k = 0; k < 8; ++k) {
-              s4[0] += xword_value(a[k].x);
-              s4[1] += xword_value(a[k].y);
-              s4[2] += xword_value(a[k].z);
-              s4[3] += xword_value(a[k].w);
+              s4[0] += fword_value(a[k].x);
+              s4[1] += fword_value(a[k].y);
+              s4[2] += fword_value(a[k].z);
+              s4[3] += fword_value(a[k].w);
             }
           }
 #pragma unroll
@@ -759,9 +783,9 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
             const int dest = j / U, uj = j % U;
             uint32_t* d = dstbase + ((size_t)dest * p.nHS + hs) * blk + (size_t)(mt * 16) * U + uj;
             __stcg(reinterpret_cast<uint2*>(d + (size_t)gq * U),
-                   make_uint2(xword_encode(acc[nt][0], tag), xword_encode(acc[nt][1], tag)));
+                   make_uint2(fword_encode(acc[nt][0], tag), fword_encode(acc[nt][1], tag)));
             __stcg(reinterpret_cast<uint2*>(d + (size_t)(gq + 8) * U),
-                   make_uint2(xword_encode(acc[nt][2], tag), xword_encode(acc[nt][3], tag)));
+                   make_uint2(fword_encode(acc[nt][2], tag), fword_encode(acc[nt][3], tag)));
           }
         }
       }
@@ -821,7 +845,7 @@ int run_fwd(FwdParams& p, const Geometry& g, cudaStream_t s) {
   const int ksw = ceil_div(ksteps, WARPS);
   auto smem_for = [&](int KSW) {
     const size_t arow = (size_t)WARPS * KSW * 16 + 8;
-    return (size_t)SPLIT * g.MT * 16 * arow * 2 + (size_t)2 * WARPS * 16 * (G * U + 8) * 4;
+    return (size_t)SPLIT * 16 * arow * 2 + (size_t)2 * WARPS * 16 * (G * U + 8) * 4;
   };
   const int grid = g.nHS * g.nBS;
 #define HB_FWD(KSW)                                                                          \

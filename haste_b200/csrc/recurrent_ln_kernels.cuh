@@ -82,16 +82,9 @@ struct LnBwdParams {
   long long gpl_stride;
 };
 
-// Statistics and partial gradients travel as fp32 words whose lowest mantissa bit is replaced
-// by the tag (22 explicit mantissa bits survive): LayerNorm amplifies a relative error of the
-// exchanged value roughly tenfold, so the 17 bits of the (hi, lo) bf16 pair are not enough
-// here.  Same protocol otherwise: buffers start zeroed and the expected tag alternates.
-__device__ __forceinline__ uint32_t fword_encode(float x, uint32_t tag) {
-  return (__float_as_uint(x) & ~1u) | tag;
-}
-__device__ __forceinline__ float fword_value(uint32_t w) { return __uint_as_float(w & ~1u); }
-__device__ __forceinline__ bool fword_ready(uint32_t w, uint32_t tag) { return (w & 1u) == tag; }
-
+// Statistics, partial gradients and (with fp32 storage) h travel as tagged fp32 words
+// (fword_* of recurrent_kernels.cuh): LayerNorm amplifies a relative error of the exchanged
+// value roughly tenfold, so the 17 bits of the (hi, lo) bf16 pair are not enough here.
 // h words: tagged fp32 with fp32 storage, the (hi, lo) bf16 pair with bf16 storage.
 template <int SPLIT> __device__ __forceinline__ uint32_t hword_encode(float x, uint32_t tag) {
   return SPLIT == 2 ? fword_encode(x, tag) : xword_encode(x, tag);
@@ -372,11 +365,13 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
                 else w[i] = SPLIT == 2 ? make_uint4(want, want, want, want)
                                        : make_uint4(want << 30, want << 30, want << 30, want << 30);
               }
-              bool ok = true;
+              // one logic instruction per word: the tag bit of `bad` ends up set if any is stale
+              uint32_t bad = 0;
+              const uint32_t wtag = SPLIT == 2 ? want : want << 30;
 #pragma unroll
               for (int i = 0; i < CPL; ++i)
-                ok = ok && hword_ready<SPLIT>(w[i].x, want) && hword_ready<SPLIT>(w[i].y, want) &&
-                     hword_ready<SPLIT>(w[i].z, want) && hword_ready<SPLIT>(w[i].w, want);
+                bad |= (w[i].x ^ wtag) | (w[i].y ^ wtag) | (w[i].z ^ wtag) | (w[i].w ^ wtag);
+              const bool ok = (bad & (SPLIT == 2 ? 1u : 0x40000000u)) == 0;
               if (__all_sync(0xffffffffu, ok)) break;
               if ((++spins & 63u) == 0) {
                 bool quit = *reinterpret_cast<volatile int*>(p.sync.abort_flag) != 0;
@@ -770,12 +765,11 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
                 a[k] = (sidx < p.nHS) ? ld_relaxed_u32x4(q0 + (size_t)sidx * blk)
                                       : make_uint4(rdy, rdy, rdy, rdy);
               }
-              bool ok = true;
+              uint32_t bad = 0;  // bit 0 ends up set if any tag is stale
 #pragma unroll
               for (int k = 0; k < 8; ++k)
-                ok = ok && fword_ready(a[k].x, want) && fword_ready(a[k].y, want) &&
-                     fword_ready(a[k].z, want) && fword_ready(a[k].w, want);
-              if (ok) break;
+                bad |= (a[k].x ^ want) | (a[k].y ^ want) | (a[k].z ^ want) | (a[k].w ^ want);
+              if ((bad & 1u) == 0) break;
               if ((++spins & 63u) == 0) {
                 if (*reinterpret_cast<volatile int*>(p.sync.abort_flag) != 0) { alive = false; break; }
                 if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
