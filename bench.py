@@ -254,6 +254,10 @@ def main():
     phases = {k: v / args.steps for k, v in _C.profile_read().items()}
     _C.profile_enable(False)
 
+    try:
+        exchange_us = _C.probe_exchange_latency(N, H, 2000, torch.cuda.current_stream().cuda_stream)
+    except Exception:
+        exchange_us = None  # shape does not fit the probe's one-CTA-per-SM tiling
     ms_step = ms_total / args.steps
     value = world * N * T / (ms_step * 1e-3)
     e2e_value = world * N * T / (ms_e2e / args.steps * 1e-3)
@@ -311,6 +315,12 @@ def main():
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "roofline": roof,
+        # The recurrence is bound by its step-to-step dependency, not by a throughput roofline:
+        # measured time per step of both passes beside the time per step of the inter-CTA
+        # hand-off alone (exchange-only probe kernel, same tiling, measured in this run).
+        "latency": {"fwd_us_per_step": phases["recurrence_fwd"] * 1e3 / T,
+                    "bwd_us_per_step": phases["recurrence_bwd"] * 1e3 / T,
+                    "exchange_only_us_per_step": exchange_us},
         "phases_ms": phases,
         "phase_tflops": {k: flops[k] / (phases[k] * 1e-3) / 1e12 for k in flops if phases.get(k)},
     }

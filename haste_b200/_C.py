@@ -19,6 +19,7 @@ _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlo
 SIGNATURES = {
     "haste_b200_lstm_forward": [_i] * 6 + [_p] * 8 + [_f, _p, _p],
     "haste_b200_lstm_backward": [_i] * 6 + [_p] * 17,
+    "haste_b200_probe_exchange_latency": [_i] * 3 + [_p, _p],
     "haste_b200_lstm_forward_iterate": [_i] * 5 + [_p] * 10 + [_f, _p, _p],
     "haste_b200_lstm_backward_iterate": [_i] * 5 + [_p] * 18,
     "haste_b200_gru_forward_iterate": [_i] * 5 + [_p] * 10 + [_f, _p, _p],
@@ -102,6 +103,14 @@ PHASES = ["input_projection", "recurrence_fwd", "recurrence_bwd", "weight_grad",
 
 def profile_enable(on=True):
     call("haste_b200_profile_enable", int(on))
+
+
+def probe_exchange_latency(N, H, steps=2000, stream=None):
+    """Device microseconds per step of the forward recurrence's hand-off alone (see the header)."""
+    out = ctypes.c_float(0.0)
+    call("haste_b200_probe_exchange_latency", int(N), int(H), int(steps),
+         ctypes.cast(ctypes.byref(out), ctypes.c_void_p), stream)
+    return float(out.value)
 
 
 def profile_read():

@@ -72,6 +72,10 @@ int haste_b200_lstm_backward(int dtype, int transposed_inputs, int T, int N, int
   return lstm_backward(a, (cudaStream_t)stream);
 }
 
+int haste_b200_probe_exchange_latency(int N, int H, int steps, float* us_per_step, void* stream) {
+  return exchange_probe(N, H, steps, us_per_step, (cudaStream_t)stream);
+}
+
 int haste_b200_lstm_forward_iterate(int dtype, int training, int N, int C, int H, const void* W,
                                     const void* R, const void* b, const void* x, const void* h,
                                     const void* c, void* h_out, void* c_out, void* v,

@@ -139,6 +139,10 @@ int layer_norm_gru_forward_persistent(const LnGruFwd& a, cudaStream_t s);
 int layer_norm_gru_backward_persistent(const LnGruBwd& a, float* dh_carry, float* acc,
                                        const GradPlanes& planes, cudaStream_t s);
 
+// Exchange-only probe (recurrent_host.cu): device microseconds per step of the forward
+// recurrence's hand-off alone, for the tiling (N, H) would get.
+int exchange_probe(int N, int H, int steps, float* us_per_step, cudaStream_t s);
+
 // Per-step contraction (M = batch rows).  Small products are launch-bound and stay on the
 // CUDA-core kernel; from 2^26 multiply-adds up the tensor-core kernel pays for its set-up
 // (operand split and tensor maps) even with a partly empty 128-row tile.

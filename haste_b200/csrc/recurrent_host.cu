@@ -71,6 +71,113 @@ int make_scratch(size_t words, Sync* sync, uint32_t** xwords, cudaStream_t s) {
 }  // namespace
 }  // namespace rec
 
+// ---- exchange-only probe ---------------------------------------------------------------
+// The hand-off of the forward recurrence with everything else taken out: per step every CTA
+// publishes its 16 x 16 tagged words and every warp waits for its K range of all rows, then
+// the CTA meets at its barrier.  No contraction, no gate math, no activation traffic.  Its
+// time per step is the part of a recurrence step that no amount of arithmetic tuning removes
+// (store -> L2 -> polling load, plus the CTA barrier); benchmarks quote it beside the measured
+// step time.  No reference counterpart.
+namespace rec {
+namespace {
+
+template <int KSW>
+__global__ void __launch_bounds__(THREADS, 1)
+exchange_probe_kernel(int T, int N, int Hx, int nHS, uint32_t* xbuf, Sync sync) {
+  constexpr int KW = KSW * 16, CPR = KW / 4, CPL = 16 * CPR / 32;
+  __shared__ int s_abort;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int hs = blockIdx.x % nHS, bs = blockIdx.x / nHS;
+  const int nl = tid >> 4, ul = tid & 15;
+  const int u0 = hs * U, n0 = bs * 16;
+  if (tid == 0) s_abort = 0;
+  __syncthreads();
+  float carry = 0.f;
+  for (int t = 0; t < T; ++t) {
+    const uint32_t tag = (((uint32_t)t >> 1) & 1u) ^ 1u;
+    const int n = n0 + nl;
+    if (n < N && u0 + ul < Hx)
+      __stcg(xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul,
+             xword_encode(carry * 0.5f + 0.25f, tag));
+    const uint32_t wtag = tag << 30;
+    const uint32_t* xsrc = xbuf + (size_t)(t & 1) * N * Hx;
+    uint4 w[CPL];
+    const long long t0 = clock64();
+    unsigned int spins = 0;
+    bool alive = true;
+    for (;;) {
+#pragma unroll
+      for (int i = 0; i < CPL; ++i) {
+        const int e = lane + i * 32;
+        const int r = e / CPR, k = warp * KW + (e % CPR) * 4;
+        if (n0 + r < N && k < Hx) w[i] = ld_relaxed_u32x4(xsrc + (size_t)(n0 + r) * Hx + k);
+        else w[i] = make_uint4(wtag, wtag, wtag, wtag);
+      }
+      uint32_t bad = 0;
+#pragma unroll
+      for (int i = 0; i < CPL; ++i)
+        bad |= (w[i].x ^ wtag) | (w[i].y ^ wtag) | (w[i].z ^ wtag) | (w[i].w ^ wtag);
+      if (__all_sync(0xffffffffu, (bad & 0x40000000u) == 0)) break;
+      if ((++spins & 63u) == 0) {
+        bool stop = *reinterpret_cast<volatile int*>(sync.abort_flag) != 0;
+        if (!stop && clock64() - t0 > SPIN_LIMIT_CYCLES) {
+          raise_abort(sync, &s_abort, 46, blockIdx.x, t);
+          stop = true;
+        }
+        if (__any_sync(0xffffffffu, stop)) { alive = false; break; }
+      }
+    }
+    if (!alive) *reinterpret_cast<volatile int*>(&s_abort) = 1;
+    carry = xword_value(w[0].x);  // the next word depends on a received one, as h does
+    if (__syncthreads_or(*reinterpret_cast<volatile int*>(&s_abort))) break;
+  }
+}
+
+}  // namespace
+}  // namespace rec
+
+// Runs the probe for `steps` steps with the tiling the recurrence would use for (N, H) and
+// returns the device time per step in microseconds.
+int exchange_probe(int N, int H, int steps, float* us_per_step, cudaStream_t s) {
+  using namespace rec;
+  HB_REQUIRE(N > 0 && H > 0 && steps > 0 && us_per_step, "arguments");
+  const int nHS = ceil_div(H, U), nBS = ceil_div(N, 16);
+  HB_REQUIRE((long long)nHS * nBS <= sm_count(), "does not fit one CTA per SM");
+  const int Hx = nHS * U;
+  const int ksw = ceil_div(nHS, WARPS);
+  HB_REQUIRE(ksw <= 8, "H too large for the probe");
+  Sync sync;
+  uint32_t* xbuf = nullptr;
+  HB_TRY(make_scratch((size_t)2 * N * Hx, &sync, &xbuf, s));
+  cudaEvent_t e0, e1;
+  HB_CUDA_OK(cudaEventCreate(&e0));
+  HB_CUDA_OK(cudaEventCreate(&e1));
+  int T = steps, Nn = N, Hxx = Hx, nhs = nHS;
+  void* args[] = {&T, &Nn, &Hxx, &nhs, &xbuf, &sync};
+  const void* fn = ksw <= 1   ? (const void*)exchange_probe_kernel<1>
+                   : ksw <= 2 ? (const void*)exchange_probe_kernel<2>
+                   : ksw <= 4 ? (const void*)exchange_probe_kernel<4>
+                              : (const void*)exchange_probe_kernel<8>;
+  HB_CUDA_OK(cudaEventRecord(e0, s));
+  cudaError_t e = cudaLaunchCooperativeKernel(fn, dim3(nHS * nBS), dim3(THREADS), args, 0, s);
+  if (e != cudaSuccess) {
+    set_last_error("cooperative launch failed: %s", cudaGetErrorString(e));
+    cudaGetLastError();
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    return HASTE_B200_ERR_CUDA;
+  }
+  count_launch(1);
+  HB_CUDA_OK(cudaEventRecord(e1, s));
+  HB_CUDA_OK(cudaEventSynchronize(e1));
+  float ms = 0.f;
+  HB_CUDA_OK(cudaEventElapsedTime(&ms, e0, e1));
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  *us_per_step = ms * 1e3f / steps;
+  return HASTE_B200_OK;
+}
+
 using namespace rec;
 
 int lstm_forward_persistent(const LstmFwd& a, cudaStream_t s) {

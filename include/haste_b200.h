@@ -67,6 +67,12 @@ long long haste_b200_launch_count(void);
  * asynchronous entry points cannot report that themselves. */
 int haste_b200_sync_check(void* stream);
 int haste_b200_profile_enable(int on);
+/* Measurement aid, no reference counterpart: runs `steps` steps of the forward recurrence's
+ * inter-CTA hand-off alone (publish tagged words, wait for all of them, CTA barrier; no
+ * contraction, no gate math, no activation traffic) with the tiling a recurrence of batch N
+ * and H hidden units uses, waits for it, and returns the device time per step in
+ * microseconds.  N*H must fit one CTA per SM (16 rows x 16 units per CTA). */
+int haste_b200_probe_exchange_latency(int N, int H, int steps, float* us_per_step, void* stream);
 int haste_b200_profile_read(float* ms, int n);
 
 /* ---- LSTM -------------------------------------------------------------- */
