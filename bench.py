@@ -169,7 +169,7 @@ def main():
         run_reference_arm(args)
         return
 
-    from haste_b200 import _C, ops
+    from haste_b200 import _C, data_parallel, ops
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -198,8 +198,7 @@ def main():
         dx, dh, dc0, dW, dR, db = ops.lstm_backward(x_dev, W, R, b, nomask, h, c, cache, dy, dc,
                                                     transposed=False)
         if world > 1:
-            flat = torch.cat([dW.reshape(-1), dR.reshape(-1), db])
-            dist.all_reduce(flat)
+            data_parallel.all_reduce_tensors([dW, dR, db])
         return h, db
 
     def e2e_step():
@@ -208,7 +207,7 @@ def main():
         dx, dh, dc0, dW, dR, db = ops.lstm_backward(x_dev, W, R, b, nomask, h, c, cache, dy, dc,
                                                     transposed=False)
         if world > 1:
-            dist.all_reduce(torch.cat([dW.reshape(-1), dR.reshape(-1), db]))
+            data_parallel.all_reduce_tensors([dW, dR, db])
         res_host[:N * H].copy_(h[-1].reshape(-1), non_blocking=True)
         res_host[N * H:].copy_(db, non_blocking=True)
         torch.cuda.current_stream().synchronize()

@@ -8,10 +8,10 @@ behind the API of lmnt-com/haste's `haste_pytorch` package.
 The compute path is libhaste_b200.so (hand-written CUDA for sm_100a behind a C ABI,
 see include/haste_b200.h); build it with `python -m haste_b200.build`.
 """
-from . import _C, ops
+from . import _C, data_parallel, ops
 from .rnn import GRU, LSTM, IndRNN, LayerNormGRU, LayerNormIndRNN, LayerNormLSTM, Stack
 
 __version__ = "0.1.0"
 
 __all__ = ["GRU", "IndRNN", "LSTM", "LayerNormGRU", "LayerNormIndRNN", "LayerNormLSTM", "Stack",
-           "ops"]
+           "data_parallel", "ops"]

@@ -1,0 +1,111 @@
+"""Batch-sharded data parallelism for the recurrent layers: one process per GPU.
+
+Every sequence of a batch is independent and LayerNorm statistics are per row, so a layer
+shards on the batch axis with no exchange in the forward or backward pass; the only
+collective is the sum of the parameter gradients (kernel, recurrent kernel, biases,
+LayerNorm gains) over the ranks.  This module holds that host-side logic, written against
+`torch.distributed` so that it runs over NCCL on GPUs and over gloo on CPU (which is how
+it is tested):
+
+* `shard` cuts the batch axis of an input, state, mask or upstream-gradient tensor;
+* `dropconnect_mask` draws the recurrent-weight mask from a shared seed, because every rank
+  must apply the same mask to its replica of the weights;
+* `broadcast_parameters` makes the replicas identical at start;
+* `all_reduce_tensors` / `all_reduce_gradients` sum gradients in flat buckets (one
+  launch-latency-sized collective per bucket instead of one per tensor).
+
+The reference has no multi-GPU path; its layers are used under the framework's own data
+parallel wrappers, which this mirrors.
+"""
+import torch
+import torch.distributed as dist
+
+__all__ = ["shard", "dropconnect_mask", "broadcast_parameters", "all_reduce_tensors",
+           "all_reduce_gradients"]
+
+
+def _world(group=None):
+    if not (dist.is_available() and dist.is_initialized()):
+        return 0, 1
+    return dist.get_rank(group), dist.get_world_size(group)
+
+
+def shard(t, rank, world, batch_dim=1):
+    """This rank's slice of `t` along the batch axis (`[T,N,...]` tensors: batch_dim=1,
+    `[N,H]` states: batch_dim=0).  The batch must divide evenly: a ragged split would give the
+    ranks different step times and the slowest one sets the pace."""
+    if t is None:
+        return None
+    n = t.shape[batch_dim]
+    if n % world:
+        raise ValueError(f"batch of {n} does not divide over {world} ranks")
+    per = n // world
+    return t.narrow(batch_dim, rank * per, per).contiguous()
+
+
+def dropconnect_mask(shape, drop_prob, seed, device=None, dtype=torch.float32):
+    """Bernoulli(1 - drop_prob) keep-mask for the recurrent kernel, drawn on the CPU from
+    `seed` alone so that every rank gets the same mask whatever its device state."""
+    g = torch.Generator().manual_seed(int(seed))
+    keep = torch.bernoulli(torch.full(tuple(shape), 1.0 - float(drop_prob)), generator=g)
+    return keep.to(device=device, dtype=dtype)
+
+
+def broadcast_parameters(module, src=0, group=None):
+    """Copies rank `src`'s parameters and buffers to every rank, in place."""
+    _, world = _world(group)
+    if world == 1:
+        return
+    with torch.no_grad():
+        for t in list(module.parameters()) + list(module.buffers()):
+            dist.broadcast(t.data, src=src, group=group)
+
+
+def all_reduce_tensors(tensors, group=None, bucket_bytes=64 << 20, async_op=False):
+    """Sums each tensor of `tensors` over the ranks, in place.
+
+    Tensors are packed into flat buckets of up to `bucket_bytes` per dtype; each bucket is one
+    all-reduce.  With `async_op` the call returns a `finish()` callable: the collectives are in
+    flight when it returns, and `finish()` waits for them and scatters the sums back - issue it
+    after queuing the next layer's backward pass to overlap the two."""
+    _, world = _world(group)
+    tensors = [t for t in tensors if t is not None]
+    if world == 1 or not tensors:
+        return (lambda: None) if async_op else None
+    buckets, cur, cur_bytes = [], [], 0
+    for t in tensors:
+        nbytes = t.numel() * t.element_size()
+        if cur and (cur[0].dtype != t.dtype or cur[0].device != t.device
+                    or cur_bytes + nbytes > bucket_bytes):
+            buckets.append(cur)
+            cur, cur_bytes = [], 0
+        cur.append(t)
+        cur_bytes += nbytes
+    buckets.append(cur)
+    pending = []
+    for b in buckets:
+        flat = torch.cat([t.reshape(-1) for t in b])
+        work = dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        pending.append((b, flat, work))
+
+    def finish():
+        for b, flat, work in pending:
+            work.wait()
+            off = 0
+            for t in b:
+                n = t.numel()
+                t.copy_(flat[off:off + n].view_as(t))
+                off += n
+
+    if async_op:
+        return finish
+    finish()
+    return None
+
+
+def all_reduce_gradients(module_or_params, group=None, bucket_bytes=64 << 20, async_op=False):
+    """Sums the `.grad` of every parameter over the ranks (see `all_reduce_tensors`)."""
+    params = (module_or_params.parameters() if hasattr(module_or_params, "parameters")
+              else module_or_params)
+    return all_reduce_tensors([p.grad for p in params if p.grad is not None], group=group,
+                              bucket_bytes=bucket_bytes, async_op=async_op)

@@ -1,0 +1,111 @@
+"""Host-side logic of the multi-GPU path, run as two gloo ranks on CPU: batch sharding,
+shared DropConnect masks, parameter broadcast and the bucketed gradient all-reduce.  The
+per-rank computation is the CPU oracle (test infrastructure); what is under test is
+haste_b200.data_parallel."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+import haste_oracle as oracle
+
+WORLD = 2
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, port, cell, results):
+    from haste_b200 import data_parallel as dp
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD)
+    try:
+        torch.set_num_threads(1)
+        T, N, C, H = 5, 6, 4, 8
+        d = oracle.make_inputs(cell, T, N, C, H, seed=5, zoneout=0.2)
+        # the same DropConnect mask on every rank, from the seed alone
+        keep = dp.dropconnect_mask(d["R"].shape, 0.25, seed=77, dtype=torch.float64)
+        gathered = [torch.empty_like(keep) for _ in range(WORLD)]
+        dist.all_gather(gathered, keep)
+        assert all(torch.equal(g, keep) for g in gathered)
+        d["R"] = d["R"] * keep / 0.75
+        ref_out, ref_g = oracle.forward_backward(cell, d, zoneout=0.2)
+
+        # rank-local shard of everything that carries a batch axis
+        ds = dict(d)
+        for k in ("x", "mask", "dh", "dc"):
+            if d.get(k) is not None:
+                ds[k] = dp.shard(d[k], rank, WORLD, batch_dim=1)
+        for k in ("h0", "c0"):
+            if k in d:
+                ds[k] = dp.shard(d[k], rank, WORLD, batch_dim=0)
+        out, g = oracle.forward_backward(cell, ds, zoneout=0.2)
+        per = N // WORLD
+        assert torch.allclose(out["h"], ref_out["h"][:, rank * per:(rank + 1) * per], atol=1e-12)
+
+        # parameter gradients: summed over ranks in flat buckets; tiny buckets force several
+        weights = [k for k in g if k not in ("x", "h0", "c0")]
+        tensors = [g[k].clone() for k in weights]
+        finish = dp.all_reduce_tensors(tensors, bucket_bytes=256, async_op=True)
+        finish()
+        for k, t in zip(weights, tensors):
+            assert torch.allclose(t, ref_g[k], rtol=1e-10, atol=1e-12), k
+        # per-sample gradients stay local and equal the matching slice
+        assert torch.allclose(g["x"], ref_g["x"][:, rank * per:(rank + 1) * per], atol=1e-12)
+
+        # module form: broadcast, then all_reduce_gradients on .grad
+        lin = torch.nn.Linear(3, 2).double()
+        with torch.no_grad():
+            for p in lin.parameters():
+                p.add_(rank + 1.0)
+        dp.broadcast_parameters(lin, src=0)
+        ref = [p.detach().clone() for p in lin.parameters()]
+        gathered = [torch.empty_like(ref[0]) for _ in range(WORLD)]
+        dist.all_gather(gathered, ref[0])
+        assert torch.equal(gathered[0], gathered[1])
+        for p in lin.parameters():
+            p.grad = torch.full_like(p, float(rank + 1))
+        dp.all_reduce_gradients(lin)
+        for p in lin.parameters():
+            assert torch.equal(p.grad, torch.full_like(p, 3.0))
+        results[rank] = "ok"
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("cell", ["lstm", "layer_norm_gru"])
+def test_two_gloo_ranks_reproduce_the_single_process_gradients(cell):
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_rank_main, args=(r, port, cell, results)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=240)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            pytest.fail("rank did not finish")
+    assert all(p.exitcode == 0 for p in procs), [p.exitcode for p in procs]
+    assert dict(results) == {0: "ok", 1: "ok"}
+
+
+def test_shard_rejects_ragged_batches_and_is_identity_for_one_rank():
+    from haste_b200 import data_parallel as dp
+    x = torch.arange(24.0).reshape(2, 6, 2)
+    assert torch.equal(dp.shard(x, 0, 1), x)
+    assert torch.equal(dp.shard(x, 1, 3), x[:, 2:4])
+    assert dp.shard(None, 0, 2) is None
+    with pytest.raises(ValueError):
+        dp.shard(x, 0, 4)
+    # without a process group the collectives are no-ops
+    t = torch.ones(3)
+    assert dp.all_reduce_tensors([t]) is None and torch.equal(t, torch.ones(3))
+    dp.all_reduce_tensors([t], async_op=True)()
