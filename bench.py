@@ -164,9 +164,16 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--ref-cuda", action="store_true",
                     help="also time the reference's own CUDA build if oracle/_ref holds it")
+    ap.add_argument("--workload", default="headline",
+                    help="headline (default) | grid-<lstm|gru>-N<n>-H<h> | config2 | "
+                         "config3-indrnn | config3-lnindrnn | config4-N<n>: the other benchmark "
+                         "configurations, one JSON line each (single GPU)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
+        return
+    if args.workload != "headline":
+        run_config_workload(args)
         return
 
     from haste_b200 import _C, data_parallel, ops
@@ -338,6 +345,137 @@ def main():
         print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
+
+
+def _event_ms(fn, steps, warmup):
+    for _ in range(max(warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def _wall_ms(fn, steps, warmup):
+    for _ in range(max(warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        fn()
+    torch.cuda.synchronize()
+    return (time.perf_counter() - t0) / steps * 1e3
+
+
+def run_config_workload(args):
+    """The benchmark configurations other than the headline, on one GPU, synthetic seeded
+    inputs of the configuration's shapes.  One JSON line; `value` is batch*steps/s of a
+    forward+backward pass of the whole (possibly stacked, bidirectional) network."""
+    import re
+    import haste_b200 as hb
+    from haste_b200 import ops
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
+    steps, warmup = args.steps, max(args.warmup, 3)
+    name = args.workload
+    torch.manual_seed(1234)
+    out = {"workload": name, "unit": UNIT, "steps": steps, "warmup": warmup, "n_gpus": 1,
+           "dtype": args.dtype, "data": "synthetic", "higher_is_better": True}
+
+    def stack_step(net, x):
+        def f():
+            y = net(x)
+            y.backward(torch.ones_like(y))
+        return f
+
+    m = re.fullmatch(r"grid-(lstm|gru)-N(\d+)-H(\d+)", name)
+    if m:
+        cell, N, H = m.group(1), int(m.group(2)), int(m.group(3))
+        T, C = 1000, H
+        G = 4 if cell == "lstm" else 3
+        g = torch.Generator().manual_seed(7)
+        x = torch.randn(T, N, C, generator=g).to(dev, dtype)
+        W = ((torch.rand(C, G * H, generator=g) * 2 - 1) * (6.0 / (C + H)) ** 0.5).to(dev, dtype)
+        R = torch.cat([torch.linalg.qr(torch.randn(H, H, generator=g))[0] for _ in range(G)], 1)
+        R = R.contiguous().to(dev, dtype)
+        bz = torch.zeros(G * H, device=dev, dtype=dtype)
+        h0 = torch.zeros(N, H, device=dev, dtype=dtype)
+        dy = torch.cat([torch.zeros(1, N, H), torch.randn(T, N, H, generator=g)]).to(dev, dtype)
+        dc = torch.zeros(T + 1, N, H, device=dev, dtype=dtype)
+        nomask = torch.empty(0, 0, 0, device=dev, dtype=dtype)
+        if cell == "lstm":
+            def train():
+                h, c, v = ops.lstm_forward(True, 0.0, x, h0, h0, W, R, bz, nomask)
+                ops.lstm_backward(x, W, R, bz, nomask, h, c, v, dy, dc, transposed=False)
+            infer = lambda: ops.lstm_forward(False, 0.0, x, h0, h0, W, R, bz, nomask)
+        else:
+            def train():
+                h, v = ops.gru_forward(True, 0.0, x, h0, W, R, bz, bz, nomask)
+                ops.gru_backward(x, W, R, bz, bz, nomask, h, v, dy, transposed=False)
+            infer = lambda: ops.gru_forward(False, 0.0, x, h0, W, R, bz, bz, nomask)
+        ms, ms_inf = _event_ms(train, steps, warmup), _event_ms(infer, steps, warmup)
+        out.update(metric=f"{cell.upper()} fwd+bwd batch*steps/sec (N={N},H=C={H},T={T})",
+                   value=N * T / (ms * 1e-3), ms_per_step=ms,
+                   forward_only={"value": N * T / (ms_inf * 1e-3), "ms_per_step": ms_inf})
+        if args.ref_cuda:
+            sys.path.insert(0, os.path.join(ROOT, "oracle"))
+            import ref_cuda
+            if ref_cuda.available() and dtype == torch.float32:
+                if cell == "lstm":
+                    def rtrain():
+                        h, c, v = ref_cuda.lstm_forward(True, 0.0, x, h0, h0, W, R, bz, None)
+                        ref_cuda.lstm_backward(x, W, R, bz, None, h, c, v, dy, dc)
+                    rinfer = lambda: ref_cuda.lstm_forward(False, 0.0, x, h0, h0, W, R, bz, None)
+                else:
+                    def rtrain():
+                        h, v = ref_cuda.gru_forward(True, 0.0, x, h0, W, R, bz, bz, None)
+                        ref_cuda.gru_backward(x, W, R, bz, bz, None, h, v, dy)
+                    rinfer = lambda: ref_cuda.gru_forward(False, 0.0, x, h0, W, R, bz, bz, None)
+                r, ri = _wall_ms(rtrain, min(steps, 3), 1), _wall_ms(rinfer, min(steps, 3), 1)
+                out["reference_cuda"] = {"ms_per_step": r, "forward_only_ms": ri,
+                                         "value": N * T / (r * 1e-3),
+                                         "timing": "host wall clock around synchronous calls"}
+            else:
+                out["reference_cuda"] = {"unavailable": "oracle/_ref not built or dtype not fp32"}
+    elif name == "config2":
+        T, N, C, H = 400, 64, 80, 512
+        net = hb.Stack(hb.LayerNormLSTM, C, H, num_layers=3, bidirectional=True, zoneout=0.1,
+                       dropout=0.05).to(dev).to(dtype)
+        net.train()
+        x = torch.randn(T, N, C, device=dev, dtype=dtype, requires_grad=True)
+        ms = _event_ms(stack_step(net, x), steps, warmup)
+        out.update(metric="3-layer bidirectional LayerNormLSTM fwd+bwd batch*steps/sec "
+                          "(N=64,C=80,H=512,T=400, zoneout 0.1, DropConnect 0.05)",
+                   value=N * T / (ms * 1e-3), ms_per_step=ms)
+    elif name in ("config3-indrnn", "config3-lnindrnn"):
+        T, N, C, H = 2000, 128, 1024, 1024
+        cls = hb.IndRNN if name.endswith("-indrnn") and "ln" not in name else hb.LayerNormIndRNN
+        net = hb.Stack(cls, C, H, num_layers=6, zoneout=0.1).to(dev).to(dtype)
+        net.train()
+        x = torch.randn(T, N, C, device=dev, dtype=dtype, requires_grad=True)
+        ms = _event_ms(stack_step(net, x), steps, warmup)
+        out.update(metric=f"6-layer {cls.__name__} fwd+bwd batch*steps/sec (N=128,C=H=1024,T=2000)",
+                   value=N * T / (ms * 1e-3), ms_per_step=ms)
+    elif re.fullmatch(r"config4-N(\d+)", name):
+        N = int(name.split("N")[1])
+        T, C, H = 500, 512, 1024
+        dtype = torch.bfloat16
+        out["dtype"] = "bf16"
+        net = hb.Stack(hb.GRU, C, H, num_layers=4, bidirectional=True).to(dev).to(dtype)
+        net.train()
+        x = torch.randn(T, N, C, device=dev, dtype=dtype, requires_grad=True)
+        ms = _event_ms(stack_step(net, x), steps, warmup)
+        out.update(metric=f"4-layer bidirectional GRU bf16 fwd+bwd batch*steps/sec "
+                          f"(per-GPU N={N},C=512,H=1024,T=500)",
+                   value=N * T / (ms * 1e-3), ms_per_step=ms)
+    else:
+        raise SystemExit(f"unknown workload {name!r}")
+    print(json.dumps(out))
 
 
 def time_reference_cuda(T, N, C, H, x, W, R, b, dy, dc, h0, steps):
