@@ -259,7 +259,8 @@ int haste_b200_layer_norm_indrnn_backward(
 int haste_b200_gemm(int dtype, int M, int N, int K, const void* a, long long a_rs, long long a_cs,
                     const void* b, long long b_rs, long long b_cs, void* c, long long ldc,
                     int accumulate, void* stream) {
-  HB_REQUIRE(dtype == HASTE_B200_F32 || dtype == HASTE_B200_BF16, "dtype");
+  HB_REQUIRE(dtype == HASTE_B200_F32 || dtype == HASTE_B200_BF16 || dtype == HASTE_B200_F16,
+             "dtype");
   HB_REQUIRE(M >= 0 && N >= 0 && K >= 0, "M,N,K");
   HB_REQUIRE(a && b && c, "null pointer");
   GemmDesc g{dtype, dtype, M, N, K, a, a_rs, a_cs, b, b_rs, b_cs, c, ldc, accumulate};

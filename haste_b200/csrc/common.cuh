@@ -2,6 +2,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -56,8 +57,19 @@ template <> struct is_bf16<__nv_bfloat16> { static constexpr bool value = true; 
 
 __device__ __forceinline__ float ld(const float* p) { return *p; }
 __device__ __forceinline__ float ld(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+__device__ __forceinline__ float ld(const __half* p) { return __half2float(*p); }
 __device__ __forceinline__ void st(float* p, float v) { *p = v; }
 __device__ __forceinline__ void st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+__device__ __forceinline__ void st(__half* p, float v) { *p = __float2half_rn(v); }
+
+// The value as the storage type will hold it (what a later load returns).
+template <typename T> __device__ __forceinline__ float round_to_storage(float v) { return v; }
+template <> __device__ __forceinline__ float round_to_storage<__nv_bfloat16>(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+template <> __device__ __forceinline__ float round_to_storage<__half>(float v) {
+  return __half2float(__float2half_rn(v));
+}
 
 // ---------------------------------------------------------------------------
 // Gate math (accurate expf/tanhf: the fp32 parity bar is 1e-4 over long chains).

@@ -97,6 +97,10 @@ int gemm_simt(const GemmDesc& g, cudaStream_t stream) {
     HB_SIMT_LAUNCH(__nv_bfloat16, __nv_bfloat16);
   } else if (g.dtype == HASTE_B200_BF16 && g.dtype_c == HASTE_B200_F32) {
     HB_SIMT_LAUNCH(__nv_bfloat16, float);
+  } else if (g.dtype == HASTE_B200_F16 && g.dtype_c == HASTE_B200_F16) {
+    HB_SIMT_LAUNCH(__half, __half);
+  } else if (g.dtype == HASTE_B200_F16 && g.dtype_c == HASTE_B200_F32) {
+    HB_SIMT_LAUNCH(__half, float);
   } else {
     set_last_error("gemm: unsupported dtype combination %d/%d", g.dtype, g.dtype_c);
     return HASTE_B200_ERR_INVALID;

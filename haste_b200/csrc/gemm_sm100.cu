@@ -146,7 +146,7 @@ struct Params {
   int M, N, K;
   int a_mn_major, b_mn_major;  // 0: K contiguous, 1: M/N contiguous
   int tiles_m, tiles_n, splits, kb_per_split, kb_total;
-  int c_is_bf16, accumulate;   // direct epilogue only
+  int c_is_bf16, accumulate;   // direct epilogue only; c_is_bf16: 0 fp32, 1 bf16, 2 fp16 output
   void* c;
   long long ldc;
   float* partial;              // non-null: write fp32 partial tiles [split][M][N]
@@ -352,23 +352,40 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
                   const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
-                    v[2 * e] += __uint_as_float(ow[e] << 16);
-                    v[2 * e + 1] += __uint_as_float(ow[e] & 0xFFFF0000u);
+                    if (p.c_is_bf16 == 2) {
+                      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ow[e]));
+                      v[2 * e] += f.x;
+                      v[2 * e + 1] += f.y;
+                    } else {
+                      v[2 * e] += __uint_as_float(ow[e] << 16);
+                      v[2 * e + 1] += __uint_as_float(ow[e] & 0xFFFF0000u);
+                    }
                   }
                 }
                 uint32_t w[4];
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                  __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                  w[e] = *reinterpret_cast<uint32_t*>(&t2);
+                  if (p.c_is_bf16 == 2) {
+                    __half2 t2 = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+                    w[e] = *reinterpret_cast<uint32_t*>(&t2);
+                  } else {
+                    __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+                    w[e] = *reinterpret_cast<uint32_t*>(&t2);
+                  }
                 }
                 *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
               }
             } else {
               for (int j = 0; j < 32 && nb + j < p.N; ++j) {
                 float v = __uint_as_float(r[j]);
-                if (p.accumulate) v += __bfloat162float(dst[j]);
-                dst[j] = __float2bfloat16_rn(v);
+                if (p.c_is_bf16 == 2) {
+                  __half* hd = reinterpret_cast<__half*>(dst);
+                  if (p.accumulate) v += __half2float(hd[j]);
+                  hd[j] = __float2half_rn(v);
+                } else {
+                  if (p.accumulate) v += __bfloat162float(dst[j]);
+                  dst[j] = __float2bfloat16_rn(v);
+                }
               }
             }
           } else {
@@ -414,8 +431,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 // same orientation as the source, leading dimension ld_dst (a multiple of 8), planes
 // `plane_stride` elements apart.  One thread converts 4 consecutive elements of a row:
 // a 16-byte load and one 8-byte store per plane when the source allows it.
-template <int PLANES>
-__global__ void split_planes_kernel(const float* __restrict__ src, long long ld_src, int rows,
+template <int PLANES, typename TS>
+__global__ void split_planes_kernel(const TS* __restrict__ src, long long ld_src, int rows,
                                     int cols, __nv_bfloat16* __restrict__ dst, long long ld_dst,
                                     long long plane_stride, int vec_ok) {
   const int quads = (int)(ld_dst / 4);
@@ -425,14 +442,22 @@ __global__ void split_planes_kernel(const float* __restrict__ src, long long ld_
     const long long r = i / quads;
     const int c = (int)(i - r * quads) * 4;
     float x[4] = {0.f, 0.f, 0.f, 0.f};
-    const float* sp = src + r * ld_src + c;
+    const TS* sp = src + r * ld_src + c;
     if (vec_ok && c + 3 < cols) {
-      const float4 f = *reinterpret_cast<const float4*>(sp);
-      x[0] = f.x; x[1] = f.y; x[2] = f.z; x[3] = f.w;
+      if constexpr (sizeof(TS) == 4) {
+        const float4 f = *reinterpret_cast<const float4*>(sp);
+        x[0] = f.x; x[1] = f.y; x[2] = f.z; x[3] = f.w;
+      } else {
+        const uint2 u = *reinterpret_cast<const uint2*>(sp);
+        const __half2 h0 = *reinterpret_cast<const __half2*>(&u.x);
+        const __half2 h1 = *reinterpret_cast<const __half2*>(&u.y);
+        x[0] = __low2float(h0); x[1] = __high2float(h0);
+        x[2] = __low2float(h1); x[3] = __high2float(h1);
+      }
     } else {
 #pragma unroll
       for (int j = 0; j < 4; ++j)
-        if (c + j < cols) x[j] = sp[j];
+        if (c + j < cols) x[j] = ld(sp + j);
     }
     __nv_bfloat16* dp = dst + r * ld_dst + c;
 #pragma unroll
@@ -449,16 +474,28 @@ __global__ void split_planes_kernel(const float* __restrict__ src, long long ld_
   }
 }
 
-int launch_split(const float* src, long long ld_src, int rows, int cols, __nv_bfloat16* dst,
-                 long long ld_dst, long long plane_stride, int planes, int blocks,
-                 cudaStream_t stream) {
-  const int vec_ok = ((ld_src & 3) == 0) && ((reinterpret_cast<uintptr_t>(src) & 15) == 0);
-  if (planes == 3)
-    split_planes_kernel<3><<<blocks, 256, 0, stream>>>(src, ld_src, rows, cols, dst, ld_dst,
-                                                       plane_stride, vec_ok);
+// `half_src`: the source is __half (its 11 significant bits split exactly into two planes).
+int launch_split(const void* src, bool half_src, long long ld_src, int rows, int cols,
+                 __nv_bfloat16* dst, long long ld_dst, long long plane_stride, int planes,
+                 int blocks, cudaStream_t stream) {
+  const int vec_ok = ((ld_src & 3) == 0) &&
+                     ((reinterpret_cast<uintptr_t>(src) & (half_src ? 7 : 15)) == 0);
+  if (half_src) {
+    const __half* hs = static_cast<const __half*>(src);
+    if (planes == 3)
+      split_planes_kernel<3, __half><<<blocks, 256, 0, stream>>>(hs, ld_src, rows, cols, dst, ld_dst,
+                                                                 plane_stride, vec_ok);
+    else
+      split_planes_kernel<2, __half><<<blocks, 256, 0, stream>>>(hs, ld_src, rows, cols, dst, ld_dst,
+                                                                 plane_stride, vec_ok);
+  } else if (planes == 3)
+    split_planes_kernel<3, float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(src), ld_src,
+                                                              rows, cols, dst, ld_dst, plane_stride,
+                                                              vec_ok);
   else
-    split_planes_kernel<2><<<blocks, 256, 0, stream>>>(src, ld_src, rows, cols, dst, ld_dst,
-                                                       plane_stride, vec_ok);
+    split_planes_kernel<2, float><<<blocks, 256, 0, stream>>>(static_cast<const float*>(src), ld_src,
+                                                              rows, cols, dst, ld_dst, plane_stride,
+                                                              vec_ok);
   HB_LAUNCH_OK();
   count_launch(1);
   return HASTE_B200_OK;
@@ -543,7 +580,9 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
   // Small problems are launch-bound either way; keep them on the generic kernel.
   if ((long long)g.M * g.N * g.K < (1LL << 21) || g.M < 32 || g.N < 32)
     return unsupported("problem too small for the tensor-core path");
-  const bool f32 = g.dtype == HASTE_B200_F32;
+  // __half storage takes the split path too: a half splits exactly into two bf16 planes
+  const bool half_src = g.dtype == HASTE_B200_F16;
+  const bool f32 = g.dtype == HASTE_B200_F32 || half_src;
   const bool a_k = g.a_cs == 1, a_m = g.a_rs == 1 && !a_k;
   const bool b_k = g.b_rs == 1, b_n = g.b_cs == 1 && !b_k;
   if (!(a_k || a_m) || !(b_k || b_n)) return unsupported("operand has no unit stride");
@@ -596,10 +635,10 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
     if (!ap || !bp) return unsupported("scratch arena");
     const int blocks = 8 * sms;
     if (!a_pre)
-      HB_TRY(launch_split((const float*)g.a, a_ld_src, (int)a_rows, (int)a_cols, ap, a_ld,
+      HB_TRY(launch_split(g.a, half_src, a_ld_src, (int)a_rows, (int)a_cols, ap, a_ld,
                           a_plane / 2, planes, blocks, stream));
     if (!b_pre)
-      HB_TRY(launch_split((const float*)g.b, b_ld_src, (int)b_rows, (int)b_cols, bp, b_ld,
+      HB_TRY(launch_split(g.b, half_src, b_ld_src, (int)b_rows, (int)b_cols, bp, b_ld,
                           b_plane / 2, planes, blocks, stream));
     A.base = ap; A.plane_stride = a_plane / 2;
     B.base = bp; B.plane_stride = b_plane / 2;
@@ -631,7 +670,7 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
   p.a_mn_major = A.mn_major; p.b_mn_major = B.mn_major;
   p.tiles_m = tiles_m; p.tiles_n = tiles_n; p.splits = splits;
   p.kb_per_split = kb_per_split; p.kb_total = kb_total;
-  p.c_is_bf16 = g.dtype_c == HASTE_B200_BF16;
+  p.c_is_bf16 = g.dtype_c == HASTE_B200_BF16 ? 1 : (g.dtype_c == HASTE_B200_F16 ? 2 : 0);
   p.accumulate = g.accumulate;
   p.c = g.c; p.ldc = g.ldc;
   p.partial = partial;
@@ -660,6 +699,9 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
     if (g.dtype_c == HASTE_B200_BF16)
       splitk_reduce_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
           partial, splits, MN, N, (__nv_bfloat16*)g.c, g.ldc, g.accumulate);
+    else if (g.dtype_c == HASTE_B200_F16)
+      splitk_reduce_kernel<__half><<<blocks, 256, 0, stream>>>(partial, splits, MN, N,
+                                                                (__half*)g.c, g.ldc, g.accumulate);
     else
       splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(partial, splits, MN, N, (float*)g.c,
                                                               g.ldc, g.accumulate);

@@ -121,6 +121,11 @@ template int gru_launch_pointwise_bwd<__nv_bfloat16>(int, int, const __nv_bfloat
                                                      const __nv_bfloat16*, const __nv_bfloat16*,
                                                      float*, __nv_bfloat16*, __nv_bfloat16*,
                                                      const __nv_bfloat16*, cudaStream_t);
+template int gru_launch_pointwise_fwd<__half>(bool, bool, int, int, const __half*, const __half*,
+                                              const __half*, const __half*, const __half*, __half*,
+                                              __half*, float, const __half*, cudaStream_t);
+template int gru_launch_pointwise_bwd<__half>(int, int, const __half*, const __half*, const __half*,
+                                              float*, __half*, __half*, const __half*, cudaStream_t);
 
 namespace {
 
@@ -172,7 +177,8 @@ int gru_backward_stepwise(const GruBwd& a, float* dh_carry, cudaStream_t s) {
 }  // namespace
 
 int gru_forward(const GruFwd& a, cudaStream_t s) {
-  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
+  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16 || a.dtype == HASTE_B200_F16,
+             "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
   if (a.T == 0) return HASTE_B200_OK;  // nothing to do; scratch pointers may be null
   HB_REQUIRE(a.W && a.R && a.bx && a.br && a.h && a.tmp_Wx && a.tmp_Rh, "null pointer");
@@ -191,11 +197,13 @@ int gru_forward(const GruFwd& a, cudaStream_t s) {
   int st_ = a.h_out ? HASTE_B200_ERR_UNSUPPORTED : gru_forward_persistent(a, s);
   if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
   if (a.dtype == HASTE_B200_F32) return gru_forward_stepwise<float>(a, s);
+  if (a.dtype == HASTE_B200_F16) return gru_forward_stepwise<__half>(a, s);
   return gru_forward_stepwise<__nv_bfloat16>(a, s);
 }
 
 int gru_backward(const GruBwd& a, cudaStream_t s) {
-  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
+  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16 || a.dtype == HASTE_B200_F16,
+             "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
   if (a.T == 0) return HASTE_B200_OK;  // nothing to do; scratch pointers may be null
   HB_REQUIRE(a.W && a.R && a.h && a.v && a.dh_new && a.dW && a.dR && a.dbx && a.dbr && a.dh &&
@@ -231,8 +239,9 @@ int gru_backward(const GruBwd& a, cudaStream_t s) {
                     : gru_backward_persistent(a, dh_carry, planes, s);
     have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
     if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
-    st_ = (a.dtype == HASTE_B200_F32) ? gru_backward_stepwise<float>(a, dh_carry, s)
-                                      : gru_backward_stepwise<__nv_bfloat16>(a, dh_carry, s);
+    st_ = (a.dtype == HASTE_B200_F32)   ? gru_backward_stepwise<float>(a, dh_carry, s)
+          : (a.dtype == HASTE_B200_F16) ? gru_backward_stepwise<__half>(a, dh_carry, s)
+                                        : gru_backward_stepwise<__nv_bfloat16>(a, dh_carry, s);
     }
   }
   HB_TRY(st_);

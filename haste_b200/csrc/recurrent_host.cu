@@ -38,7 +38,8 @@ bool pick_geometry(int N, int H, Geometry* g) {
 
 bool supported(int dtype, int N, int H, Geometry* g) {
   if (recurrence_path() == HASTE_B200_PATH_STEPWISE) return false;
-  if (dtype == HASTE_B200_F32 && H > 512) return false;   // R slice must fit the register file
+  // R slice must fit the register file (two bf16 planes for fp32 and fp16 storage, one for bf16)
+  if (dtype != HASTE_B200_BF16 && H > 512) return false;
   if (dtype == HASTE_B200_BF16 && H > 1024) return false;
   return pick_geometry(N, H, g);
 }
@@ -203,6 +204,7 @@ int gru_forward_persistent(const GruFwd& a, cudaStream_t s) {
   const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
   FwdParams p{a.T, a.N, a.H, Hx, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.bx,
               a.br, a.tmp_Wx, a.h, nullptr, a.v, a.zoneout_mask, xbuf, sync, debug_skip()};
+  if (a.dtype == HASTE_B200_F16) return run_fwd_gru_f16(p, g, s);
   return a.dtype == HASTE_B200_F32 ? run_fwd_gru_f32(p, g, s) : run_fwd_gru_bf16(p, g, s);
 }
 
@@ -237,7 +239,9 @@ int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& 
   BwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R, a.h,
               nullptr, const_cast<void*>(a.v), a.dh_new, nullptr, a.dp, a.dq, a.zoneout_mask,
               dh_carry, nullptr, exch, sync, debug_skip(), planes.p, planes.p2, planes.stride};
-  int st_ = a.dtype == HASTE_B200_F32 ? run_bwd_gru_f32(p, g, s) : run_bwd_gru_bf16(p, g, s);
+  int st_ = a.dtype == HASTE_B200_F16   ? run_bwd_gru_f16(p, g, s)
+            : a.dtype == HASTE_B200_F32 ? run_bwd_gru_f32(p, g, s)
+                                        : run_bwd_gru_bf16(p, g, s);
   if (st_ != HASTE_B200_OK) return st_;
   const int H = a.H;
   GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 3 * H, a.dq, 3LL * H, 1, a.R,

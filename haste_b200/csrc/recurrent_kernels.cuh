@@ -443,7 +443,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
           if (p.has_zoneout)
             h_new = p.training ? zoneout<true>(h_new, hp, p.zoneout_prob, m)
                                : zoneout<false>(h_new, hp, p.zoneout_prob, m);
-          if (is_bf16<T>::value) h_new = __bfloat162float(__float2bfloat16_rn(h_new));
+          h_new = round_to_storage<T>(h_new);  // exchange exactly what a later load of h returns
           if (t + 1 < p.T) __stcg(xdst, xword_encode(h_new, tag));  // first: it is on the critical path
           st(hbuf + (long long)(t + 1) * NH + o0, h_new);
           st(cbuf + (long long)(t + 1) * NH + o0, c_new);
@@ -460,7 +460,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
           if (p.has_zoneout)
             h_new = p.training ? zoneout<true>(h_new, hp, p.zoneout_prob, m)
                                : zoneout<false>(h_new, hp, p.zoneout_prob, m);
-          if (is_bf16<T>::value) h_new = __bfloat162float(__float2bfloat16_rn(h_new));
+          h_new = round_to_storage<T>(h_new);  // exchange exactly what a later load of h returns
           if (t + 1 < p.T) __stcg(xdst, xword_encode(h_new, tag));
           st(hbuf + (long long)(t + 1) * NH + o0, h_new);
           if (p.training && vbuf) {
@@ -893,6 +893,8 @@ int run_bwd_lstm_f32(BwdParams& p, const Geometry& g, cudaStream_t s);
 int run_bwd_lstm_bf16(BwdParams& p, const Geometry& g, cudaStream_t s);
 int run_bwd_gru_f32(BwdParams& p, const Geometry& g, cudaStream_t s);
 int run_bwd_gru_bf16(BwdParams& p, const Geometry& g, cudaStream_t s);
+int run_fwd_gru_f16(FwdParams& p, const Geometry& g, cudaStream_t s);
+int run_bwd_gru_f16(BwdParams& p, const Geometry& g, cudaStream_t s);
 
 }  // namespace rec
 }  // namespace hb

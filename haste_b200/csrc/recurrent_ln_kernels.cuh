@@ -535,7 +535,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           if (p.has_zoneout)
             h_new = p.training ? zoneout<true>(h_new, h_reg[mt], p.zoneout_prob, mk[mt])
                                : zoneout<false>(h_new, h_reg[mt], p.zoneout_prob, mk[mt]);
-          if (is_bf16<T>::value) h_new = __bfloat162float(__float2bfloat16_rn(h_new));
+          h_new = round_to_storage<T>(h_new);
           uint32_t* xdst = p.xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul;
           if (ok) {
             if (t + 1 < p.T) __stcg(xdst, hword_encode<SPLIT>(h_new, tag));
@@ -575,7 +575,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           if (p.has_zoneout)
             h_new = p.training ? zoneout<true>(h_new, h_reg[mt], p.zoneout_prob, mk[mt])
                                : zoneout<false>(h_new, h_reg[mt], p.zoneout_prob, mk[mt]);
-          if (is_bf16<T>::value) h_new = __bfloat162float(__float2bfloat16_rn(h_new));
+          h_new = round_to_storage<T>(h_new);
           uint32_t* xdst = p.xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul;
           if (ok) {
             if (t + 1 < p.T) __stcg(xdst, hword_encode<SPLIT>(h_new, tag));

@@ -221,6 +221,8 @@ int add_float_into(int dtype, const float* src, void* dst, size_t n, cudaStream_
   const int blocks = ceil_div((long long)n, 256);
   if (dtype == HASTE_B200_F32)
     add_float_into_kernel<float><<<blocks, 256, 0, stream>>>(src, (float*)dst, n);
+  else if (dtype == HASTE_B200_F16)
+    add_float_into_kernel<__half><<<blocks, 256, 0, stream>>>(src, (__half*)dst, n);
   else
     add_float_into_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(src, (__nv_bfloat16*)dst, n);
   HB_LAUNCH_OK();
@@ -238,6 +240,9 @@ int colsum(int in_dtype, const void* in, long long ld_, int rows, int width, int
   if (in_dtype == HASTE_B200_F32)
     colsum_stage1<float><<<g1, CS_COLS, 0, stream>>>((const float*)in, ld_, rows, width, chunks,
                                                       scratch);
+  else if (in_dtype == HASTE_B200_F16)
+    colsum_stage1<__half><<<g1, CS_COLS, 0, stream>>>((const __half*)in, ld_, rows, width, chunks,
+                                                       scratch);
   else
     colsum_stage1<__nv_bfloat16><<<g1, CS_COLS, 0, stream>>>((const __nv_bfloat16*)in, ld_, rows,
                                                               width, chunks, scratch);
@@ -245,6 +250,9 @@ int colsum(int in_dtype, const void* in, long long ld_, int rows, int width, int
   if (out_dtype == HASTE_B200_F32)
     colsum_stage2<float><<<ceil_div(width, 128), 128, 0, stream>>>(scratch, width, chunks,
                                                                     (float*)out, accumulate);
+  else if (out_dtype == HASTE_B200_F16)
+    colsum_stage2<__half><<<ceil_div(width, 128), 128, 0, stream>>>(scratch, width, chunks,
+                                                                     (__half*)out, accumulate);
   else
     colsum_stage2<__nv_bfloat16><<<ceil_div(width, 128), 128, 0, stream>>>(
         scratch, width, chunks, (__nv_bfloat16*)out, accumulate);
@@ -258,6 +266,8 @@ int to_float(int dtype, const void* src, float* dst, size_t n, cudaStream_t stre
   const int blocks = ceil_div((long long)n, 256);
   if (dtype == HASTE_B200_F32)
     to_float_kernel<float><<<blocks, 256, 0, stream>>>((const float*)src, dst, n);
+  else if (dtype == HASTE_B200_F16)
+    to_float_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)src, dst, n);
   else
     to_float_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, dst, n);
   HB_LAUNCH_OK();
@@ -270,6 +280,8 @@ int from_float(int dtype, const float* src, void* dst, size_t n, cudaStream_t st
   const int blocks = ceil_div((long long)n, 256);
   if (dtype == HASTE_B200_F32)
     from_float_kernel<float><<<blocks, 256, 0, stream>>>(src, (float*)dst, n);
+  else if (dtype == HASTE_B200_F16)
+    from_float_kernel<__half><<<blocks, 256, 0, stream>>>(src, (__half*)dst, n);
   else
     from_float_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(src, (__nv_bfloat16*)dst, n);
   HB_LAUNCH_OK();

@@ -68,6 +68,6 @@ struct ProfScope {
   ~ProfScope() { if (on) profile_mark(phase, false, s); }
 };
 
-inline size_t dtype_size(int dtype) { return dtype == HASTE_B200_BF16 ? 2 : 4; }
+inline size_t dtype_size(int dtype) { return dtype == HASTE_B200_F32 ? 4 : 2; }
 
 }  // namespace hb

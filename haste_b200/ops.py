@@ -19,7 +19,10 @@ def _dtype(t):
         return _C.F32
     if t.dtype == torch.bfloat16:
         return _C.BF16
-    raise TypeError(f"haste_b200 supports float32 and bfloat16 tensors, got {t.dtype}")
+    if t.dtype == torch.float16:
+        return _C.F16  # accepted by the GRU ops and gemm only; other entry points reject it
+    raise TypeError(f"haste_b200 supports float32, bfloat16 and (GRU only) float16 tensors, "
+                    f"got {t.dtype}")
 
 
 def _check(*tensors):

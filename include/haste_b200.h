@@ -8,8 +8,9 @@
  *     Tensors are dense, row-major, rightmost index fastest
  *     (T steps, N batch, C input size, H hidden size), as in lib/haste.h:18-26.
  *   - `dtype` selects the storage type of EVERY tensor of the call:
- *     HASTE_B200_F32 (float) or HASTE_B200_BF16 (__nv_bfloat16; all arithmetic,
- *     carries and accumulators stay fp32).
+ *     HASTE_B200_F32 (float), HASTE_B200_BF16 (__nv_bfloat16; all arithmetic,
+ *     carries and accumulators stay fp32) or, for the GRU entry points and
+ *     haste_b200_gemm, HASTE_B200_F16 (__half, same rule).
  *   - `h`/`c` are [T+1,N,H]; slot 0 holds the initial state and is filled by the
  *     caller.  Gate order: i,g,f,o (LSTM), z,r,g (GRU).
  *   - Outputs documented as "accumulated" are added to and must be zeroed by the
@@ -40,7 +41,10 @@ enum {
   HASTE_B200_ERR_UNSUPPORTED = 4  /* shape outside what a kernel supports */
 };
 
-enum { HASTE_B200_F32 = 0, HASTE_B200_BF16 = 1 };
+/* HASTE_B200_F16 (__half storage, fp32-grade arithmetic on exact bf16 (hi, lo) splits of the
+ * stored values): GRU entry points and haste_b200_gemm only - the one reduced-precision type
+ * the reference ships (lib/gru_forward_gpu.cu.cc:373). */
+enum { HASTE_B200_F32 = 0, HASTE_B200_BF16 = 1, HASTE_B200_F16 = 2 };
 
 const char* haste_b200_last_error(void);
 const char* haste_b200_version(void);

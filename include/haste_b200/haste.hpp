@@ -15,6 +15,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <cuda_runtime_api.h>
 
 #include <stdexcept>
@@ -31,6 +32,8 @@ namespace detail {
 template <typename T> struct dtype_of;
 template <> struct dtype_of<float> { static constexpr int value = HASTE_B200_F32; };
 template <> struct dtype_of<__nv_bfloat16> { static constexpr int value = HASTE_B200_BF16; };
+// __half: the gru classes only (as in the reference, lib/gru_forward_gpu.cu.cc:373)
+template <> struct dtype_of<__half> { static constexpr int value = HASTE_B200_F16; };
 inline void check(int status) {
   if (status != HASTE_B200_OK)
     throw std::runtime_error(std::string("haste_b200: ") + haste_b200_last_error());

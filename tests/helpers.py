@@ -12,6 +12,9 @@ GOLDEN_DIR = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 # parity bars (max|a-b| / max|b|): fp32 storage and bf16 storage with fp32 accumulate
 TOL_F32 = 1e-4
 TOL_BF16 = 2e-2
+# float16 storage (GRU only): the stored values are used exactly and accumulated in fp32, so
+# what remains is the rounding of stored results to 11 significant bits along the recurrence
+TOL_F16 = 5e-3
 # LayerNormLSTM with bf16 storage: the tensors the interface stores in bf16 (x.W, LN(x.W), h)
 # are rounded whatever the arithmetic, and the three LayerNorms amplify that rounding.  An
 # exact float64 evaluation that only rounds those stored tensors is already 2e-2 .. 4.5e-2

@@ -31,6 +31,39 @@ def test_cpp_api_compiles_and_links(binary):
     assert os.path.exists(binary)
 
 
+BENCH_SRC = os.path.join(ROOT, "haste_b200", "examples", "benchmark_rnn.cu")
+
+
+@pytest.fixture(scope="module")
+def bench_binary(tmp_path_factory):
+    from haste_b200 import build
+    lib = build.build()
+    out = str(tmp_path_factory.mktemp("cppbench") / "benchmark_rnn")
+    libdir = os.path.dirname(lib)
+    r = subprocess.run([NVCC, "-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-I",
+                        os.path.join(ROOT, "include"), BENCH_SRC, "-o", out, "-L", libdir,
+                        "-lhaste_b200", "-Xlinker", "-rpath=" + libdir],
+                       capture_output=True, text=True)
+    assert r.returncode == 0, r.stderr
+    return out
+
+
+def test_cpp_benchmark_driver_compiles(bench_binary):
+    assert os.path.exists(bench_binary)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("extra", [[], ["--inference"], ["--cell", "gru"]])
+def test_cpp_benchmark_driver_prints_the_reference_csv(bench_binary, extra):
+    r = subprocess.run([bench_binary, "--point", "32,128,64", "--sample_size", "2",
+                        "--time_steps", "20"] + extra, capture_output=True, text=True, timeout=120)
+    assert r.returncode == 0, r.stderr
+    rows = [l for l in r.stdout.splitlines() if l and not l.startswith("#")]
+    assert len(rows) == 1
+    n, h, c, ms = rows[0].split(",")
+    assert (int(n), int(h), int(c)) == (32, 128, 64) and 0.0 < float(ms) < 1000.0
+
+
 def _fill(n, phase, scale):
     return torch.tensor([scale * math.sin(0.37 * i + phase) for i in range(n)], dtype=torch.float32)
 

@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import haste_oracle as oracle
-from helpers import (TOL_BF16, TOL_BF16_LN_LSTM, TOL_F32, assert_close, golden_files, load_golden, run_cuda)
+from helpers import (TOL_BF16, TOL_BF16_LN_LSTM, TOL_F16, TOL_F32, assert_close, golden_files, load_golden, run_cuda)
 
 pytestmark = pytest.mark.gpu
 
@@ -148,3 +148,36 @@ def test_persistent_path_bf16(cell, shape):
     _C.sync_check(torch.cuda.current_stream().cuda_stream)
     _compare(cell, dq, out, grads, ref_out, ref_grads,
              TOL_BF16_LN_LSTM if cell == "layer_norm_lstm" else TOL_BF16)
+
+
+@pytest.mark.parametrize("path", ["stepwise", "persistent"])
+@pytest.mark.parametrize("shape", [(6, 3, 16, 24), (16, 32, 64, 64), (20, 64, 64, 512), (6, 130, 48, 512)],
+                         ids=lambda s: "T%d_N%d_C%d_H%d" % s)
+def test_gru_float16_against_oracle(shape, path):
+    """The reference's one reduced-precision type (half GRU): __half storage, oracle on the
+    fp16-rounded inputs."""
+    from haste_b200 import _C
+    T, N, C, H = shape
+    zoneout = 0.2
+    d = oracle.make_inputs("gru", T, N, C, H, seed=31 + H, zoneout=zoneout)
+    dq = {k: (v.to(torch.float16).to(torch.float64) if v is not None else None)
+          for k, v in d.items()}
+    ref_out, ref_grads = oracle.forward_backward("gru", dq, zoneout=zoneout)
+    _C.set_recurrence_path(_C.PATH_STEPWISE if path == "stepwise" else _C.PATH_AUTO)
+    try:
+        out, grads = run_cuda("gru", dq, zoneout=zoneout, dtype=torch.float16)
+        _C.sync_check(torch.cuda.current_stream().cuda_stream)
+    finally:
+        _C.set_recurrence_path(_C.PATH_AUTO)
+    _compare("gru", dq, out, grads, ref_out, ref_grads, TOL_F16)
+
+
+def test_float16_is_rejected_outside_the_gru():
+    from haste_b200 import ops
+    h = torch.zeros(2, 4, device="cuda", dtype=torch.float16)
+    x = torch.zeros(3, 2, 3, device="cuda", dtype=torch.float16)
+    W = torch.zeros(3, 16, device="cuda", dtype=torch.float16)
+    R = torch.zeros(4, 16, device="cuda", dtype=torch.float16)
+    b = torch.zeros(16, device="cuda", dtype=torch.float16)
+    with pytest.raises(RuntimeError):
+        ops.lstm_forward(True, 0.0, x, h, h, W, R, b, torch.empty(0, 0, 0, device="cuda", dtype=torch.float16))
