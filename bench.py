@@ -291,8 +291,8 @@ def main():
     # steps; the summary is profiles/rec_kernels_and_gemm_T200_full_capture.md).  Every
     # step touches its own slice of the activations once, so a launch's traffic is this
     # times T.
-    ncu_bytes_per_step = {"recurrence_fwd": (109.374208e6 + 104.630528e6) / 200,
-                          "recurrence_bwd": (188.176896e6 + 167.613184e6) / 200}
+    ncu_bytes_per_step = {"recurrence_fwd": (109.377024e6 + 108.569600e6) / 200,
+                          "recurrence_bwd": (188.500992e6 + 168.230144e6) / 200}
     dom = max(phases, key=phases.get)
     if dom in alg_bytes:
         ach = alg_bytes[dom] / (phases[dom] * 1e-3) / 1e9
