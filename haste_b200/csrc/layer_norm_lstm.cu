@@ -229,9 +229,16 @@ int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
   GemmDesc g{a.dtype, a.dtype, (int)TN, 4 * a.H, a.C, a.x, a.C, 1, a.W, 4LL * a.H, 1, a.act_Wx,
              4LL * a.H, 0};
   g.precise = 1;
-  HB_TRY(gemm(g, s));
-  HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma_Wx, nullptr, a.act_Wx, a.act_Wx_norm,
-                            a.cache_Wx, s));
+  {
+    ProfScope p(PH_PROJ, s);
+    HB_TRY(gemm(g, s));
+  }
+  {
+    ProfScope p(PH_OTHER, s);
+    HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma_Wx, nullptr, a.act_Wx,
+                              a.act_Wx_norm, a.cache_Wx, s));
+  }
+  ProfScope prec(PH_REC_FWD, s);
   {
     const int st_ = layer_norm_lstm_forward_persistent(a, s);
     if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
@@ -277,6 +284,7 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
 
   // Persistent recurrence first; it adds its LayerNorm parameter gradients into `acc`.
   HB_CUDA_OK(cudaMemsetAsync(acc, 0, 6 * H * sizeof(float), s));
+  if (profile_enabled()) profile_mark(PH_REC_BWD, true, s);
   int st_ = layer_norm_lstm_backward_persistent(a, dh_carry, dc_carry, acc, GradPlanes{}, s);
   bool use_acc = st_ == HASTE_B200_OK;
   if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
@@ -294,6 +302,7 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
              : backward_steps<float>(a, dh_carry, dc_carry, dgamma1, dgamma_h, dbeta_h,
                                      HASTE_B200_F32, lns, s);
   }
+  if (profile_enabled()) profile_mark(PH_REC_BWD, false, s);
   HB_TRY(st_);
   if (use_acc) {
     HB_TRY(add_float_into(a.dtype, acc, a.dgamma_Rh, 4 * H, s));
@@ -303,24 +312,36 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
   HB_TRY(from_float(a.dtype, dh_carry, a.dh, NH, s));
   HB_TRY(from_float(a.dtype, dc_carry, a.dc, NH, s));
 
-  // act_Wx_norm now holds the gradient w.r.t. (LN1(x.W) + LN2(h.R) + b).
-  HB_TRY(colsum(a.dtype, a.act_Wx_norm, 4LL * H, (int)TN, 4 * H, a.dtype, a.db, 1, cs, s));
-  // LayerNorm 1 backward over all steps: act_Wx <- d/d(x.W).
-  HB_TRY(layer_norm_backward(a.dtype, (int)TN, 4 * H, a.gamma_Wx, a.act_Wx, a.act_Wx_norm, a.act_Wx,
-                             a.dtype, a.dgamma_Wx, nullptr, a.cache_Wx, lns, s));
+  {
+    ProfScope p(PH_OTHER, s);
+    // act_Wx_norm now holds the gradient w.r.t. (LN1(x.W) + LN2(h.R) + b).
+    HB_TRY(colsum(a.dtype, a.act_Wx_norm, 4LL * H, (int)TN, 4 * H, a.dtype, a.db, 1, cs, s));
+    // LayerNorm 1 backward over all steps: act_Wx <- d/d(x.W).
+    HB_TRY(layer_norm_backward(a.dtype, (int)TN, 4 * H, a.gamma_Wx, a.act_Wx, a.act_Wx_norm,
+                               a.act_Wx, a.dtype, a.dgamma_Wx, nullptr, a.cache_Wx, lns, s));
+  }
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gw{a.dtype, a.dtype, C, 4 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.act_Wx,
               4LL * H, 1, a.dW, 4LL * H, 1};
   gw.precise = 1;
-  HB_TRY(gemm(gw, s));
+  {
+    ProfScope p(PH_WGRAD, s);
+    HB_TRY(gemm(gw, s));
+  }
   GemmDesc gr{a.dtype, a.dtype, H, 4 * H, (int)TN, a.h, 1, H, a.act_Rh, 4LL * H, 1, a.dR,
               4LL * H, 1};
   gr.precise = 1;
-  HB_TRY(gemm(gr, s));
+  {
+    ProfScope p(PH_WGRAD, s);
+    HB_TRY(gemm(gr, s));
+  }
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 4 * H, a.act_Wx, 4LL * H, 1, a.W, tr ? C : 1,
               tr ? 1 : 4LL * H, a.dx, C, 0};
   gx.precise = 1;
-  HB_TRY(gemm(gx, s));
+  {
+    ProfScope p(PH_DGRAD, s);
+    HB_TRY(gemm(gx, s));
+  }
   return HASTE_B200_OK;
 }
 

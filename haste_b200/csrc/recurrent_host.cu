@@ -98,8 +98,8 @@ exchange_probe_kernel(int T, int N, int Hx, int nHS, uint32_t* xbuf, Sync sync) 
     const uint32_t tag = (((uint32_t)t >> 1) & 1u) ^ 1u;
     const int n = n0 + nl;
     if (n < N && u0 + ul < Hx)
-      __stcg(xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul,
-             xword_encode(carry * 0.5f + 0.25f, tag));
+      publish_u32(xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul,
+                  xword_encode(carry * 0.5f + 0.25f, tag));
     const uint32_t wtag = tag << 30;
     const uint32_t* xsrc = xbuf + (size_t)(t & 1) * N * Hx;
     uint4 w[CPL];
@@ -265,7 +265,7 @@ int layer_norm_lstm_forward_persistent(const LnLstmFwd& a, cudaStream_t s) {
   LnFwdParams p{a.T, a.N, a.H, Hx, g.nHS, g.MT, a.training, zo ? 1 : 0, a.zoneout_prob, a.R, a.b,
                 nullptr, a.act_Wx_norm, a.gamma_Rh, a.gamma_h, a.beta_h, a.act_Wx_norm, a.act_Rh, a.cache_Rh,
                 a.act_c_norm, a.cache_c, a.h, a.c, a.zoneout_mask, words,
-                words + ((xwords + 63) & ~size_t(63)), sync};
+                words + ((xwords + 63) & ~size_t(63)), sync, debug_skip()};
   return a.dtype == HASTE_B200_F32 ? run_ln_fwd_f32(p, g, s) : run_ln_fwd_bf16(p, g, s);
 }
 
@@ -292,7 +292,7 @@ int layer_norm_lstm_backward_persistent(const LnLstmBwd& a, float* dh_carry, flo
                 a.cache_Rh, a.act_c_norm,
                 a.cache_c, a.dh_new, a.dc_new, a.zoneout_mask, dh_carry, dc_carry, part,
                 part + (size_t)prow * 4 * H, part + (size_t)prow * 5 * H, words, words + ewords,
-                sync, planes.p, planes.p2, planes.stride};
+                sync, planes.p, planes.p2, planes.stride, debug_skip()};
   int st_ = a.dtype == HASTE_B200_F32 ? run_ln_bwd_f32(p, g, s) : run_ln_bwd_bf16(p, g, s);
   if (st_ != HASTE_B200_OK) return st_;
   HB_TRY(colsum(HASTE_B200_F32, part, 4LL * H, prow, 4 * H, HASTE_B200_F32, acc, 1, cs, s));

@@ -143,6 +143,20 @@ __device__ __forceinline__ uint4 ld_relaxed_u32x4(const uint32_t* p) {
   return v;
 }
 
+__device__ __forceinline__ void prefetch_l2(const void* p) {
+  asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+}
+
+// Publishing stores of the exchange: `volatile` with a memory clobber, so that the compiler
+// issues them exactly where they are written - ahead of the bulky activation stores of the same
+// stage, never behind them.  .cg: the word goes to L2, where the consumers poll.
+__device__ __forceinline__ void publish_u32(uint32_t* p, uint32_t v) {
+  asm volatile("st.global.cg.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void publish_u32x2(uint32_t* p, uint32_t a, uint32_t b) {
+  asm volatile("st.global.cg.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+
 // Exchange word: bits 0-15 hi (bf16), bits 16-31 lo (bf16) with bit 30 replaced by `tag`.
 __device__ __forceinline__ uint32_t xword_encode(float x, uint32_t tag) {
   float hi, lo;
@@ -291,6 +305,13 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
         wxr[mt][g] = ok ? ld(wx + ((long long)t * N + n) * GH + g * H + u0 + ul) : 0.f;
       mk[mt] = (ok && p.has_zoneout && p.training)
                    ? ld(mask + (long long)t * NH + (long long)n * H + u0 + ul) : 0.f;
+      if (MTMAX == 1 && ok && t + 1 < p.T && !(p.dbg & 512)) {  // next step inputs: into L2 now
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+          prefetch_l2(wx + ((long long)(t + 1) * N + n) * GH + g * H + u0 + ul);
+        if (p.has_zoneout && p.training)
+          prefetch_l2(mask + (long long)(t + 1) * NH + (long long)n * H + u0 + ul);
+      }
     }
 
     for (int mt = 0; mt < p.MT; ++mt) {
@@ -444,7 +465,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
             h_new = p.training ? zoneout<true>(h_new, hp, p.zoneout_prob, m)
                                : zoneout<false>(h_new, hp, p.zoneout_prob, m);
           h_new = round_to_storage<T>(h_new);  // exchange exactly what a later load of h returns
-          if (t + 1 < p.T) __stcg(xdst, xword_encode(h_new, tag));  // first: it is on the critical path
+          if (t + 1 < p.T) publish_u32(xdst, xword_encode(h_new, tag));  // first: it is on the critical path
           st(hbuf + (long long)(t + 1) * NH + o0, h_new);
           st(cbuf + (long long)(t + 1) * NH + o0, c_new);
           if (p.training) {
@@ -461,7 +482,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
             h_new = p.training ? zoneout<true>(h_new, hp, p.zoneout_prob, m)
                                : zoneout<false>(h_new, hp, p.zoneout_prob, m);
           h_new = round_to_storage<T>(h_new);  // exchange exactly what a later load of h returns
-          if (t + 1 < p.T) __stcg(xdst, xword_encode(h_new, tag));
+          if (t + 1 < p.T) publish_u32(xdst, xword_encode(h_new, tag));
           st(hbuf + (long long)(t + 1) * NH + o0, h_new);
           if (p.training && vbuf) {
             T* vt = vbuf + ((long long)t * N + n) * 4 * H + u0 + ul;
@@ -472,7 +493,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
         for (int k = 0; k < MTMAX; ++k)
           if (k == mt) { h_reg[k] = h_new; c_reg[k] = c_new; }
       } else if (n < N && unit_pad && t + 1 < p.T) {
-        __stcg(xdst, xword_encode(0.0f, tag));
+        publish_u32(xdst, xword_encode(0.0f, tag));
       }
     }
   }
@@ -591,6 +612,20 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
       } else {
         hprev[mt] = ok ? ld(hbuf + (long long)t * NH + o0) : 0.f;
         cprev[mt] = cnew[mt] = dcv[mt] = 0.f;
+      }
+      // Ask L2 for the next step's inputs now, so that their loads return from L2 and do not
+      // occupy the SM's miss queue for an HBM round trip while the exchange polls need it.
+      if (MTMAX == 1 && ok && t > 0 && !(p.dbg & 512)) {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) prefetch_l2(vt - (long long)N * 4 * H + g * H);
+        prefetch_l2(dhn + (long long)t * NH + o0);
+        if (p.has_zoneout) prefetch_l2(mask + (long long)(t - 1) * NH + o0);
+        if (G == 4) {
+          prefetch_l2(cbuf + (long long)(t - 1) * NH + o0);
+          prefetch_l2(dcn + (long long)t * NH + o0);
+        } else {
+          prefetch_l2(hbuf + (long long)(t - 1) * NH + o0);
+        }
       }
     }
 
@@ -782,10 +817,10 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
           if (j < p.nHS * U) {
             const int dest = j / U, uj = j % U;
             uint32_t* d = dstbase + ((size_t)dest * p.nHS + hs) * blk + (size_t)(mt * 16) * U + uj;
-            __stcg(reinterpret_cast<uint2*>(d + (size_t)gq * U),
-                   make_uint2(fword_encode(acc[nt][0], tag), fword_encode(acc[nt][1], tag)));
-            __stcg(reinterpret_cast<uint2*>(d + (size_t)(gq + 8) * U),
-                   make_uint2(fword_encode(acc[nt][2], tag), fword_encode(acc[nt][3], tag)));
+            publish_u32x2(d + (size_t)gq * U, fword_encode(acc[nt][0], tag),
+                          fword_encode(acc[nt][1], tag));
+            publish_u32x2(d + (size_t)(gq + 8) * U, fword_encode(acc[nt][2], tag),
+                          fword_encode(acc[nt][3], tag));
           }
         }
       }

@@ -49,6 +49,7 @@ struct LnFwdParams {
   uint32_t* xbuf;       // [2][N][Hx] tagged h words
   uint32_t* sbuf;       // [2 stats][2 parity][nBS][rows][nHS][2] tagged statistic pairs
   Sync sync;
+  int dbg = 0;          // timing experiments only (wrong results): 1 no h wait, 2 no MMA, 4 no statistic waits
 };
 
 struct LnBwdParams {
@@ -80,6 +81,7 @@ struct LnBwdParams {
   __nv_bfloat16* gpl;     // optional bf16 planes of d(x.W-side gate gradient) (dv)
   __nv_bfloat16* gpl2;    // optional bf16 planes of d(h.R)
   long long gpl_stride;
+  int dbg = 0;            // timing experiments only (wrong results): 1 no dh wait, 2 no MMA, 4 no statistic waits
 };
 
 // Statistics, partial gradients and (with fp32 storage) h travel as tagged fp32 words
@@ -114,8 +116,7 @@ __device__ __forceinline__ float row16_sum(float v) {
 // stat_publish: lane ul == 0 of the row's 16-thread group stores this CTA's pair (a, b).
 __device__ __forceinline__ void stat_publish(uint32_t* area, int row, int hs, int nHS,
                                              uint32_t tag, float a, float b) {
-  __stcg(reinterpret_cast<uint2*>(area + ((size_t)row * nHS + hs) * 2),
-         make_uint2(fword_encode(a, tag), fword_encode(b, tag)));
+  publish_u32x2(area + ((size_t)row * nHS + hs) * 2, fword_encode(a, tag), fword_encode(b, tag));
 }
 // stat_collect: thread ul of the group fetches the pairs of sources ul, ul+16, ul+32, ul+48
 // (zero where there is no such source, or when `active` is false); the caller combines them
@@ -309,6 +310,13 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
         wxr[mt][g] = ok ? ld(wx + ((long long)t * N + n) * GH + g * H + u0 + ul) : 0.f;
       mk[mt] = (ok && p.has_zoneout && p.training)
                    ? ld(mask + (long long)t * NH + (long long)n * H + u0 + ul) : 0.f;
+      if (MTMAX == 1 && ok && t + 1 < p.T && !(p.dbg & 512)) {  // next step inputs: into L2 now
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+          prefetch_l2(wx + ((long long)(t + 1) * N + n) * GH + g * H + u0 + ul);
+        if (p.has_zoneout && p.training)
+          prefetch_l2(mask + (long long)(t + 1) * NH + (long long)n * H + u0 + ul);
+      }
     }
 
     // ---- stage A: step product, pre-norm h.R saved, its row statistics published
@@ -348,7 +356,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
                     make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
               }
             }
-          } else if (alive) {
+          } else if (alive && !(p.dbg & 1)) {
             const uint32_t want = (((uint32_t)(t - 1) >> 1) & 1u) ^ 1u;
             const uint32_t* xsrc = p.xbuf + (size_t)((t - 1) & 1) * N * Hx;
             uint4 w[CPL];
@@ -409,7 +417,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < KSW; ++ks) {
+        for (int ks = 0; ks < ((p.dbg & 2) ? 0 : KSW); ++ks) {
           const int row = lane & 15;
           const int kcol = warp * KW + ks * 16 + (lane >> 4) * 8;
           uint32_t a0[4], a1[4], a2[4];
@@ -488,7 +496,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           const int n = n0 + mt * 16 + nl;
           const bool ok = n < N && unit_ok;
           float sa[4], sb[4], mean1, inv1;
-          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 27))
+          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 27))
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           chan_combine(sa, sb, ul, p.nHS, GH, COLS, mean1, inv1);
           float pre[G];
@@ -527,7 +535,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           const int n = n0 + mt * 16 + nl;
           const bool ok = n < N && unit_ok;
           float sa[4], sb[4], mean3, inv3;
-          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 28))
+          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 28))
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           chan_combine(sa, sb, ul, p.nHS, H, U, mean3, inv3);
           const float c_norm = (cnew[mt] - mean3) * inv3 * gh + bh;
@@ -538,14 +546,14 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           h_new = round_to_storage<T>(h_new);
           uint32_t* xdst = p.xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul;
           if (ok) {
-            if (t + 1 < p.T) __stcg(xdst, hword_encode<SPLIT>(h_new, tag));
+            if (t + 1 < p.T) publish_u32(xdst, hword_encode<SPLIT>(h_new, tag));
             const long long o0 = (long long)n * H + u0 + ul;
             st(hbuf + (long long)(t + 1) * NH + o0, h_new);
             st(cnbuf + (long long)t * NH + o0, c_norm);
             h_reg[mt] = h_new;
             c_reg[mt] = cnew[mt];
           } else if (n < N && unit_pad && t + 1 < p.T) {
-            __stcg(xdst, hword_encode<SPLIT>(0.0f, tag));
+            publish_u32(xdst, hword_encode<SPLIT>(0.0f, tag));
           }
           if (hs == 0 && ul == 0 && n < N) {
             st(cache3 + ((long long)t * N + n) * 2, mean3);
@@ -561,7 +569,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           const int n = n0 + mt * 16 + nl;
           const bool ok = n < N && unit_ok;
           float sa[4], sb[4], mean1, inv1;
-          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 27))
+          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 27))
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           chan_combine(sa, sb, ul, p.nHS, GH, COLS, mean1, inv1);
           float rn[G];
@@ -578,7 +586,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           h_new = round_to_storage<T>(h_new);
           uint32_t* xdst = p.xbuf + (size_t)(t & 1) * N * Hx + (size_t)n * Hx + u0 + ul;
           if (ok) {
-            if (t + 1 < p.T) __stcg(xdst, hword_encode<SPLIT>(h_new, tag));
+            if (t + 1 < p.T) publish_u32(xdst, hword_encode<SPLIT>(h_new, tag));
             st(hbuf + (long long)(t + 1) * NH + (long long)n * H + u0 + ul, h_new);
             if (p.training && vbuf) {
               T* vt = vbuf + ((long long)t * N + n) * 4 * H + u0 + ul;
@@ -586,7 +594,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
             }
             h_reg[mt] = h_new;
           } else if (n < N && unit_pad && t + 1 < p.T) {
-            __stcg(xdst, hword_encode<SPLIT>(0.0f, tag));
+            publish_u32(xdst, hword_encode<SPLIT>(0.0f, tag));
           }
           if (hs == 0 && ul == 0 && n < N) {
             st(cache1 + ((long long)t * N + n) * 2, mean1);
@@ -740,10 +748,29 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
       } else {
         hprev[mt] = ok ? ld(hbuf + (long long)t * NH + o0) : 0.f;
       }
+      // Ask L2 for the next step's inputs now: when that step loads them they come back from
+      // L2 in a fraction of the HBM latency and do not sit in the SM's miss queue while the
+      // polling loads of the exchange need it.
+      if (MTMAX == 1 && ok && t > 0 && !(p.dbg & 512)) {
+        const long long w1 = w0 - (long long)N * GH, v1 = v0 - (long long)N * 4 * H;
+#pragma unroll
+        for (int g = 0; g < 4; ++g) prefetch_l2(vbuf + v1 + g * H);
+#pragma unroll
+        for (int g = 0; g < G; ++g) prefetch_l2(rhbuf + w1 + g * H);
+        prefetch_l2(dhn + (long long)t * NH + o0);
+        if (p.has_zoneout) prefetch_l2(mask + (long long)(t - 1) * NH + o0);
+        if constexpr (G == 4) {
+          prefetch_l2(dcn + (long long)t * NH + o0);
+          prefetch_l2(cbuf + (long long)(t - 1) * NH + o0);
+          prefetch_l2(cnbuf + (long long)(t - 1) * NH + o0);
+        } else {
+          prefetch_l2(hbuf + (long long)(t - 1) * NH + o0);
+        }
+      }
     }
 
     // ---- recurrent part of dh_t: the partials published at the previous step
-    if (ti > 0) {
+    if (ti > 0 && !(p.dbg & 1)) {
       const uint32_t want = (((uint32_t)(ti - 1) >> 1) & 1u) ^ 1u;
       const uint32_t* src =
           p.exch + ((((size_t)((ti - 1) & 1) * nBS + bs) * p.nHS + hs) * p.nHS) * blk;
@@ -797,7 +824,12 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
       }
     }
     if (!alive) *reinterpret_cast<volatile int*>(&s_abort) = 1;
-    alive = true;  // from here on failures only mark s_abort; the barrier below decides
+    alive = true;  // from here on failures only mark s_abort; the barriers below decide
+    // All warps leave the wait above together.  Without this barrier the warps that are still
+    // polling (32 KB of loads per round and CTA) keep the SM's load/store path full, and the
+    // small statistic stores and loads of the warps that are already through queue up behind
+    // them: measured 12.5 -> 9.8 us per step.
+    if (__syncthreads_or(*reinterpret_cast<volatile int*>(&s_abort))) { alive = false; break; }
 
     float dgate[MTMAX][G];
     if constexpr (G == 4) {
@@ -837,7 +869,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
           const int n = n0 + mt * 16 + nl;
           const bool ok = n < N && unit_ok;
           float sa[4], sb[4];
-          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 38))
+          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 38))
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           const float S1 = row16_sum((sa[0] + sa[1]) + (sa[2] + sa[3]));
           const float S2 = row16_sum((sb[0] + sb[1]) + (sb[2] + sb[3]));
@@ -940,7 +972,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
         const int n = n0 + mt * 16 + nl;
         const bool ok = n < N && unit_ok;
         float sa[4], sb[4];
-        if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N, sa, sb, p.sync, &s_abort, 39))
+        if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 39))
           *reinterpret_cast<volatile int*>(&s_abort) = 1;
         const float S1 = row16_sum((sa[0] + sa[1]) + (sa[2] + sa[3]));
         const float S2 = row16_sum((sb[0] + sb[1]) + (sb[2] + sb[3]));
@@ -979,7 +1011,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
 #pragma unroll
         for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
+        for (int ks = 0; ks < ((p.dbg & 2) ? 0 : KS); ++ks) {
           const int row = mt * 16 + (lane & 15);
           const int kcol = ks * 16 + (lane >> 4) * 8;
           uint32_t a0[4], a1[4], a2[4];
@@ -990,11 +1022,13 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
           }
 #pragma unroll
           for (int nt = 0; nt < NTW; ++nt) {
-            if (SPLIT == 2) {
+            if (SPLIT == 2 && !(p.dbg & 8)) {
               const uint32_t* bq = b2f + ((((size_t)warp * NTW + nt) * KS + ks) * 2) * 32 + lane;
               mma_bf16(acc[nt], a0, bq[0], bq[32]);
               mma_bf16(acc[nt], a2, rf[0][nt][ks][0], rf[0][nt][ks][1]);
               mma_bf16(acc[nt], a1, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+            }
+            if (SPLIT == 2) {
               mma_bf16(acc[nt], a0, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
               mma_bf16(acc[nt], a1, rf[0][nt][ks][0], rf[0][nt][ks][1]);
             }
@@ -1007,10 +1041,10 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
           if (j < p.nHS * U) {
             const int dest = j / U, uj = j % U;
             uint32_t* d = dstbase + ((size_t)dest * p.nHS + hs) * blk + (size_t)(mt * 16) * U + uj;
-            __stcg(reinterpret_cast<uint2*>(d + (size_t)gq * U),
-                   make_uint2(fword_encode(acc[nt][0], tag), fword_encode(acc[nt][1], tag)));
-            __stcg(reinterpret_cast<uint2*>(d + (size_t)(gq + 8) * U),
-                   make_uint2(fword_encode(acc[nt][2], tag), fword_encode(acc[nt][3], tag)));
+            publish_u32x2(d + (size_t)gq * U, fword_encode(acc[nt][0], tag),
+                          fword_encode(acc[nt][1], tag));
+            publish_u32x2(d + (size_t)(gq + 8) * U, fword_encode(acc[nt][2], tag),
+                          fword_encode(acc[nt][3], tag));
           }
         }
       }
