@@ -112,7 +112,7 @@ __device__ __forceinline__ float row16_sum(float v) {
 }
 
 // One exchange round of per-row pairs among the CTAs of a batch slice, in two halves.
-//   area : this round's buffer, laid out [rows][nHS][2] tagged words
+//   area : this exchange's buffer, laid out [rows][nHS][2] tagged words
 // stat_publish: lane ul == 0 of the row's 16-thread group stores this CTA's pair (a, b).
 __device__ __forceinline__ void stat_publish(uint32_t* area, int row, int hs, int nHS,
                                              uint32_t tag, float a, float b) {

@@ -181,3 +181,26 @@ def test_float16_is_rejected_outside_the_gru():
     b = torch.zeros(16, device="cuda", dtype=torch.float16)
     with pytest.raises(RuntimeError):
         ops.lstm_forward(True, 0.0, x, h, h, W, R, b, torch.empty(0, 0, 0, device="cuda", dtype=torch.float16))
+
+
+@pytest.mark.parametrize("cell", ["lstm", "gru", "layer_norm_lstm", "layer_norm_gru"])
+def test_hidden_size_beyond_the_persistent_kernels_falls_back_and_stays_correct(cell):
+    """fp32 H > 512 does not fit the register-resident recurrence; the step-wise path takes
+    over without the caller noticing anything but the launch count."""
+    from haste_b200 import _C
+    T, N, C, H = 5, 6, 24, 640
+    d = oracle.make_inputs(cell, T, N, C, H, seed=H, zoneout=0.1)
+    ref_out, ref_grads = oracle.forward_backward(cell, d, zoneout=0.1)
+    n0 = _C.launch_count()
+    out, grads = run_cuda(cell, d, zoneout=0.1)
+    _C.sync_check(torch.cuda.current_stream().cuda_stream)
+    assert _C.launch_count() - n0 >= 4 * T
+    _compare(cell, d, out, grads, ref_out, ref_grads, TOL_F32)
+
+
+def test_sequence_too_long_for_32_bit_row_index_is_rejected():
+    from haste_b200 import _C
+    # T*N >= 2^31 rows: rejected before anything is launched (pointers are never touched)
+    with pytest.raises(RuntimeError):
+        _C.call("haste_b200_lstm_forward", _C.F32, 1, 1 << 20, 1 << 11, 8, 8, 1, 1, 1, 1, 1, 1, 1,
+                1, 0.0, None, None)
