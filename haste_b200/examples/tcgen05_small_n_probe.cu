@@ -7,10 +7,10 @@
 // two consecutive K elements per 32-bit column) and times 32 and 64 instructions of
 // M=128, N=16, K=16 with 1, 2, 4 and 8 independent accumulators, issue loop fully unrolled.
 //
-// Measured on B200: ~60 cycles per instruction whatever the number of accumulators, ~1750 cycles
-// of fixed cost per batch (commit, mbarrier wait, tcgen05.ld, CTA barrier) - 3700 cycles for the
-// 64 instructions a step of the fp32 LSTM needs, against ~2000 cycles for the 768 mma.sync
-// m16n8k16 the persistent kernels issue.  At N = 16 the tensor-memory path runs at an eighth of
+// Measured on B200: 32 instructions 1760 cycles, 64 instructions 3670 cycles (commit, mbarrier
+// wait, tcgen05.ld and CTA barrier included), i.e. ~60 cycles per instruction whatever the number
+// of accumulators - 3700 cycles for the 64 instructions a step of the fp32 LSTM needs, against
+// ~2000 cycles for the 768 mma.sync m16n8k16 the persistent kernels issue.  At N = 16 the tensor-memory path runs at an eighth of
 // its peak, which is why the recurrence stays on mma.sync.
 //
 //   nvcc -std=c++17 -gencode arch=compute_100a,code=sm_100a -O3 tcgen05_small_n_probe.cu -o probe
