@@ -222,7 +222,7 @@ int gru_backward(const GruBwd& a, cudaStream_t s) {
   HB_REQUIRE(dh_carry && cs, "scratch arena");
   HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
   GradPlanes planes;
-  bool have_planes = false;
+  bool have_planes = false, persistent_ran = false;
   if (a.dtype == HASTE_B200_F32 && ((3 * H) % 8) == 0) {
     const size_t pe = Arena::pad((size_t)TN * 3 * H * 2) / 2;  // elements per plane
     void* pw = workspace(s, 4 * pe * 2 + 256, /*slot=*/3);
@@ -238,6 +238,7 @@ int gru_backward(const GruBwd& a, cudaStream_t s) {
     st_ = a.iterate ? HASTE_B200_ERR_UNSUPPORTED
                     : gru_backward_persistent(a, dh_carry, planes, s);
     have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
+    persistent_ran = st_ == HASTE_B200_OK;
     if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
     st_ = (a.dtype == HASTE_B200_F32)   ? gru_backward_stepwise<float>(a, dh_carry, s)
           : (a.dtype == HASTE_B200_F16) ? gru_backward_stepwise<__half>(a, dh_carry, s)
@@ -246,8 +247,10 @@ int gru_backward(const GruBwd& a, cudaStream_t s) {
   }
   HB_TRY(st_);
   HB_TRY(from_float(a.dtype, dh_carry, a.dh, NH, s));
-  HB_TRY(colsum(a.dtype, a.dp, 3LL * H, (int)TN, 3 * H, a.dtype, a.dbx, 1, cs, s));
-  HB_TRY(colsum(a.dtype, a.dq, 3LL * H, (int)TN, 3 * H, a.dtype, a.dbr, 1, cs, s));
+  if (!persistent_ran) {  // (the persistent kernel summed the bias gradients itself)
+    HB_TRY(colsum(a.dtype, a.dp, 3LL * H, (int)TN, 3 * H, a.dtype, a.dbx, 1, cs, s));
+    HB_TRY(colsum(a.dtype, a.dq, 3LL * H, (int)TN, 3 * H, a.dtype, a.dbr, 1, cs, s));
+  }
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 3 * H, a.dp, 3LL * H, 1, a.W, tr ? C : 1,
               tr ? 1 : 3LL * H, a.dx, C, 0};

@@ -197,7 +197,7 @@ int lstm_backward(const LstmBwd& a, cudaStream_t s) {
 
   // fp32: room for the gate gradients as bf16 planes (written by the persistent kernel)
   GradPlanes planes;
-  bool have_planes = false;
+  bool have_planes = false, persistent_ran = false;
   if (a.dtype == HASTE_B200_F32 && ((4 * H) % 8) == 0) {
     const size_t pe = Arena::pad((size_t)TN * 4 * H * 2) / 2;  // elements per plane
     void* pw = workspace(s, 2 * pe * 2 + 256, /*slot=*/3);
@@ -212,6 +212,7 @@ int lstm_backward(const LstmBwd& a, cudaStream_t s) {
     st_ = a.iterate ? HASTE_B200_ERR_UNSUPPORTED
                     : lstm_backward_persistent(a, dh_carry, dc_carry, planes, s);
     have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
+    persistent_ran = st_ == HASTE_B200_OK;
     if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
     st_ = (a.dtype == HASTE_B200_F32) ? lstm_backward_stepwise<float>(a, dh_carry, dc_carry, s)
                                       : lstm_backward_stepwise<__nv_bfloat16>(a, dh_carry, dc_carry, s);
@@ -222,7 +223,9 @@ int lstm_backward(const LstmBwd& a, cudaStream_t s) {
   HB_TRY(from_float(a.dtype, dc_carry, a.dc, NH, s));
 
   // v now holds dv = d(loss)/d(pre-activation) for every step.
-  HB_TRY(colsum(a.dtype, a.v, 4LL * H, (int)TN, 4 * H, a.dtype, a.db, 1, cs, s));
+  // (the persistent kernel summed the bias gradient itself)
+  if (!persistent_ran)
+    HB_TRY(colsum(a.dtype, a.v, 4LL * H, (int)TN, 4 * H, a.dtype, a.db, 1, cs, s));
   const bool tr = a.transposed_inputs != 0;
   // dW[C,4H] += x^T . dv
   GemmDesc gw{a.dtype, a.dtype, C, 4 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.v, 4LL * H, 1,

@@ -224,13 +224,19 @@ int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry,
   if (!supported(a.dtype, a.N, a.H, &g)) return HASTE_B200_ERR_UNSUPPORTED;
   Sync sync;
   uint32_t* exch = nullptr;
-  HB_TRY(make_scratch((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U, &sync, &exch, s));
+  const int H = a.H;
+  const size_t ewords = ((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U + 63) & ~size_t(63);
+  const int prow = g.nBS * 16;
+  const size_t pwords = (size_t)prow * 4 * H;
+  HB_TRY(make_scratch(ewords + pwords + colsum_scratch_floats(prow, 4 * H) + 64, &sync, &exch, s));
+  float* part = reinterpret_cast<float*>(exch + ewords);
   BwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R, a.h,
               a.c, a.v, a.dh_new, a.dc_new, nullptr, nullptr, a.zoneout_mask, dh_carry, dc_carry,
-              exch, sync, debug_skip(), planes.p, planes.p2, planes.stride};
+              exch, sync, debug_skip(), planes.p, planes.p2, planes.stride, part};
   int st_ = a.dtype == HASTE_B200_F32 ? run_bwd_lstm_f32(p, g, s) : run_bwd_lstm_bf16(p, g, s);
   if (st_ != HASTE_B200_OK) return st_;
-  const int H = a.H;
+  // db += column sums of the kernel's per-row-group partials
+  HB_TRY(colsum(HASTE_B200_F32, part, 4LL * H, prow, 4 * H, a.dtype, a.db, 1, part + pwords, s));
   GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 4 * H, a.v, 4LL * H, 1, a.R,
               a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 4LL * H, dh_carry, H, 1};
   return gemm_small(gd, s);
@@ -242,15 +248,30 @@ int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& 
   if (!supported(a.dtype, a.N, a.H, &g)) return HASTE_B200_ERR_UNSUPPORTED;
   Sync sync;
   uint32_t* exch = nullptr;
-  HB_TRY(make_scratch((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U, &sync, &exch, s));
+  const int H = a.H;
+  const size_t ewords = ((size_t)2 * g.nBS * g.nHS * g.nHS * g.MT * 16 * U + 63) & ~size_t(63);
+  const int prow = g.nBS * 16;
+  const size_t pwords = (size_t)prow * 4 * H;
+  HB_TRY(make_scratch(ewords + pwords + colsum_scratch_floats(prow, 3 * H) + 64, &sync, &exch, s));
+  float* part = reinterpret_cast<float*>(exch + ewords);
   BwdParams p{a.T, a.N, a.H, g.nHS, g.MT, a.zoneout_mask ? 1 : 0, a.transposed_inputs, a.R, a.h,
               nullptr, const_cast<void*>(a.v), a.dh_new, nullptr, a.dp, a.dq, a.zoneout_mask,
-              dh_carry, nullptr, exch, sync, debug_skip(), planes.p, planes.p2, planes.stride};
+              dh_carry, nullptr, exch, sync, debug_skip(), planes.p, planes.p2, planes.stride, part};
   int st_ = a.dtype == HASTE_B200_F16   ? run_bwd_gru_f16(p, g, s)
             : a.dtype == HASTE_B200_F32 ? run_bwd_gru_f32(p, g, s)
                                         : run_bwd_gru_bf16(p, g, s);
   if (st_ != HASTE_B200_OK) return st_;
-  const int H = a.H;
+  {
+    // partial columns: dp_z, dp_r, dp_g, dq_g.  dbx += sums of (dp_z, dp_r, dp_g);
+    // dbr += sums of (dp_z, dp_r, dq_g)
+    float* cs = part + pwords;
+    const size_t es = dtype_size(a.dtype);
+    char* dbr = static_cast<char*>(a.dbr);
+    HB_TRY(colsum(HASTE_B200_F32, part, 4LL * H, prow, 3 * H, a.dtype, a.dbx, 1, cs, s));
+    HB_TRY(colsum(HASTE_B200_F32, part, 4LL * H, prow, 2 * H, a.dtype, dbr, 1, cs, s));
+    HB_TRY(colsum(HASTE_B200_F32, part + 3 * H, 4LL * H, prow, H, a.dtype, dbr + (size_t)2 * H * es,
+                  1, cs, s));
+  }
   GemmDesc gd{a.dtype, HASTE_B200_F32, a.N, H, 3 * H, a.dq, 3LL * H, 1, a.R,
               a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 3LL * H, dh_carry, H, 1};
   return gemm_small(gd, s);

@@ -94,6 +94,10 @@ struct BwdParams {
   __nv_bfloat16* gpl;
   __nv_bfloat16* gpl2;
   long long gpl_stride;
+  // Bias gradients: every thread sums its gate gradients over all steps in registers and leaves
+  // them here as [nBS*16 rows][4H] partials - LSTM (di, dg, df, do); GRU (dp_z, dp_r, dp_g,
+  // dq_g) - which the host reduces over 16*nBS rows instead of over T*N rows of the gradients.
+  float* db_part;
 };
 
 // ---------------------------------------------------------------------------------------
@@ -586,6 +590,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
     dc_c[mt] = (G == 4 && ok) ? p.dc_carry[(long long)n * H + u0 + ul] : 0.f;
   }
   const size_t blk = (size_t)BNR * U;  // words per (dest, src) exchange block
+  float acc_b[4] = {0.f, 0.f, 0.f, 0.f};  // bias-gradient sums of this thread's (rows, unit)
   bool alive = true;
   __syncthreads();
 
@@ -717,6 +722,8 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
           dc_c[mt] = f * dc_total;
           dh_c[mt] = keep;
           if (ok) {
+#pragma unroll
+            for (int g4 = 0; g4 < 4; ++g4) acc_b[g4] += dgate[g4 % G];
             T* vt = vbuf + ((long long)t * N + n) * 4 * H + u0 + ul;
 #pragma unroll
             for (int g4 = 0; g4 < 4; ++g4) st(vt + g4 * H, dgate[g4 % G]);
@@ -743,6 +750,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
           dgate[2] = dp_g * r;  // dq
           dh_c[mt] = keep + z * dh_total;
           if (ok) {
+            acc_b[0] += dp_z; acc_b[1] += dp_r; acc_b[2] += dp_g; acc_b[3] += dgate[2];
             const long long w0 = ((long long)t * N + n) * 3 * H + u0 + ul;
             st(dpb + w0, dp_z); st(dpb + w0 + H, dp_r); st(dpb + w0 + 2 * H, dp_g);
             st(dqb + w0, dp_z); st(dqb + w0 + H, dp_r); st(dqb + w0 + 2 * H, dgate[2]);
@@ -827,6 +835,11 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
     }
   }
 
+  if (p.db_part && unit_ok) {
+    float* dst = p.db_part + ((size_t)bs * 16 + nl) * 4 * H + u0 + ul;
+#pragma unroll
+    for (int g4 = 0; g4 < 4; ++g4) dst[(size_t)g4 * H] = acc_b[g4];
+  }
   // ---- carries out.  After the last step dh_c holds only the zoneout / GRU direct part
   // of dh_0; the recurrent part of that step is added by the host-issued contraction.
   if (alive) {
