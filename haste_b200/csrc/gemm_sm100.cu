@@ -603,8 +603,22 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
   int splits = 1;
   const int sms = sm_count();
   if (tiles_m * tiles_n < sms && kb_total >= 8) {
-    splits = min(min(kb_total / 4, ceil_div(2 * sms, tiles_m * tiles_n)), 64);
-    if (splits < 1) splits = 1;
+    // Split K so that the work items fill whole waves of the persistent grid: pick the split
+    // count with the smallest estimated time = (waves / splits) x K blocks x time per K block
+    // + the traffic of the partial tiles (written once, read once by the reduction).
+    const int tiles = tiles_m * tiles_n;
+    const int max_splits = min(kb_total / 4, 64);
+    const double products = g.dtype == HASTE_B200_BF16 ? 1.0 : (g.precise ? 6.0 : 3.0);
+    const double t_kb = 0.13 * products;                              // us per K block and CTA
+    const double t_part = 2.0 * (double)M * N * 4.0 / 6.0e6;          // us per split (HBM)
+    double best = 1e30;
+    for (int sp = 1; sp <= max_splits; ++sp) {
+      const int per = ceil_div(kb_total, sp);
+      const int real = ceil_div(kb_total, per);
+      if (real != sp) continue;  // the same blocks per split as a smaller count: skip
+      const double t = (double)ceil_div(tiles * sp, sms) * per * t_kb + (sp > 1 ? sp * t_part : 0.0);
+      if (t < best) { best = t; splits = sp; }
+    }
   }
   int kb_per_split = ceil_div(kb_total, splits);
   splits = ceil_div(kb_total, kb_per_split);
