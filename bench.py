@@ -198,23 +198,25 @@ def main():
     h0 = torch.zeros(N, H, device=dev, dtype=dtype)
     nomask = torch.empty(0, 0, 0, device=dev, dtype=dtype)
     res_host = torch.empty(N * H + 4 * H, dtype=dtype).pin_memory()
-    comm = torch.cuda.Stream(device=dev) if world > 1 else None
+    # dW, dR and db are views of one flat buffer: the backward pass writes into it and the
+    # gradient sum over the ranks is one collective on that buffer, with no pack or scatter
+    bucket = data_parallel.GradientBucket.for_cell("lstm", C, H, dtype, dev)
 
     def step(x_dev):
         h, c, cache = ops.lstm_forward(True, 0.0, x_dev, h0, h0, W, R, b, nomask)
+        bucket.reset()
         dx, dh, dc0, dW, dR, db = ops.lstm_backward(x_dev, W, R, b, nomask, h, c, cache, dy, dc,
-                                                    transposed=False)
-        if world > 1:
-            data_parallel.all_reduce_tensors([dW, dR, db])
+                                                    transposed=False, grads=bucket)
+        bucket.all_reduce()
         return h, db
 
     def e2e_step():
         # host-resident input: the public streamed-input op overlaps the copy with compute
         h, c, cache, x_dev = ops.lstm_forward_from_host(True, 0.0, x_host, h0, h0, W, R, b, nomask)
+        bucket.reset()
         dx, dh, dc0, dW, dR, db = ops.lstm_backward(x_dev, W, R, b, nomask, h, c, cache, dy, dc,
-                                                    transposed=False)
-        if world > 1:
-            data_parallel.all_reduce_tensors([dW, dR, db])
+                                                    transposed=False, grads=bucket)
+        bucket.all_reduce()
         res_host[:N * H].copy_(h[-1].reshape(-1), non_blocking=True)
         res_host[N * H:].copy_(db, non_blocking=True)
         torch.cuda.current_stream().synchronize()

@@ -12,7 +12,10 @@ it is tested):
   must apply the same mask to its replica of the weights;
 * `broadcast_parameters` makes the replicas identical at start;
 * `all_reduce_tensors` / `all_reduce_gradients` sum gradients in flat buckets (one
-  launch-latency-sized collective per bucket instead of one per tensor).
+  launch-latency-sized collective per bucket instead of one per tensor);
+* `GradientBucket` is the flat buffer itself, handed to a backward op as its gradient
+  outputs: the weight-gradient contractions and the bias column sums write straight into the
+  buffer that the collective then reduces, with no pack before it and no scatter after.
 
 The reference has no multi-GPU path; its layers are used under the framework's own data
 parallel wrappers, which this mirrors.
@@ -21,7 +24,7 @@ import torch
 import torch.distributed as dist
 
 __all__ = ["shard", "dropconnect_mask", "broadcast_parameters", "all_reduce_tensors",
-           "all_reduce_gradients"]
+           "all_reduce_gradients", "GradientBucket"]
 
 
 def _world(group=None):
@@ -109,3 +112,82 @@ def all_reduce_gradients(module_or_params, group=None, bucket_bytes=64 << 20, as
               else module_or_params)
     return all_reduce_tensors([p.grad for p in params if p.grad is not None], group=group,
                               bucket_bytes=bucket_bytes, async_op=async_op)
+
+
+_CELL_GATES = {"lstm": 4, "gru": 3, "indrnn": 1, "layer_norm_lstm": 4, "layer_norm_gru": 3,
+               "layer_norm_indrnn": 1}
+
+
+class GradientBucket:
+    """One flat buffer that holds every parameter gradient of a layer (one direction).
+
+    Pass it to a backward op (`ops.lstm_backward(..., grads=bucket)` and the like): the op
+    takes its zero-initialised `dW`, `dR`, bias and LayerNorm-gain outputs as views of the
+    buffer instead of allocating them, so the library's contractions write into the bucket
+    directly, and `all_reduce` is then a single collective over memory that is already
+    packed.  `reset` zeroes the buffer (the ops accumulate into their outputs) and rewinds it
+    for the next step.  Views start on 256-byte boundaries, which the contraction's 16-byte
+    stores need.
+    """
+
+    ALIGN_BYTES = 256
+
+    def __init__(self, shapes, dtype, device):
+        self.dtype = dtype
+        self._align = self.ALIGN_BYTES // torch.empty((), dtype=dtype).element_size()
+        total = sum(self._padded(_numel(s)) for s in shapes)
+        self.flat = torch.zeros(max(total, 1), dtype=dtype, device=device)
+        self._cursor = 0
+
+    @classmethod
+    def for_cell(cls, cell, input_size, hidden_size, dtype, device):
+        """A bucket sized for the parameter gradients of one `cell` layer."""
+        C, H, G = input_size, hidden_size, _CELL_GATES[cell]
+        if "indrnn" in cell:
+            shapes = [(C, H), (H,), (H,)]
+        elif "gru" in cell:
+            shapes = [(C, G * H), (H, G * H), (G * H,), (G * H,)]
+        else:
+            shapes = [(C, G * H), (H, G * H), (G * H,)]
+        if cell.startswith("layer_norm"):
+            shapes.append((2, G * H))
+        if cell == "layer_norm_lstm":
+            shapes += [(H,), (H,)]
+        return cls(shapes, dtype, device)
+
+    def _padded(self, n):
+        return (n + self._align - 1) // self._align * self._align
+
+    def reset(self):
+        self.flat.zero_()
+        self._cursor = 0
+
+    def take(self, *shape):
+        """The next `shape`-sized view of the buffer (zero after `reset`)."""
+        if len(shape) == 1 and not isinstance(shape[0], int):
+            shape = tuple(shape[0])
+        n = _numel(shape)
+        if self._cursor + n > self.flat.numel():
+            raise ValueError("gradient bucket is too small for the outputs taken from it")
+        view = self.flat[self._cursor:self._cursor + n].view(*shape)
+        self._cursor += self._padded(n)
+        return view
+
+    def all_reduce(self, group=None, async_op=False):
+        """Sums the buffer over the ranks, in place.  With `async_op` returns the work handle
+        (or None on a single rank); wait on it before reading the views."""
+        _, world = _world(group)
+        if world == 1:
+            return None
+        work = dist.all_reduce(self.flat, op=dist.ReduceOp.SUM, group=group, async_op=True)
+        if async_op:
+            return work
+        work.wait()
+        return None
+
+
+def _numel(shape):
+    n = 1
+    for d in shape:
+        n *= int(d)
+    return n

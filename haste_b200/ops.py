@@ -49,6 +49,16 @@ def _mask_ptr(zoneout_prob, mask):
     return (mask.data_ptr() if has else None), (float(zoneout_prob) if has else 0.0)
 
 
+def _zeros(grads, like, *shape):
+    """A zeroed parameter-gradient output: a view of the caller's `GradientBucket` when one is
+    given (`haste_b200.data_parallel`), else a fresh tensor."""
+    if grads is None:
+        return like.new_zeros(*shape)
+    if grads.dtype != like.dtype or grads.flat.device != like.device:
+        raise ValueError("gradient bucket has the wrong dtype or device")
+    return grads.take(*shape)
+
+
 def _dims_fwd(x, recurrent):
     T, N, C = x.shape
     return T, N, C, recurrent.shape[0]
@@ -81,15 +91,15 @@ def lstm_forward(training, zoneout_prob, x, h0, c0, kernel, recurrent_kernel, bi
 
 
 def lstm_backward(x, kernel, recurrent_kernel, bias, zoneout_mask, h, c, cache, dh_new, dc_new,
-                  transposed=True):
+                  transposed=True, grads=None):
     _check(x, kernel, recurrent_kernel, bias, zoneout_mask, h, c, cache, dh_new, dc_new)
     H = h.shape[2]
     T, N, C, H = _dims_bwd(x, transposed, H)
     with torch.cuda.device(h.device):
         dx = h.new_empty(T, N, C)
-        dW = h.new_zeros(C, 4 * H)
-        dR = h.new_zeros(H, 4 * H)
-        db = h.new_zeros(4 * H)
+        dW = _zeros(grads, h, C, 4 * H)
+        dR = _zeros(grads, h, H, 4 * H)
+        db = _zeros(grads, h, 4 * H)
         dh = h.new_zeros(N, H)
         dc = h.new_zeros(N, H)
         _C.call("haste_b200_lstm_backward", _dtype(h), int(transposed), T, N, C, H, _p(kernel),
@@ -178,16 +188,16 @@ def gru_forward(training, zoneout_prob, x, h0, kernel, recurrent_kernel, bias, r
 
 
 def gru_backward(x, kernel, recurrent_kernel, bias, recurrent_bias, zoneout_mask, h, cache,
-                 dh_new, transposed=True):
+                 dh_new, transposed=True, grads=None):
     _check(x, kernel, recurrent_kernel, bias, recurrent_bias, zoneout_mask, h, cache, dh_new)
     H = h.shape[2]
     T, N, C, H = _dims_bwd(x, transposed, H)
     with torch.cuda.device(h.device):
         dx = h.new_empty(T, N, C)
-        dW = h.new_zeros(C, 3 * H)
-        dR = h.new_zeros(H, 3 * H)
-        dbx = h.new_zeros(3 * H)
-        dbr = h.new_zeros(3 * H)
+        dW = _zeros(grads, h, C, 3 * H)
+        dR = _zeros(grads, h, H, 3 * H)
+        dbx = _zeros(grads, h, 3 * H)
+        dbr = _zeros(grads, h, 3 * H)
         dh = h.new_zeros(N, H)
         dp = h.new_empty(T, N, 3 * H)
         dq = h.new_empty(T, N, 3 * H)
@@ -213,15 +223,15 @@ def indrnn_forward(training, zoneout_prob, x, h0, kernel, recurrent_scale, bias,
     return h
 
 
-def indrnn_backward(x, kernel, recurrent_scale, bias, zoneout_mask, h, dh_new, transposed=True):
+def indrnn_backward(x, kernel, recurrent_scale, bias, zoneout_mask, h, dh_new, transposed=True, grads=None):
     _check(x, kernel, recurrent_scale, bias, zoneout_mask, h, dh_new)
     H = h.shape[2]
     T, N, C, H = _dims_bwd(x, transposed, H)
     with torch.cuda.device(h.device):
         dx = h.new_empty(T, N, C)
-        dW = h.new_zeros(C, H)
-        du = h.new_zeros(H)
-        db = h.new_zeros(H)
+        dW = _zeros(grads, h, C, H)
+        du = _zeros(grads, h, H)
+        db = _zeros(grads, h, H)
         dh = h.new_zeros(N, H)
         workspace = h.new_empty(T, N, H)
         _C.call("haste_b200_indrnn_backward", _dtype(h), int(transposed), T, N, C, H, _p(kernel),
@@ -259,19 +269,19 @@ def layer_norm_lstm_forward(training, zoneout_prob, x, h0, c0, kernel, recurrent
 
 def layer_norm_lstm_backward(x, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h,
                              zoneout_mask, h, c, act_Wx, act_Wx_norm, cache_Wx, act_Rh, cache_Rh,
-                             act_c_norm, cache_c, dh_new, dc_new, transposed=True):
+                             act_c_norm, cache_c, dh_new, dc_new, transposed=True, grads=None):
     _check(x, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h, zoneout_mask, h, c, act_Wx,
            act_Wx_norm, cache_Wx, act_Rh, cache_Rh, act_c_norm, cache_c, dh_new, dc_new)
     H = h.shape[2]
     T, N, C, H = _dims_bwd(x, transposed, H)
     with torch.cuda.device(h.device):
         dx = h.new_empty(T, N, C)
-        dW = h.new_zeros(C, 4 * H)
-        dR = h.new_zeros(H, 4 * H)
-        db = h.new_zeros(4 * H)
-        dgamma = torch.zeros_like(gamma)
-        dgamma_h = torch.zeros_like(gamma_h)
-        dbeta_h = torch.zeros_like(beta_h)
+        dW = _zeros(grads, h, C, 4 * H)
+        dR = _zeros(grads, h, H, 4 * H)
+        db = _zeros(grads, h, 4 * H)
+        dgamma = _zeros(grads, h, *gamma.shape)
+        dgamma_h = _zeros(grads, h, *gamma_h.shape)
+        dbeta_h = _zeros(grads, h, *beta_h.shape)
         dh = h.new_zeros(N, H)
         dc = h.new_zeros(N, H)
         _C.call("haste_b200_layer_norm_lstm_backward", _dtype(h), int(transposed), T, N, C, H,
@@ -310,21 +320,21 @@ def layer_norm_gru_forward(training, zoneout_prob, x, h0, kernel, recurrent_kern
 
 def layer_norm_gru_backward(x, kernel, recurrent_kernel, bias, recurrent_bias, gamma,
                             zoneout_mask, h, cache, act_Wx, cache_Wx, act_Rh, cache_Rh, dh_new,
-                            transposed=True):
+                            transposed=True, grads=None):
     _check(x, kernel, recurrent_kernel, bias, recurrent_bias, gamma, zoneout_mask, h, cache,
            act_Wx, cache_Wx, act_Rh, cache_Rh, dh_new)
     H = h.shape[2]
     T, N, C, H = _dims_bwd(x, transposed, H)
     with torch.cuda.device(h.device):
         dx = h.new_empty(T, N, C)
-        dW = h.new_zeros(C, 3 * H)
-        dR = h.new_zeros(H, 3 * H)
-        dbx = h.new_zeros(3 * H)
-        dbr = h.new_zeros(3 * H)
+        dW = _zeros(grads, h, C, 3 * H)
+        dR = _zeros(grads, h, H, 3 * H)
+        dbx = _zeros(grads, h, 3 * H)
+        dbr = _zeros(grads, h, 3 * H)
         dh = h.new_zeros(N, H)
         dp = h.new_empty(T, N, 3 * H)
         dq = h.new_empty(T, N, 3 * H)
-        dgamma = torch.zeros_like(gamma)
+        dgamma = _zeros(grads, h, *gamma.shape)
         _C.call("haste_b200_layer_norm_gru_backward", _dtype(h), int(transposed), T, N, C, H,
                 _p(kernel), _p(recurrent_kernel), _p(bias), _p(recurrent_bias), _p(gamma[0]),
                 _p(gamma[1]), _p(x),
@@ -355,17 +365,17 @@ def layer_norm_indrnn_forward(training, zoneout_prob, x, h0, kernel, recurrent_s
 
 
 def layer_norm_indrnn_backward(x, kernel, recurrent_scale, bias, gamma, zoneout_mask, h, act_Wx,
-                               cache_Wx, dh_new, transposed=True):
+                               cache_Wx, dh_new, transposed=True, grads=None):
     _check(x, kernel, recurrent_scale, bias, gamma, zoneout_mask, h, act_Wx, cache_Wx, dh_new)
     H = h.shape[2]
     T, N, C, H = _dims_bwd(x, transposed, H)
     with torch.cuda.device(h.device):
         dx = h.new_empty(T, N, C)
-        dW = h.new_zeros(C, H)
-        du = h.new_zeros(H)
-        db = h.new_zeros(H)
+        dW = _zeros(grads, h, C, H)
+        du = _zeros(grads, h, H)
+        db = _zeros(grads, h, H)
         dh = h.new_zeros(N, H)
-        dgamma = torch.zeros_like(gamma)
+        dgamma = _zeros(grads, h, *gamma.shape)
         workspace = h.new_empty(T, N, H)
         _C.call("haste_b200_layer_norm_indrnn_backward", _dtype(h), int(transposed), T, N, C, H,
                 _p(kernel), _p(recurrent_scale), _p(bias), _p(gamma), _p(x), _p(h), _p(dh_new),

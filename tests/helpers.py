@@ -50,7 +50,7 @@ max_rel_err = oracle.max_rel_err
 # input dictionary, returning outputs and gradients under the oracle's names.
 # ---------------------------------------------------------------------------
 def run_cuda(cell, d, zoneout=0.0, dtype=torch.float32, transposed=False, training=True,
-             backward=True, device="cuda"):
+             backward=True, device="cuda", grads=None):
     from haste_b200 import ops
     _, names, has_c = oracle.CELLS[cell]
     t = {k: (v.to(device=device, dtype=dtype).contiguous() if v is not None else None)
@@ -102,8 +102,8 @@ def run_cuda(cell, d, zoneout=0.0, dtype=torch.float32, transposed=False, traini
     else:
         args = (xx, W, rec, t["b"], t["gamma"], mask, fwd[0], *saved, t["dh"])
         gn = ["x", "h0", "W", "u", "b", "gamma"]
-    grads = getattr(ops, cell + "_backward")(*args, transposed=transposed)
-    return out, dict(zip(gn, grads))
+    got = getattr(ops, cell + "_backward")(*args, transposed=transposed, grads=grads)
+    return out, dict(zip(gn, got))
 
 
 def assert_close(got, want, tol, what=""):

@@ -74,6 +74,23 @@ def _rank_main(rank, port, cell, results):
         dp.all_reduce_gradients(lin)
         for p in lin.parameters():
             assert torch.equal(p.grad, torch.full_like(p, 3.0))
+
+        # gradient bucket: the outputs are views of one flat buffer, summed by one collective
+        bucket = dp.GradientBucket.for_cell(cell, C, H, torch.float64, "cpu")
+        for _ in range(2):  # a second step reuses the buffer after reset()
+            bucket.reset()
+            views = [bucket.take(*g[k].shape) for k in weights]
+            base = bucket.flat.untyped_storage().data_ptr()
+            for v, k in zip(views, weights):
+                assert v.untyped_storage().data_ptr() == base and v.data_ptr() % 256 == base % 256
+                assert not v.any()
+                v.add_(g[k])  # what a backward op does: accumulate into its zeroed output
+            work = bucket.all_reduce(async_op=True)
+            work.wait()
+            for v, k in zip(views, weights):
+                assert torch.allclose(v, ref_g[k], rtol=1e-10, atol=1e-12), k
+        with pytest.raises(ValueError):
+            bucket.take(1 << 20)
         results[rank] = "ok"
     finally:
         dist.destroy_process_group()

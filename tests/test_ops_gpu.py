@@ -217,3 +217,27 @@ def test_streamed_host_input_equals_single_call():
         for a, b in zip(got[:3], want):
             assert_close(a, b, 2e-5, "streamed vs single call")
         assert torch.equal(got[3], cu(d["x"]))
+
+
+@pytest.mark.parametrize("cell", ["lstm", "gru", "indrnn", "layer_norm_lstm", "layer_norm_gru",
+                                  "layer_norm_indrnn"])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parameter_gradients_written_into_a_bucket(cell, dtype):
+    """With `grads=bucket` the backward op's parameter gradients are views of the caller's
+    flat buffer (what the gradient all-reduce then sums) and equal the separately allocated
+    ones bit for bit."""
+    from haste_b200.data_parallel import GradientBucket
+    from helpers import run_cuda
+    T, N, C, H = 9, 32, 24, 64
+    d = oracle.make_inputs(cell, T, N, C, H, seed=21, zoneout=0.1)
+    _, want = run_cuda(cell, d, zoneout=0.1, dtype=dtype)
+    bucket = GradientBucket.for_cell(cell, C, H, dtype, "cuda")
+    for _ in range(2):  # the second pass reuses the buffer
+        bucket.reset()
+        _, got = run_cuda(cell, d, zoneout=0.1, dtype=dtype, grads=bucket)
+        lo = bucket.flat.data_ptr()
+        hi = lo + bucket.flat.numel() * bucket.flat.element_size()
+        for k, v in got.items():
+            assert torch.equal(v, want[k]), k
+            if k not in ("x", "h0", "c0"):
+                assert lo <= v.data_ptr() < hi and v.data_ptr() % 16 == 0, k
