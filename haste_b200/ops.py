@@ -113,7 +113,7 @@ _copy_streams = {}
 
 
 def lstm_forward_from_host(training, zoneout_prob, x_host, h0, c0, kernel, recurrent_kernel, bias,
-                           zoneout_mask, chunks=4):
+                           zoneout_mask, chunks=8):
     """`lstm_forward` for an input that still lives in pinned HOST memory.
 
     The sequence is cut into `chunks` pieces along time; while the GPU runs the projection and
@@ -122,6 +122,10 @@ def lstm_forward_from_host(training, zoneout_prob, x_host, h0, c0, kernel, recur
     `[T+1,N,H]` / `[T,N,4H]` buffers (the state slot a piece ends on is the initial state of
     the next), so the result equals one call on the whole sequence up to the rounding of the
     input projection (a short piece may take the CUDA-core contraction path).
+    The default of 8 pieces measured best at T=1000, N=64, C=H=512 in fp32, where the copy of
+    the whole input takes about as long as the forward pass (fwd+bwd step with host input:
+    1 piece 9.98 ms, 2: 8.83, 4: 8.34, 8: 8.21, 16: 8.43, 24: 8.88; each piece costs ~50 us of
+    launches and start-up).
     Returns [h, c, cache, x_device].
     """
     _check(h0, c0, kernel, recurrent_kernel, bias, zoneout_mask)
