@@ -294,7 +294,7 @@ def main():
     # step touches its own slice of the activations once, so a launch's traffic is this
     # times T.
     ncu_bytes_per_step = {"recurrence_fwd": (109.377024e6 + 108.569600e6) / 200,
-                          "recurrence_bwd": (188.500992e6 + 168.230144e6) / 200}
+                          "recurrence_bwd": (188.644096e6 + 166.822912e6) / 200}
     dom = max(phases, key=phases.get)
     if dom in alg_bytes:
         ach = alg_bytes[dom] / (phases[dom] * 1e-3) / 1e9
