@@ -26,6 +26,7 @@
 #include <cuda.h>
 #include <cudaTypedefs.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "cells.cuh"
@@ -554,18 +555,11 @@ struct Operand {
   const void* base;
 };
 
-int sm_count() {
-  static int n = 0;
-  if (!n) {
-    int dev = 0;
-    cudaGetDevice(&dev);
-    cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-    if (n <= 0) n = 148;
-  }
-  return n;
-}
-
-std::once_flag g_attr_once;
+// The opt-in to more than 48 KB of dynamic shared memory is a per-device (per-context)
+// function attribute: one flag per device ordinal, so that a process driving several GPUs
+// opts in on each of them.
+constexpr int kMaxDevices = 64;
+std::atomic<bool> g_attr_set[kMaxDevices];
 
 }  // namespace
 
@@ -690,14 +684,19 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
   p.partial = partial;
   p.err = err;
 
-  std::call_once(g_attr_once, [] {
-    cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         Cfg<1>::SMEM);
-    cudaFuncSetAttribute(gemm_tcgen05_kernel<3>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         Cfg<3>::SMEM);
-    cudaFuncSetAttribute(gemm_tcgen05_kernel<6>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                         Cfg<6>::SMEM);
-  });
+  {
+    int dev = 0;
+    HB_CUDA_OK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= kMaxDevices || !g_attr_set[dev].load(std::memory_order_acquire)) {
+      HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<1>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM));
+      HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<3>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<3>::SMEM));
+      HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<6>,
+                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<6>::SMEM));
+      if (dev >= 0 && dev < kMaxDevices) g_attr_set[dev].store(true, std::memory_order_release);
+    }
+  }
   const int grid = min(sms, tiles_m * tiles_n * splits);
   if (planes == 3)
     gemm_tcgen05_kernel<6><<<grid, THREADS, Cfg<6>::SMEM, stream>>>(m_a, m_b, p);

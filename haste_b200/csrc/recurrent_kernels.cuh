@@ -51,6 +51,14 @@ constexpr int WARPS = 8;
 constexpr int THREADS = WARPS * 32;
 constexpr long long SPIN_LIMIT_CYCLES = 4000000000LL;
 
+// Timing experiments (attributing step time to waits, contraction, prefetch) are compiled in
+// only with -DHASTE_B200_TIMING_EXPERIMENTS; the shipped kernels carry none of their branches.
+#ifdef HASTE_B200_TIMING_EXPERIMENTS
+#define HB_DBG(p, bit) (((p).dbg & (bit)) != 0)
+#else
+#define HB_DBG(p, bit) false
+#endif
+
 struct Sync {
   int* abort_flag;  // device-global
   int* err;         // process error word (pinned host memory)
@@ -69,7 +77,7 @@ struct FwdParams {
   const void* mask;  // [T, N, H]
   uint32_t* xbuf;    // [2][N][Hx] tagged exchange words, zeroed before launch
   Sync sync;
-  int dbg;           // timing experiments only (wrong results): 1 no waits, 2 no MMA
+  int dbg;           // read only in timing-experiment builds (see HB_DBG): 1 no waits, 2 no MMA
 };
 
 struct BwdParams {
@@ -309,7 +317,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
         wxr[mt][g] = ok ? ld(wx + ((long long)t * N + n) * GH + g * H + u0 + ul) : 0.f;
       mk[mt] = (ok && p.has_zoneout && p.training)
                    ? ld(mask + (long long)t * NH + (long long)n * H + u0 + ul) : 0.f;
-      if (MTMAX == 1 && ok && t + 1 < p.T && !(p.dbg & 512)) {  // next step inputs: into L2 now
+      if (MTMAX == 1 && ok && t + 1 < p.T && !HB_DBG(p, 512)) {  // next step inputs: into L2 now
 #pragma unroll
         for (int g = 0; g < G; ++g)
           prefetch_l2(wx + ((long long)(t + 1) * N + n) * GH + g * H + u0 + ul);
@@ -345,7 +353,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
               *reinterpret_cast<uint2*>(a_lo + (size_t)r * AROW + k) =
                   make_uint2(pack_bf16(lo[0], lo[1]), pack_bf16(lo[2], lo[3]));
           }
-        } else if (alive && !(p.dbg & 1)) {
+        } else if (alive && !HB_DBG(p, 1)) {
           const uint32_t want = (((uint32_t)(t - 1) >> 1) & 1u) ^ 1u;
           const uint32_t wtag = want << 30;
           const uint32_t* xsrc = p.xbuf + (size_t)((t - 1) & 1) * N * Hx;
@@ -397,7 +405,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_fwd_kernel(const FwdParams p) 
       float acc[NT][4];
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-      if (!(p.dbg & 2)) {
+      if (!HB_DBG(p, 2)) {
 #pragma unroll
         for (int ks = 0; ks < KSW; ++ks) {
           const int row = lane & 15;
@@ -664,7 +672,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
       }
       // Ask L2 for the next step's inputs now, so that their loads return from L2 and do not
       // occupy the SM's miss queue for an HBM round trip while the exchange polls need it.
-      if (MTMAX == 1 && ok && t > 0 && !(p.dbg & 512)) {
+      if (MTMAX == 1 && ok && t > 0 && !HB_DBG(p, 512)) {
 #pragma unroll
         for (int g = 0; g < 4; ++g) prefetch_l2(vt - (long long)N * 4 * H + g * H);
         prefetch_l2(dhn + (long long)t * NH + o0);
@@ -679,7 +687,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
     }
 
     // ---- recurrent part of dh_t: the partials published at the previous step (ti-1)
-    if (ti > 0 && !(p.dbg & 1)) {
+    if (ti > 0 && !HB_DBG(p, 1)) {
       const uint32_t want = (((uint32_t)(ti - 1) >> 1) & 1u) ^ 1u;
       const uint32_t* src =
           p.exch + ((((size_t)((ti - 1) & 1) * nBS + bs) * p.nHS + hs) * p.nHS) * blk;
@@ -927,7 +935,7 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
         float acc[NTW][4];
 #pragma unroll
         for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
-        if (!(p.dbg & 2)) {
+        if (!HB_DBG(p, 2)) {
 #pragma unroll
           for (int ks = 0; ks < KS; ++ks) {
             const int row = mt * 16 + (lane & 15);
@@ -987,8 +995,6 @@ __global__ void __launch_bounds__(THREADS, 1) rec_bwd_kernel(const BwdParams p) 
 struct Geometry {
   int nHS, nBS, MT;
 };
-
-int sm_count();
 
 template <typename K>
 int launch_coop(K kernel, int grid, size_t smem, void* params, cudaStream_t s) {

@@ -49,7 +49,7 @@ struct LnFwdParams {
   uint32_t* xbuf;       // [2][N][Hx] tagged h words
   uint32_t* sbuf;       // [2 stats][2 parity][nBS][rows][nHS][2] tagged statistic pairs
   Sync sync;
-  int dbg = 0;          // timing experiments only (wrong results): 1 no h wait, 2 no MMA, 4 no statistic waits
+  int dbg = 0;          // read only in timing-experiment builds (HB_DBG): 1 no h wait, 2 no MMA, 4 no statistic waits
 };
 
 struct LnBwdParams {
@@ -81,7 +81,7 @@ struct LnBwdParams {
   __nv_bfloat16* gpl;     // optional bf16 planes of d(x.W-side gate gradient) (dv)
   __nv_bfloat16* gpl2;    // optional bf16 planes of d(h.R)
   long long gpl_stride;
-  int dbg = 0;            // timing experiments only (wrong results): 1 no dh wait, 2 no MMA, 4 no statistic waits
+  int dbg = 0;            // read only in timing-experiment builds (HB_DBG): 1 no dh wait, 2 no MMA, 4 no statistic waits
 };
 
 // Statistics, partial gradients and (with fp32 storage) h travel as tagged fp32 words
@@ -310,7 +310,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
         wxr[mt][g] = ok ? ld(wx + ((long long)t * N + n) * GH + g * H + u0 + ul) : 0.f;
       mk[mt] = (ok && p.has_zoneout && p.training)
                    ? ld(mask + (long long)t * NH + (long long)n * H + u0 + ul) : 0.f;
-      if (MTMAX == 1 && ok && t + 1 < p.T && !(p.dbg & 512)) {  // next step inputs: into L2 now
+      if (MTMAX == 1 && ok && t + 1 < p.T && !HB_DBG(p, 512)) {  // next step inputs: into L2 now
 #pragma unroll
         for (int g = 0; g < G; ++g)
           prefetch_l2(wx + ((long long)(t + 1) * N + n) * GH + g * H + u0 + ul);
@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
                     make_uint2(pack_bf16(x[0], x[1]), pack_bf16(x[2], x[3]));
               }
             }
-          } else if (alive && !(p.dbg & 1)) {
+          } else if (alive && !HB_DBG(p, 1)) {
             const uint32_t want = (((uint32_t)(t - 1) >> 1) & 1u) ^ 1u;
             const uint32_t* xsrc = p.xbuf + (size_t)((t - 1) & 1) * N * Hx;
             uint4 w[CPL];
@@ -417,7 +417,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < ((p.dbg & 2) ? 0 : KSW); ++ks) {
+        for (int ks = 0; ks < (HB_DBG(p, 2) ? 0 : KSW); ++ks) {
           const int row = lane & 15;
           const int kcol = warp * KW + ks * 16 + (lane >> 4) * 8;
           uint32_t a0[4], a1[4], a2[4];
@@ -496,7 +496,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           const int n = n0 + mt * 16 + nl;
           const bool ok = n < N && unit_ok;
           float sa[4], sb[4], mean1, inv1;
-          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 27))
+          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !HB_DBG(p, 4), sa, sb, p.sync, &s_abort, 27))
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           chan_combine(sa, sb, ul, p.nHS, GH, COLS, mean1, inv1);
           float pre[G];
@@ -535,7 +535,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           const int n = n0 + mt * 16 + nl;
           const bool ok = n < N && unit_ok;
           float sa[4], sb[4], mean3, inv3;
-          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 28))
+          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N && !HB_DBG(p, 4), sa, sb, p.sync, &s_abort, 28))
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           chan_combine(sa, sb, ul, p.nHS, H, U, mean3, inv3);
           const float c_norm = (cnew[mt] - mean3) * inv3 * gh + bh;
@@ -569,7 +569,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           const int n = n0 + mt * 16 + nl;
           const bool ok = n < N && unit_ok;
           float sa[4], sb[4], mean1, inv1;
-          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 27))
+          if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !HB_DBG(p, 4), sa, sb, p.sync, &s_abort, 27))
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           chan_combine(sa, sb, ul, p.nHS, GH, COLS, mean1, inv1);
           float rn[G];
@@ -751,7 +751,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
       // Ask L2 for the next step's inputs now: when that step loads them they come back from
       // L2 in a fraction of the HBM latency and do not sit in the SM's miss queue while the
       // polling loads of the exchange need it.
-      if (MTMAX == 1 && ok && t > 0 && !(p.dbg & 512)) {
+      if (MTMAX == 1 && ok && t > 0 && !HB_DBG(p, 512)) {
         const long long w1 = w0 - (long long)N * GH, v1 = v0 - (long long)N * 4 * H;
 #pragma unroll
         for (int g = 0; g < 4; ++g) prefetch_l2(vbuf + v1 + g * H);
@@ -770,7 +770,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
     }
 
     // ---- recurrent part of dh_t: the partials published at the previous step
-    if (ti > 0 && !(p.dbg & 1)) {
+    if (ti > 0 && !HB_DBG(p, 1)) {
       const uint32_t want = (((uint32_t)(ti - 1) >> 1) & 1u) ^ 1u;
       const uint32_t* src =
           p.exch + ((((size_t)((ti - 1) & 1) * nBS + bs) * p.nHS + hs) * p.nHS) * blk;
@@ -869,7 +869,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
           const int n = n0 + mt * 16 + nl;
           const bool ok = n < N && unit_ok;
           float sa[4], sb[4];
-          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 38))
+          if (!stat_collect(area3, mt * 16 + nl, p.nHS, ul, tag, n < N && !HB_DBG(p, 4), sa, sb, p.sync, &s_abort, 38))
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           const float S1 = row16_sum((sa[0] + sa[1]) + (sa[2] + sa[3]));
           const float S2 = row16_sum((sb[0] + sb[1]) + (sb[2] + sb[3]));
@@ -972,7 +972,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
         const int n = n0 + mt * 16 + nl;
         const bool ok = n < N && unit_ok;
         float sa[4], sb[4];
-        if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !(p.dbg & 4), sa, sb, p.sync, &s_abort, 39))
+        if (!stat_collect(area1, mt * 16 + nl, p.nHS, ul, tag, n < N && !HB_DBG(p, 4), sa, sb, p.sync, &s_abort, 39))
           *reinterpret_cast<volatile int*>(&s_abort) = 1;
         const float S1 = row16_sum((sa[0] + sa[1]) + (sa[2] + sa[3]));
         const float S2 = row16_sum((sb[0] + sb[1]) + (sb[2] + sb[3]));
@@ -1011,7 +1011,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
 #pragma unroll
         for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 #pragma unroll
-        for (int ks = 0; ks < ((p.dbg & 2) ? 0 : KS); ++ks) {
+        for (int ks = 0; ks < (HB_DBG(p, 2) ? 0 : KS); ++ks) {
           const int row = mt * 16 + (lane & 15);
           const int kcol = ks * 16 + (lane >> 4) * 8;
           uint32_t a0[4], a1[4], a2[4];
@@ -1022,7 +1022,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
           }
 #pragma unroll
           for (int nt = 0; nt < NTW; ++nt) {
-            if (SPLIT == 2 && !(p.dbg & 8)) {
+            if (SPLIT == 2 && !HB_DBG(p, 8)) {
               const uint32_t* bq = b2f + ((((size_t)warp * NTW + nt) * KS + ks) * 2) * 32 + lane;
               mma_bf16(acc[nt], a0, bq[0], bq[32]);
               mma_bf16(acc[nt], a2, rf[0][nt][ks][0], rf[0][nt][ks][1]);

@@ -6,6 +6,9 @@
 
 namespace hb {
 
+// SM count of the current device (cached per device ordinal).
+int sm_count();
+
 // Counts kernels launched by this library (reported through the C ABI).
 void count_launch(int n);
 

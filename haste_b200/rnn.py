@@ -524,10 +524,13 @@ class Stack(nn.Module):
             if self._side is None:
                 self._side = torch.cuda.Stream(device=x.device)
             main = torch.cuda.current_stream()
+            # the side stream starts after everything queued so far (x included) and makes its
+            # own reversed copy, so no kernel of the backward-direction layer can run ahead
+            # of the flip that produces its input
             self._side.wait_stream(main)
-            x_rev = torch.flip(x, [0])
             with torch.cuda.stream(self._side):
-                x_rev.record_stream(self._side)
+                x.record_stream(self._side)
+                x_rev = torch.flip(x, [0])
                 y_bw, _ = level[1](x_rev, **kw[1])
                 y_bw = torch.flip(y_bw, [0])
             y_fw, _ = level[0](x, **kw[0])

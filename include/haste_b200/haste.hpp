@@ -11,7 +11,8 @@
 //  * All work is issued on the stream given to the constructor, in order.
 //  * The reference's methods return void and check nothing; here a failed call throws
 //    std::runtime_error carrying haste_b200_last_error().
-//  * The per-step Iterate() methods are not provided.
+//  * The per-step Iterate() methods exist for the LSTM and GRU passes (the cells for which the
+//    reference has them in working order); the LayerNorm cells and IndRNN have Run() only.
 #pragma once
 
 #include <cuda_bf16.h>

@@ -1,6 +1,6 @@
 """Builds the REFERENCE's CUDA library for B200 into oracle/_ref/ (test infrastructure).
 
-    python oracle/build_ref.py [/path/to/haste]
+    python oracle/build_ref.py /path/to/haste      (or HASTE_REFERENCE_ROOT=/path/to/haste)
 
 Compiles the reference's own `lib/*.cu.cc`, untouched and where they lie, with nvcc
 for sm_100 (its Makefile targets compute_37/60/70, which CUDA 12.9 no longer
@@ -20,7 +20,20 @@ LIB = os.path.join(OUT, "libhaste_ref.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 
-def build(root="/root/reference", force=False):
+def reference_root():
+    """The reference checkout: $HASTE_REFERENCE_ROOT, else a `reference` directory beside
+    this repository (where the build driver mounts it), else None."""
+    env = os.environ.get("HASTE_REFERENCE_ROOT")
+    if env:
+        return env
+    sibling = os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return sibling if os.path.isdir(os.path.join(sibling, "lib")) else None
+
+
+def build(root=None, force=False):
+    root = root or reference_root()
+    if not root:
+        return LIB if os.path.exists(LIB) else None
     lib_dir = os.path.join(root, "lib")
     if not os.path.isdir(lib_dir):
         return None
@@ -49,4 +62,4 @@ def build(root="/root/reference", force=False):
 
 
 if __name__ == "__main__":
-    print(build(*(sys.argv[1:2] or ["/root/reference"]), force=True))
+    print(build(*(sys.argv[1:2]), force=True))
