@@ -131,22 +131,25 @@ def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    w = WORKLOAD
+    w = dict(WORKLOAD, T=args.T)
     threads = os.cpu_count() or 1
-    sample_T = 100
+    # the whole workload per timed step (a few seconds of CPU time each): same configuration
+    # as the GPU arm, not a sample of it
+    sample_T = w["T"]
     for _ in range(max(args.warmup, 1)):
         cpu_oracle_step(sample_T, w["N"], w["C"], w["H"], threads)
     times = [cpu_oracle_step(sample_T, w["N"], w["C"], w["H"], threads) for _ in range(args.steps)]
     sec = sum(times) / len(times)
     value = w["N"] * sample_T / sec
-    sample = f"T={sample_T} of {w['T']} steps per timed step, same N/C/H, float32 torch CPU"
+    sample = (f"all T={sample_T} steps per timed step, N={w['N']}, C={w['C']}, H={w['H']}, "
+              "float32 torch CPU, all host threads")
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": sec * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
         "data": "synthetic",
-        "config": {"workload": "lstm_N64_C512_H512_T1000_f32_fwd_bwd", "per_gpu_batch": 64,
-                   "sample": sample},
+        "config": {"workload": f"lstm_N{w['N']}_C{w['C']}_H{w['H']}_T{w['T']}_f32_fwd_bwd",
+                   "per_gpu_batch": w["N"], "sample": sample},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": threads, "kind": "port",
                          "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -162,12 +165,21 @@ def main():
     ap.add_argument("--dtype", default="f32", choices=["f32", "bf16"])
     ap.add_argument("--T", type=int, default=WORKLOAD["T"], help="override steps per sequence (tests)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--ref-cuda", action="store_true",
-                    help="also time the reference's own CUDA build if oracle/_ref holds it")
+    ap.add_argument("--no-ref-cuda", action="store_true",
+                    help="skip timing the reference's own CUDA build (oracle/_ref), which is "
+                         "timed by default wherever that library exists")
+    ap.add_argument("--ref-cuda", action="store_true", help=argparse.SUPPRESS)  # old spelling
+    ap.add_argument("--no-dp-parity", action="store_true",
+                    help="config4: skip the single-GPU whole-batch run that checks the reduced "
+                         "gradients (it needs the whole batch on rank 0)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="config4: issue the gradient all-reduces after the backward pass "
+                         "instead of from inside it")
     ap.add_argument("--workload", default="headline",
                     help="headline (default) | grid-<lstm|gru>-N<n>-H<h> | config2 | "
-                         "config3-indrnn | config3-lnindrnn | config4-N<n>: the other benchmark "
-                         "configurations, one JSON line each (single GPU)")
+                         "config3-indrnn | config3-lnindrnn | config4 (global batch 1024 sharded "
+                         "over the ranks, under torchrun) | config4-N<n> (per-GPU batch n): the "
+                         "other benchmark configurations, one JSON line each")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -289,10 +301,9 @@ def main():
         "input_grad": 2.0 * T * N * C * 4 * H,
     }
     # DRAM bytes per time step of the fp32 N=64 H=512 recurrence launches, from one ncu
-    # --set full capture at T=200 (dram__bytes_read.sum + dram__bytes_write.sum over 200
-    # steps; the summary is profiles/rec_kernels_and_gemm_T200_full_capture.md).  Every
-    # step touches its own slice of the activations once, so a launch's traffic is this
-    # times T.
+    # capture of each kernel at T=200 (dram__bytes_read.sum + dram__bytes_write.sum over
+    # the 200 steps).  Every step touches its own slice of the activations once, so a
+    # launch's traffic is this times T.
     ncu_bytes_per_step = {"recurrence_fwd": (109.377024e6 + 108.569600e6) / 200,
                           "recurrence_bwd": (188.644096e6 + 166.822912e6) / 200}
     dom = max(phases, key=phases.get)
@@ -334,15 +345,19 @@ def main():
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        sample_T = 100
-        cpu_oracle_step(sample_T, N, C, H, threads)
-        secs = sorted(cpu_oracle_step(sample_T, N, C, H, threads) for _ in range(3))
-        out["cpu_baseline"] = {"value": N * sample_T / secs[1], "unit": UNIT, "cores": threads,
+        cpu_oracle_step(T, N, C, H, threads)
+        secs = sorted(cpu_oracle_step(T, N, C, H, threads) for _ in range(3))
+        out["cpu_baseline"] = {"value": N * T / secs[1], "unit": UNIT, "cores": threads,
                                "kind": "port",
-                               "sample": f"T={sample_T} of {T} steps, same N/C/H, float32 torch CPU, "
-                                         "median of 3"}
-    if rank == 0 and world == 1 and args.ref_cuda:
-        out["reference_cuda"] = time_reference_cuda(T, N, C, H, x, W, R, b, dy, dc, h0, args.steps)
+                               "sample": f"the whole workload (all T={T} steps), float32 torch CPU, "
+                                         "1 warm-up + median of 3"}
+    if rank == 0 and world == 1 and not args.no_ref_cuda:
+        # the reference's own CUDA build on the same buffers: the denominator of the
+        # ">= 2x the reference CUDA build" target
+        out["reference_cuda"] = time_reference_cuda(T, N, C, H, x, W, R, b, dy, dc, h0,
+                                                    min(args.steps, 5))
+        if "ms_per_step" in out["reference_cuda"]:
+            out["reference_cuda"]["speedup"] = out["reference_cuda"]["ms_per_step"] / ms_step
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
@@ -362,6 +377,24 @@ def _event_ms(fn, steps, warmup):
     return e0.elapsed_time(e1) / steps
 
 
+def _event_and_wall_ms(fn, steps, warmup):
+    """(device ms, host wall ms) per call of `fn`, which launches on the legacy default stream
+    (the reference's own CUDA build does): events are recorded there."""
+    for _ in range(max(warmup, 1)):
+        fn()
+    torch.cuda.synchronize()
+    legacy = torch.cuda.default_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    e0.record(legacy)
+    for _ in range(steps):
+        fn()
+    e1.record(legacy)
+    torch.cuda.synchronize()
+    wall = (time.perf_counter() - t0) / steps * 1e3
+    return e0.elapsed_time(e1) / steps, wall
+
+
 def _wall_ms(fn, steps, warmup):
     for _ in range(max(warmup, 1)):
         fn()
@@ -373,32 +406,167 @@ def _wall_ms(fn, steps, warmup):
     return (time.perf_counter() - t0) / steps * 1e3
 
 
+# ---------------------------------------------------------------------------------------
+# The other benchmark configurations
+# ---------------------------------------------------------------------------------------
+def _peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        return json.load(open(path)), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}, "fallback"
+
+
+def _phases_of(fn, steps):
+    """Per-phase device milliseconds of one call of `fn` (library phase events)."""
+    from haste_b200 import _C
+    _C.profile_enable(True)
+    _C.profile_read()
+    for _ in range(steps):
+        fn()
+    torch.cuda.synchronize()
+    ph = {k: v / steps for k, v in _C.profile_read().items()}
+    _C.profile_enable(False)
+    return ph
+
+
+def _roofline(phases, alg_bytes, flops):
+    """Roofline entry of the phase that takes the most device time: HBM bytes for the
+    recurrence / scan phases, tensor FLOPs for the contraction phases."""
+    peaks, src = _peaks()
+    live = {k: v for k, v in phases.items() if v > 0 and (k in alg_bytes or k in flops)}
+    if not live:
+        return None
+    dom = max(live, key=live.get)
+    if dom in alg_bytes:
+        ach = alg_bytes[dom] / (phases[dom] * 1e-3) / 1e9
+        return {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"],
+                "unit": "GB/s", "frac": ach / peaks["hbm_gbs"], "traffic": None,
+                "algorithmic_bytes": alg_bytes[dom], "peak_source": src}
+    ach = flops[dom] / (phases[dom] * 1e-3) / 1e12
+    return {"kernel": dom, "bound": "tensor", "achieved": ach, "peak": peaks["bf16_tflops"],
+            "unit": "TFLOP/s", "frac": ach / peaks["bf16_tflops"], "traffic": None,
+            "algorithmic_flops": flops[dom], "peak_source": src}
+
+
+def _stack_work(cell, T, N, C, H, layers, dirs, es):
+    """Algorithmic HBM bytes of the recurrence phases and FLOPs of the contraction phases of
+    a whole stack (formulas per layer and direction, summed)."""
+    G = {"lstm": 4, "gru": 3, "indrnn": 1}[cell.replace("layer_norm_", "")]
+    ab = {"recurrence_fwd": 0.0, "recurrence_bwd": 0.0}
+    fl = {"input_projection": 0.0, "weight_grad": 0.0, "input_grad": 0.0}
+    for l in range(layers):
+        c = C if l == 0 else H * dirs
+        for _ in range(dirs):
+            if "indrnn" in cell:
+                # scan forward: read x.W and mask, write h; backward: read h, dh, mask, write dk
+                ab["recurrence_fwd"] += es * T * N * 3 * H
+                ab["recurrence_bwd"] += es * T * N * 4 * H
+                fl["weight_grad"] += 2.0 * T * N * H * c
+            else:
+                # forward: read x.W (G*H), write h (+c) and the gate cache; backward: read the
+                # cache, states and incoming gradients, write the gate gradients
+                states = 2 if "lstm" in cell else 1
+                cache = 4 * H
+                ab["recurrence_fwd"] += es * T * N * (G * H + states * H + cache)
+                ab["recurrence_bwd"] += es * T * N * (cache + 2 * states * H + (2 if G == 3 else 1) * G * H)
+                fl["weight_grad"] += 2.0 * T * N * G * H * (c + H)
+            fl["input_projection"] += 2.0 * T * N * G * H * c
+            fl["input_grad"] += 2.0 * T * N * G * H * c
+    return ab, fl
+
+
+def _ref_stack_step(cell, net, x, dy, dropconnect):
+    """One forward+backward of the same stack through the REFERENCE's own CUDA build, composed
+    from its single layers the way a user composes them (flip / run / flip back, concatenate),
+    fp32 only.  Returns a callable, or None where the reference has no such cell."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ref_cuda
+    if not ref_cuda.available() or x.dtype != torch.float32:
+        return None
+    fwd = getattr(ref_cuda, cell + "_forward")
+    bwd = getattr(ref_cuda, cell + "_backward")
+    has_c = "lstm" in cell
+
+    def params(layer):
+        p = dict(layer.named_parameters())
+        if "indrnn" in cell:
+            a = [p["kernel"], p["recurrent_scale"], p["bias"]]
+        elif "gru" in cell:
+            a = [p["kernel"], p["recurrent_kernel"], p["bias"], p["recurrent_bias"]]
+        else:
+            a = [p["kernel"], p["recurrent_kernel"], p["bias"]]
+        a += [p[k] for k in ("gamma", "gamma_h", "beta_h") if k in p]
+        return [t.detach() for t in a]
+
+    def step():
+        inp, tape = x, []
+        for level in net.layers:
+            outs, H = [], level[0].hidden_size
+            for d_, layer in enumerate(level):
+                xi = torch.flip(inp, [0]).contiguous() if d_ == 1 else inp
+                a = params(layer)
+                if dropconnect and "indrnn" not in cell:
+                    a[1] = a[1] * (torch.bernoulli(torch.full_like(a[1], 1 - dropconnect)) / (1 - dropconnect))
+                N = xi.shape[1]
+                z = xi.new_zeros(N, H)
+                mask = torch.bernoulli(torch.full((xi.shape[0], N, H), 0.9, device=xi.device)) \
+                    if layer.zoneout else None
+                st = (z, z) if has_c else (z,)
+                res = fwd(True, layer.zoneout, xi, *st, *a, mask)
+                res = (res,) if torch.is_tensor(res) else res
+                tape.append((xi, a, mask, res))
+                y = res[0][1:]
+                outs.append(torch.flip(y, [0]) if d_ == 1 else y)
+            inp = torch.cat(outs, -1) if len(outs) > 1 else outs[0]
+        g = dy
+        for level in reversed(net.layers):
+            H, dxs = level[0].hidden_size, []
+            for d_ in reversed(range(len(level))):
+                xi, a, mask, res = tape.pop()
+                gd = g[..., d_ * H:(d_ + 1) * H] if len(level) > 1 else g
+                gd = torch.flip(gd, [0]) if d_ == 1 else gd
+                dh = torch.cat([torch.zeros_like(gd[:1]), gd]).contiguous()
+                if has_c:
+                    grads = bwd(xi, *a, mask, *res, dh, torch.zeros_like(dh))
+                else:
+                    grads = bwd(xi, *a, mask, *res, dh)
+                dxi = grads["x"]
+                dxs.append(torch.flip(dxi, [0]) if d_ == 1 else dxi)
+            g = dxs[0] if len(dxs) == 1 else dxs[0] + dxs[1]
+    return step
+
+
 def run_config_workload(args):
-    """The benchmark configurations other than the headline, on one GPU, synthetic seeded
-    inputs of the configuration's shapes.  One JSON line; `value` is batch*steps/s of a
-    forward+backward pass of the whole (possibly stacked, bidirectional) network."""
+    """The benchmark configurations other than the headline, synthetic seeded inputs of the
+    configuration's shapes.  One JSON line: `value` is batch*steps/s of a forward+backward pass
+    of the whole (possibly stacked, bidirectional) network, with `phases_ms`, the `roofline`
+    of the dominant phase and, where the reference has the cell in fp32, `reference_cuda`."""
     import re
     import haste_b200 as hb
-    from haste_b200 import ops
+    from haste_b200 import _C, ops
+    name = args.workload
+    if re.fullmatch(r"config4(-N\d+)?", name):
+        return run_config4(args)
     torch.cuda.set_device(0)
     dev = torch.device("cuda", 0)
     dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
+    es = 4 if dtype == torch.float32 else 2
     steps, warmup = args.steps, max(args.warmup, 3)
-    name = args.workload
     torch.manual_seed(1234)
     out = {"workload": name, "unit": UNIT, "steps": steps, "warmup": warmup, "n_gpus": 1,
            "dtype": args.dtype, "data": "synthetic", "higher_is_better": True}
+    ref_step = None
 
-    def stack_step(net, x):
+    def stack_step(net, x, dy):
         def f():
             y = net(x)
-            y.backward(torch.ones_like(y))
+            y.backward(dy)
         return f
 
     m = re.fullmatch(r"grid-(lstm|gru)-N(\d+)-H(\d+)", name)
     if m:
         cell, N, H = m.group(1), int(m.group(2)), int(m.group(3))
-        T, C = 1000, H
+        T, C = args.T, H
         G = 4 if cell == "lstm" else 3
         g = torch.Generator().manual_seed(7)
         x = torch.randn(T, N, C, generator=g).to(dev, dtype)
@@ -420,88 +588,220 @@ def run_config_workload(args):
                 h, v = ops.gru_forward(True, 0.0, x, h0, W, R, bz, bz, nomask)
                 ops.gru_backward(x, W, R, bz, bz, nomask, h, v, dy, transposed=False)
             infer = lambda: ops.gru_forward(False, 0.0, x, h0, W, R, bz, bz, nomask)
-        ms, ms_inf = _event_ms(train, steps, warmup), _event_ms(infer, steps, warmup)
+        ms_inf = _event_ms(infer, steps, warmup)
         out.update(metric=f"{cell.upper()} fwd+bwd batch*steps/sec (N={N},H=C={H},T={T})",
-                   value=N * T / (ms * 1e-3), ms_per_step=ms,
                    forward_only={"value": N * T / (ms_inf * 1e-3), "ms_per_step": ms_inf})
-        if args.ref_cuda:
-            sys.path.insert(0, os.path.join(ROOT, "oracle"))
-            import ref_cuda
-            if ref_cuda.available() and dtype == torch.float32:
-                if cell == "lstm":
-                    def rtrain():
-                        h, c, v = ref_cuda.lstm_forward(True, 0.0, x, h0, h0, W, R, bz, None)
-                        ref_cuda.lstm_backward(x, W, R, bz, None, h, c, v, dy, dc)
-                    rinfer = lambda: ref_cuda.lstm_forward(False, 0.0, x, h0, h0, W, R, bz, None)
-                else:
-                    def rtrain():
-                        h, v = ref_cuda.gru_forward(True, 0.0, x, h0, W, R, bz, bz, None)
-                        ref_cuda.gru_backward(x, W, R, bz, bz, None, h, v, dy)
-                    rinfer = lambda: ref_cuda.gru_forward(False, 0.0, x, h0, W, R, bz, bz, None)
-                r, ri = _wall_ms(rtrain, min(steps, 3), 1), _wall_ms(rinfer, min(steps, 3), 1)
-                out["reference_cuda"] = {"ms_per_step": r, "forward_only_ms": ri,
-                                         "value": N * T / (r * 1e-3),
-                                         "timing": "host wall clock around synchronous calls"}
+        step, layers, dirs = train, 1, 1
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import ref_cuda
+        if ref_cuda.available() and dtype == torch.float32 and not args.no_ref_cuda:
+            if cell == "lstm":
+                def ref_step():
+                    h, c, v = ref_cuda.lstm_forward(True, 0.0, x, h0, h0, W, R, bz, None)
+                    ref_cuda.lstm_backward(x, W, R, bz, None, h, c, v, dy, dc)
             else:
-                out["reference_cuda"] = {"unavailable": "oracle/_ref not built or dtype not fp32"}
+                def ref_step():
+                    h, v = ref_cuda.gru_forward(True, 0.0, x, h0, W, R, bz, bz, None)
+                    ref_cuda.gru_backward(x, W, R, bz, bz, None, h, v, dy)
     elif name == "config2":
-        T, N, C, H = 400, 64, 80, 512
+        T, N, C, H = (400 if args.T == WORKLOAD["T"] else args.T), 64, 80, 512
+        cell, layers, dirs = "layer_norm_lstm", 3, 2
         net = hb.Stack(hb.LayerNormLSTM, C, H, num_layers=3, bidirectional=True, zoneout=0.1,
                        dropout=0.05).to(dev).to(dtype)
         net.train()
         x = torch.randn(T, N, C, device=dev, dtype=dtype, requires_grad=True)
-        ms = _event_ms(stack_step(net, x), steps, warmup)
-        out.update(metric="3-layer bidirectional LayerNormLSTM fwd+bwd batch*steps/sec "
-                          "(N=64,C=80,H=512,T=400, zoneout 0.1, DropConnect 0.05)",
-                   value=N * T / (ms * 1e-3), ms_per_step=ms)
+        dy = torch.randn(T, N, 2 * H, device=dev, dtype=dtype)
+        step = stack_step(net, x, dy)
+        out["metric"] = ("3-layer bidirectional LayerNormLSTM fwd+bwd batch*steps/sec "
+                         f"(N=64,C=80,H=512,T={T}, zoneout 0.1, DropConnect 0.05)")
+        if not args.no_ref_cuda:
+            ref_step = _ref_stack_step(cell, net, x.detach(), dy, 0.05)
     elif name in ("config3-indrnn", "config3-lnindrnn"):
-        T, N, C, H = 2000, 128, 1024, 1024
-        cls = hb.IndRNN if name.endswith("-indrnn") and "ln" not in name else hb.LayerNormIndRNN
+        T, N, C, H = (2000 if args.T == WORKLOAD["T"] else args.T), 128, 1024, 1024
+        cell = "indrnn" if name == "config3-indrnn" else "layer_norm_indrnn"
+        layers, dirs = 6, 1
+        cls = hb.IndRNN if cell == "indrnn" else hb.LayerNormIndRNN
         net = hb.Stack(cls, C, H, num_layers=6, zoneout=0.1).to(dev).to(dtype)
+        with torch.no_grad():
+            for level in net.layers:
+                level[0].recurrent_scale.uniform_(0.0, 1.0)
         net.train()
         x = torch.randn(T, N, C, device=dev, dtype=dtype, requires_grad=True)
-        ms = _event_ms(stack_step(net, x), steps, warmup)
-        out.update(metric=f"6-layer {cls.__name__} fwd+bwd batch*steps/sec (N=128,C=H=1024,T=2000)",
-                   value=N * T / (ms * 1e-3), ms_per_step=ms)
-    elif re.fullmatch(r"config4-N(\d+)", name):
-        N = int(name.split("N")[1])
-        T, C, H = 500, 512, 1024
-        dtype = torch.bfloat16
-        out["dtype"] = "bf16"
-        net = hb.Stack(hb.GRU, C, H, num_layers=4, bidirectional=True).to(dev).to(dtype)
-        net.train()
-        x = torch.randn(T, N, C, device=dev, dtype=dtype, requires_grad=True)
-        ms = _event_ms(stack_step(net, x), steps, warmup)
-        out.update(metric=f"4-layer bidirectional GRU bf16 fwd+bwd batch*steps/sec "
-                          f"(per-GPU N={N},C=512,H=1024,T=500)",
-                   value=N * T / (ms * 1e-3), ms_per_step=ms)
+        dy = torch.randn(T, N, H, device=dev, dtype=dtype)
+        step = stack_step(net, x, dy)
+        out["metric"] = f"6-layer {cls.__name__} fwd+bwd batch*steps/sec (N=128,C=H=1024,T={T})"
+        if not args.no_ref_cuda:
+            ref_step = _ref_stack_step(cell, net, x.detach(), dy, 0.0)
     else:
         raise SystemExit(f"unknown workload {name!r}")
+
+    ms = _event_ms(step, steps, warmup)
+    _C.sync_check(torch.cuda.current_stream().cuda_stream)
+    phases = _phases_of(step, min(steps, 3))
+    ab, fl = _stack_work(cell, T, N, C, H, layers, dirs, es)
+    out.update(value=N * T / (ms * 1e-3), ms_per_step=ms, phases_ms=phases,
+               roofline=_roofline(phases, ab, fl),
+               phase_tflops={k: fl[k] / (phases[k] * 1e-3) / 1e12 for k in fl if phases.get(k)},
+               phase_gbs={k: ab[k] / (phases[k] * 1e-3) / 1e9 for k in ab if phases.get(k)})
+    if ref_step is not None:
+        rms, rwall = _event_and_wall_ms(ref_step, min(steps, 3), 1)
+        out["reference_cuda"] = {"ms_per_step": rms, "wall_ms_per_step": rwall,
+                                 "value": N * T / (rms * 1e-3), "speedup": rms / ms,
+                                 "timing": "CUDA events on the legacy default stream"}
+    elif not args.no_ref_cuda:
+        out["reference_cuda"] = {"unavailable": "oracle/_ref not built, or the reference has no "
+                                                "such cell in this dtype"}
     print(json.dumps(out))
 
 
+def run_config4(args):
+    """Configuration 4: a data-parallel training step of a 4-layer bidirectional GRU in bf16,
+    C=512, H=1024, T=500.  `config4` shards a GLOBAL batch of 1024 evenly over the ranks
+    (strong scaling; launch under torchrun for more than one GPU); `config4-N<n>` runs a
+    per-GPU batch of n on one GPU.  Parameter gradients are written by each layer's backward
+    pass into that layer's bucket and all-reduced over NCCL from inside the backward pass, so
+    the collectives overlap the backward passes of the layers below."""
+    import haste_b200 as hb
+    from haste_b200 import _C, data_parallel
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+    T, C, H, layers = (500 if args.T == WORKLOAD["T"] else args.T), 512, 1024, 4
+    fixed = "-N" in args.workload
+    n_global = int(args.workload.split("N")[1]) * world if fixed else 1024
+    n_local = n_global // world
+    dtype = torch.bfloat16
+    torch.manual_seed(4321)  # same parameters on every rank
+    net = hb.Stack(hb.GRU, C, H, num_layers=layers, bidirectional=True).to(dev).to(dtype)
+    net.train()
+    data_parallel.broadcast_parameters(net)
+    g = torch.Generator().manual_seed(99)
+    x_all = torch.randn(T, n_global, C, generator=g).to(dtype)
+    dy_all = torch.randn(T, n_global, 2 * H, generator=g).to(dtype)
+    x = data_parallel.shard(x_all, rank, world).to(dev).requires_grad_(True)
+    dy = data_parallel.shard(dy_all, rank, world).to(dev)
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    def make_step(dp):
+        def f():
+            dp.zero_grad()
+            y = net(x)
+            y.backward(dy)
+            dp.finish()
+        return f
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def timed(fn, k, warm=warmup):
+        for _ in range(warm):
+            fn()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(k):
+            fn()
+        e1.record()
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1) / k], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    dp = data_parallel.attach(net, overlap=not args.no_overlap)
+    step = make_step(dp)
+    for _ in range(warmup):
+        step()
+    launches0 = _C.launch_count()
+    with ClockSampler(local) as clocks:
+        ms = timed(step, steps, warm=0)
+    launches = _C.launch_count() - launches0
+    _C.sync_check(torch.cuda.current_stream().cuda_stream)
+    grads = {k: v.grad.float().clone() for k, v in net.named_parameters()}
+    bucket_bytes = dp.bucket_bytes()
+    dp.detach()
+    # the same step without any collective: what communication adds when it is exposed
+    dp0 = data_parallel.attach(net, reduce=False)
+    ms_nocomm = timed(make_step(dp0), max(2, steps // 2)) if world > 1 else ms
+    dp0.detach()
+    phases = _phases_of(make_step(data_parallel.attach(net, reduce=False)), 2)
+    for m_ in net.modules():
+        if hasattr(m_, "_dp"):
+            m_._dp = None
+
+    # parity of the reduced gradients with a single-GPU run of the whole batch (rank 0)
+    dp_err = None
+    if world > 1 and rank == 0 and not args.no_dp_parity:
+        for p in net.parameters():
+            p.grad = None
+        xf = x_all.to(dev).requires_grad_(True)
+        net(xf).backward(dy_all.to(dev))
+        torch.cuda.synchronize()
+        dp_err = 0.0
+        for k, v in net.named_parameters():
+            want = v.grad.float()
+            dp_err = max(dp_err, float((grads[k] - want).abs().max() / max(float(want.abs().max()), 1e-6)))
+    ab, fl = _stack_work("gru", T, n_local, C, H, layers, 2, 2)
+    total_flops = 6.0 * T * n_global * 3 * H * ((C + H) + (layers - 1) * (2 * H + H)) * 2
+    peaks, src = _peaks()
+    out = {
+        "workload": args.workload, "metric": "4-layer bidirectional GRU bf16 data-parallel fwd+bwd "
+        f"batch*steps/sec (global N={n_global}, C=512, H=1024, T={T})",
+        "value": n_global * T / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": steps,
+        "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "weak" if fixed else "strong", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic",
+        "config": {"workload": args.workload, "global_batch": n_global, "per_gpu_batch": n_local,
+                   "layers": layers, "bidirectional": True,
+                   "grad_allreduce": "per layer and direction, issued from inside the backward pass"
+                   if not args.no_overlap else "after the backward pass",
+                   "bucket_bytes_per_step": bucket_bytes,
+                   "l2": "inputs larger than L2"},
+        "gpu_launches": int(launches), "clocks": clocks.summary(),
+        "ms_per_step_without_allreduce": ms_nocomm,
+        "exposed_communication_ms": max(ms - ms_nocomm, 0.0),
+        "dp_parity_err": dp_err,
+        "tflops": total_flops / (ms * 1e-3) / 1e12,
+        "tensor_frac_of_peak": total_flops / world / (ms * 1e-3) / 1e12 / peaks["bf16_tflops"],
+        "phases_ms": phases, "roofline": _roofline(phases, ab, fl),
+        "phase_tflops": {k: fl[k] / (phases[k] * 1e-3) / 1e12 for k in fl if phases.get(k)},
+    }
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def time_reference_cuda(T, N, C, H, x, W, R, b, dy, dc, h0, steps):
-    """Times the reference's own CUDA build (fp32) on the same buffers, including the
-    three transposes its backward needs (as its own benchmark does)."""
+    """Times the reference's own CUDA build (fp32) on the same buffers, including the three
+    transposes its backward pass needs (its own benchmark charges them too).  Device time by
+    CUDA events on the stream the reference runs on, host wall clock beside it (the
+    reference's LSTM passes block the host when they are destroyed)."""
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import ref_cuda
-    if not ref_cuda.available() or x.dtype != torch.float32:
-        return {"unavailable": "oracle/_ref/libhaste_ref.so not built or dtype not fp32"}
+    if not ref_cuda.available():
+        return {"unavailable": "oracle/_ref/libhaste_ref.so is not built on this machine"}
+    if x.dtype != torch.float32:
+        return {"unavailable": "the reference has no bf16 build"}
 
     def one():
         h, c, v = ref_cuda.lstm_forward(True, 0.0, x, h0, h0, W, R, b, None)
         ref_cuda.lstm_backward(x, W, R, b, None, h, c, v, dy, dc)
 
-    for _ in range(2):
-        one()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        one()
-    torch.cuda.synchronize()
-    sec = (time.perf_counter() - t0) / steps
-    return {"value": N * T / sec, "unit": UNIT, "ms_per_step": sec * 1e3,
-            "timing": "host wall clock around synchronous calls (the reference blocks the host)"}
+    ms, wall = _event_and_wall_ms(one, steps, 2)
+    return {"value": N * T / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "wall_ms_per_step": wall,
+            "steps": steps,
+            "timing": "CUDA events on the legacy default stream the reference launches on; "
+                      "includes its three transposes"}
 
 
 if __name__ == "__main__":

@@ -9,7 +9,7 @@ import os
 _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libhaste_b200.so")
 
-F32, BF16, F16 = 0, 1, 2
+F32, BF16, F16, BF16_WIDE = 0, 1, 2, 3
 PATH_AUTO, PATH_STEPWISE, PATH_PERSISTENT = 0, 1, 2
 GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05 = 0, 1, 2
 

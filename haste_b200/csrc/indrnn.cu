@@ -143,10 +143,16 @@ int indrnn_forward(const IndrnnFwd& a, cudaStream_t s) {
   void* proj = a.gamma ? a.act_Wx : a.workspace;
   GemmDesc g{a.dtype, a.dtype, (int)TN, a.H, a.C, a.x, a.C, 1, a.W, a.H, 1, proj, a.H, 0};
   g.precise = a.gamma ? 1 : 0;
-  HB_TRY(gemm(g, s));
-  if (a.gamma)
+  {
+    ProfScope p(PH_PROJ, s);
+    HB_TRY(gemm(g, s));
+  }
+  if (a.gamma) {
+    ProfScope p(PH_OTHER, s);
     HB_TRY(layer_norm_forward(a.dtype, (int)TN, a.H, a.gamma, nullptr, a.act_Wx, a.workspace,
                               a.cache_Wx, s));
+  }
+  ProfScope p(PH_REC_FWD, s);
   if (a.dtype == HASTE_B200_F32) return scan_fwd<float>(a, a.workspace, s);
   return scan_fwd<__nv_bfloat16>(a, a.workspace, s);
 }
@@ -174,12 +180,16 @@ int indrnn_backward(const IndrnnBwd& a, cudaStream_t s) {
   float* lns = ws.take<float>(lnf);
   HB_REQUIRE(dh_carry && du_part && db_part && cs && (lns || !lnf), "scratch arena");
   HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
-  if (a.dtype == HASTE_B200_F32) HB_TRY(scan_bwd<float>(a, du_part, db_part, dh_carry, s));
-  else HB_TRY(scan_bwd<__nv_bfloat16>(a, du_part, db_part, dh_carry, s));
+  {
+    ProfScope p(PH_REC_BWD, s);
+    if (a.dtype == HASTE_B200_F32) HB_TRY(scan_bwd<float>(a, du_part, db_part, dh_carry, s));
+    else HB_TRY(scan_bwd<__nv_bfloat16>(a, du_part, db_part, dh_carry, s));
+  }
   HB_TRY(from_float(a.dtype, dh_carry, a.dh, NH, s));
   HB_TRY(colsum(HASTE_B200_F32, du_part, H, N, H, a.dtype, a.du, 1, cs, s));
   HB_TRY(colsum(HASTE_B200_F32, db_part, H, N, H, a.dtype, a.db, 1, cs, s));
   if (a.gamma) {
+    ProfScope p(PH_OTHER, s);
     // workspace holds dk = d/d(LN(x.W)); turn it into d/d(x.W) in place.
     HB_TRY(layer_norm_backward(a.dtype, (int)TN, H, a.gamma, a.act_Wx, a.workspace, a.workspace,
                                a.dtype, a.dgamma, nullptr, a.cache_Wx, lns, s));
@@ -189,11 +199,17 @@ int indrnn_backward(const IndrnnBwd& a, cudaStream_t s) {
   GemmDesc gw{a.dtype, a.dtype, C, H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.workspace, H, 1,
               a.dW, H, 0};
   gw.precise = a.gamma ? 1 : 0;
-  HB_TRY(gemm(gw, s));
+  {
+    ProfScope p(PH_WGRAD, s);
+    HB_TRY(gemm(gw, s));
+  }
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, H, a.workspace, H, 1, a.W, tr ? C : 1, tr ? 1 : H,
               a.dx, C, 0};
   gx.precise = a.gamma ? 1 : 0;
-  HB_TRY(gemm(gx, s));
+  {
+    ProfScope p(PH_DGRAD, s);
+    HB_TRY(gemm(gx, s));
+  }
   return HASTE_B200_OK;
 }
 

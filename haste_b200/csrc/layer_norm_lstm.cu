@@ -214,30 +214,8 @@ int backward_steps(const LnLstmBwd& a, float* dh_carry, float* dc_carry, void* d
   return HASTE_B200_OK;
 }
 
-}  // namespace
-
-int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
-  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
-  HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
-  HB_REQUIRE(a.W && a.R && a.b && a.gamma_Wx && a.gamma_Rh && a.gamma_h && a.beta_h && a.h && a.c && a.act_Wx &&
-                 a.act_Wx_norm && a.cache_Wx && a.act_Rh && a.cache_Rh && a.act_c_norm &&
-                 a.cache_c && a.tmp_Rh, "null pointer");
-  if (a.T == 0) return HASTE_B200_OK;
-  HB_REQUIRE(a.x, "x is null");
-  const long long TN = (long long)a.T * a.N;
-  HB_REQUIRE(TN < (1LL << 31), "T*N too large");
-  GemmDesc g{a.dtype, a.dtype, (int)TN, 4 * a.H, a.C, a.x, a.C, 1, a.W, 4LL * a.H, 1, a.act_Wx,
-             4LL * a.H, 0};
-  g.precise = 1;
-  {
-    ProfScope p(PH_PROJ, s);
-    HB_TRY(gemm(g, s));
-  }
-  {
-    ProfScope p(PH_OTHER, s);
-    HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma_Wx, nullptr, a.act_Wx,
-                              a.act_Wx_norm, a.cache_Wx, s));
-  }
+// Recurrence part of the forward pass: LN(x.W) is in a.act_Wx_norm.
+int forward_recurrence(const LnLstmFwd& a, cudaStream_t s) {
   ProfScope prec(PH_REC_FWD, s);
   {
     const int st_ = layer_norm_lstm_forward_persistent(a, s);
@@ -254,8 +232,183 @@ int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
   return forward_steps<__nv_bfloat16>(a, rh_f32, c_f32, s);
 }
 
+int backward_core(const LnLstmBwd& a, cudaStream_t s);
+
+// ---- HASTE_B200_BF16_WIDE --------------------------------------------------------------
+// bf16 tensors at the interface (x, parameters, h, c, masks, incoming and outgoing gradients),
+// fp32 everywhere a value is carried from one step to the next or saved for the backward
+// pass.  Three LayerNorms per step amplify a relative perturbation of their inputs about
+// tenfold and the recurrence feeds it back, so rounding x.W, LN(x.W) or the running h to bf16
+// moves outputs and gradients by 2e-2 .. 1e-1 over a few dozen steps however exact the
+// arithmetic is.  In this mode only the copies of h and c handed to the caller are rounded:
+// the pass converts the bf16 operands to fp32 scratch once and runs the fp32 kernels on them.
+constexpr int kWideSlot = 4;
+
+int forward_wide(const LnLstmFwd& a, cudaStream_t s) {
+  const int T = a.T, N = a.N, C = a.C, H = a.H;
+  const long long TN = (long long)T * N;
+  const size_t NH = (size_t)N * H, RW = (size_t)H * 4 * H;
+  const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
+  const int BF = HASTE_B200_BF16;
+  Arena ws;
+  const size_t bytes = Arena::pad(RW * 4) + 3 * Arena::pad((size_t)4 * H * 4) +
+                       2 * Arena::pad((size_t)H * 4) + 2 * Arena::pad((T + 1) * NH * 4) +
+                       (zo ? Arena::pad(T * NH * 4) : 0) + 4096;
+  HB_TRY(make_arena(&ws, s, bytes, kWideSlot));
+  float* R = ws.take<float>(RW);
+  float* b = ws.take<float>(4 * H);
+  float* gWx = ws.take<float>(4 * H);
+  float* gRh = ws.take<float>(4 * H);
+  float* gh = ws.take<float>(H);
+  float* bh = ws.take<float>(H);
+  float* h = ws.take<float>((T + 1) * NH);
+  float* c = ws.take<float>((T + 1) * NH);
+  float* mask = zo ? ws.take<float>(T * NH) : nullptr;
+  HB_REQUIRE(R && b && gWx && gRh && gh && bh && h && c && (!zo || mask), "scratch arena");
+  HB_TRY(to_float(BF, a.R, R, RW, s));
+  HB_TRY(to_float(BF, a.b, b, 4 * H, s));
+  HB_TRY(to_float(BF, a.gamma_Wx, gWx, 4 * H, s));
+  HB_TRY(to_float(BF, a.gamma_Rh, gRh, 4 * H, s));
+  HB_TRY(to_float(BF, a.gamma_h, gh, H, s));
+  HB_TRY(to_float(BF, a.beta_h, bh, H, s));
+  HB_TRY(to_float(BF, a.h, h, NH, s));  // slot 0: the initial state
+  HB_TRY(to_float(BF, a.c, c, NH, s));
+  if (zo) HB_TRY(to_float(BF, a.zoneout_mask, mask, T * NH, s));
+  // x.W: bf16 operands are exact in the tensor-core product; the fp32 accumulator is stored
+  // unrounded
+  GemmDesc g{BF, HASTE_B200_F32, (int)TN, 4 * H, C, a.x, C, 1, a.W, 4LL * H, 1, a.act_Wx,
+             4LL * H, 0};
+  {
+    ProfScope p(PH_PROJ, s);
+    HB_TRY(gemm(g, s));
+  }
+  {
+    ProfScope p(PH_OTHER, s);
+    HB_TRY(layer_norm_forward(HASTE_B200_F32, (int)TN, 4 * H, gWx, nullptr, a.act_Wx,
+                              a.act_Wx_norm, a.cache_Wx, s));
+  }
+  LnLstmFwd f = a;
+  f.dtype = HASTE_B200_F32;
+  f.R = R; f.b = b; f.gamma_Wx = gWx; f.gamma_Rh = gRh; f.gamma_h = gh; f.beta_h = bh;
+  f.h = h; f.c = c; f.zoneout_mask = mask;
+  HB_TRY(forward_recurrence(f, s));
+  HB_TRY(from_float(BF, h + NH, static_cast<char*>(a.h) + NH * 2, (size_t)T * NH, s));
+  HB_TRY(from_float(BF, c + NH, static_cast<char*>(a.c) + NH * 2, (size_t)T * NH, s));
+  return HASTE_B200_OK;
+}
+
+int backward_wide(const LnLstmBwd& a, cudaStream_t s) {
+  const int T = a.T, N = a.N, C = a.C, H = a.H;
+  const size_t NH = (size_t)N * H, RW = (size_t)H * 4 * H, WW = (size_t)C * 4 * H;
+  const size_t XN = (size_t)T * N * C, SN = (size_t)(T + 1) * NH;
+  const int BF = HASTE_B200_BF16;
+  Arena ws;
+  const size_t bytes = 2 * Arena::pad(RW * 4) + 2 * Arena::pad(WW * 4) +
+                       5 * Arena::pad((size_t)4 * H * 4) + 4 * Arena::pad((size_t)H * 4) +
+                       2 * Arena::pad(XN * 4) + 4 * Arena::pad(SN * 4) + 2 * Arena::pad(NH * 4) +
+                       (a.zoneout_mask ? Arena::pad((size_t)T * NH * 4) : 0) + 8192;
+  HB_TRY(make_arena(&ws, s, bytes, kWideSlot));
+  float* R = ws.take<float>(RW);
+  float* dR = ws.take<float>(RW);
+  float* W = ws.take<float>(WW);
+  float* dW = ws.take<float>(WW);
+  float* gWx = ws.take<float>(4 * H);
+  float* gRh = ws.take<float>(4 * H);
+  float* db = ws.take<float>(4 * H);
+  float* dgWx = ws.take<float>(4 * H);
+  float* dgRh = ws.take<float>(4 * H);
+  float* gh = ws.take<float>(H);
+  float* bh = ws.take<float>(H);
+  float* dgh = ws.take<float>(H);
+  float* dbh = ws.take<float>(H);
+  float* x = ws.take<float>(XN);
+  float* dx = ws.take<float>(XN);
+  float* h = ws.take<float>(SN);
+  float* c = ws.take<float>(SN);
+  float* dhn = ws.take<float>(SN);
+  float* dcn = ws.take<float>(SN);
+  float* dh = ws.take<float>(NH);
+  float* dc = ws.take<float>(NH);
+  float* mask = a.zoneout_mask ? ws.take<float>((size_t)T * NH) : nullptr;
+  HB_REQUIRE(R && dR && W && dW && gWx && gRh && db && dgWx && dgRh && gh && bh && dgh && dbh &&
+                 x && dx && h && c && dhn && dcn && dh && dc && (!a.zoneout_mask || mask),
+             "scratch arena");
+  HB_TRY(to_float(BF, a.R, R, RW, s));
+  HB_TRY(to_float(BF, a.W, W, WW, s));
+  HB_TRY(to_float(BF, a.gamma_Wx, gWx, 4 * H, s));
+  HB_TRY(to_float(BF, a.gamma_Rh, gRh, 4 * H, s));
+  HB_TRY(to_float(BF, a.gamma_h, gh, H, s));
+  if (a.beta_h) HB_TRY(to_float(BF, a.beta_h, bh, H, s));
+  HB_TRY(to_float(BF, a.x, x, XN, s));
+  HB_TRY(to_float(BF, a.h, h, SN, s));
+  HB_TRY(to_float(BF, a.c, c, SN, s));
+  HB_TRY(to_float(BF, a.dh_new, dhn, SN, s));
+  HB_TRY(to_float(BF, a.dc_new, dcn, SN, s));
+  HB_TRY(to_float(BF, a.dh, dh, NH, s));
+  HB_TRY(to_float(BF, a.dc, dc, NH, s));
+  if (mask) HB_TRY(to_float(BF, a.zoneout_mask, mask, (size_t)T * NH, s));
+  // accumulated outputs: the fp32 pass adds into zeroed scratch, the sums go into the
+  // caller's bf16 tensors afterwards
+  HB_CUDA_OK(cudaMemsetAsync(dR, 0, RW * 4, s));
+  HB_CUDA_OK(cudaMemsetAsync(dW, 0, WW * 4, s));
+  HB_CUDA_OK(cudaMemsetAsync(db, 0, (size_t)4 * H * 4, s));
+  HB_CUDA_OK(cudaMemsetAsync(dgWx, 0, (size_t)4 * H * 4, s));
+  HB_CUDA_OK(cudaMemsetAsync(dgRh, 0, (size_t)4 * H * 4, s));
+  HB_CUDA_OK(cudaMemsetAsync(dgh, 0, (size_t)H * 4, s));
+  HB_CUDA_OK(cudaMemsetAsync(dbh, 0, (size_t)H * 4, s));
+  LnLstmBwd f = a;
+  f.dtype = HASTE_B200_F32;
+  f.W = W; f.R = R; f.gamma_Wx = gWx; f.gamma_Rh = gRh; f.gamma_h = gh;
+  f.beta_h = a.beta_h ? bh : nullptr;
+  f.x = x; f.h = h; f.c = c; f.dh_new = dhn; f.dc_new = dcn; f.dx = dx; f.dW = dW; f.dR = dR;
+  f.db = db; f.dgamma_Wx = dgWx; f.dgamma_Rh = dgRh; f.dgamma_h = dgh; f.dbeta_h = dbh;
+  f.dh = dh; f.dc = dc; f.zoneout_mask = mask;
+  HB_TRY(backward_core(f, s));
+  HB_TRY(from_float(BF, dx, a.dx, XN, s));
+  HB_TRY(from_float(BF, dh, a.dh, NH, s));
+  HB_TRY(from_float(BF, dc, a.dc, NH, s));
+  HB_TRY(add_float_into(BF, dW, a.dW, WW, s));
+  HB_TRY(add_float_into(BF, dR, a.dR, RW, s));
+  HB_TRY(add_float_into(BF, db, a.db, 4 * H, s));
+  HB_TRY(add_float_into(BF, dgWx, a.dgamma_Wx, 4 * H, s));
+  HB_TRY(add_float_into(BF, dgRh, a.dgamma_Rh, 4 * H, s));
+  HB_TRY(add_float_into(BF, dgh, a.dgamma_h, H, s));
+  HB_TRY(add_float_into(BF, dbh, a.dbeta_h, H, s));
+  return HASTE_B200_OK;
+}
+
+}  // namespace
+
+int layer_norm_lstm_forward(const LnLstmFwd& a, cudaStream_t s) {
+  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16 ||
+                 a.dtype == HASTE_B200_BF16_WIDE, "dtype");
+  HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
+  HB_REQUIRE(a.W && a.R && a.b && a.gamma_Wx && a.gamma_Rh && a.gamma_h && a.beta_h && a.h && a.c && a.act_Wx &&
+                 a.act_Wx_norm && a.cache_Wx && a.act_Rh && a.cache_Rh && a.act_c_norm &&
+                 a.cache_c && a.tmp_Rh, "null pointer");
+  if (a.T == 0) return HASTE_B200_OK;
+  HB_REQUIRE(a.x, "x is null");
+  const long long TN = (long long)a.T * a.N;
+  HB_REQUIRE(TN < (1LL << 31), "T*N too large");
+  if (a.dtype == HASTE_B200_BF16_WIDE) return forward_wide(a, s);
+  GemmDesc g{a.dtype, a.dtype, (int)TN, 4 * a.H, a.C, a.x, a.C, 1, a.W, 4LL * a.H, 1, a.act_Wx,
+             4LL * a.H, 0};
+  g.precise = 1;
+  {
+    ProfScope p(PH_PROJ, s);
+    HB_TRY(gemm(g, s));
+  }
+  {
+    ProfScope p(PH_OTHER, s);
+    HB_TRY(layer_norm_forward(a.dtype, (int)TN, 4 * a.H, a.gamma_Wx, nullptr, a.act_Wx,
+                              a.act_Wx_norm, a.cache_Wx, s));
+  }
+  return forward_recurrence(a, s);
+}
+
 int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
-  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16, "dtype");
+  HB_REQUIRE(a.dtype == HASTE_B200_F32 || a.dtype == HASTE_B200_BF16 ||
+                 a.dtype == HASTE_B200_BF16_WIDE, "dtype");
   HB_REQUIRE(a.T >= 0 && a.N > 0 && a.C > 0 && a.H > 0, "T,N,C,H");
   HB_REQUIRE(a.W && a.R && a.gamma_Wx && a.gamma_Rh && a.gamma_h && a.h && a.c && a.dh_new && a.dc_new && a.dW &&
                  a.dR && a.db && a.dgamma_Wx && a.dgamma_Rh && a.dgamma_h && a.dbeta_h && a.dh && a.dc &&
@@ -263,9 +416,15 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
                  a.act_c_norm && a.cache_c, "null pointer");
   if (a.T == 0) return HASTE_B200_OK;
   HB_REQUIRE(a.x && a.dx, "x/dx is null");
+  HB_REQUIRE((long long)a.T * a.N < (1LL << 31), "T*N too large");
+  if (a.dtype == HASTE_B200_BF16_WIDE) return backward_wide(a, s);
+  return backward_core(a, s);
+}
+
+namespace {
+int backward_core(const LnLstmBwd& a, cudaStream_t s) {
   const int N = a.N, H = a.H, C = a.C;
   const long long TN = (long long)a.T * N;
-  HB_REQUIRE(TN < (1LL << 31), "T*N too large");
   const size_t NH = (size_t)N * H;
   const bool bf = a.dtype == HASTE_B200_BF16;
   const size_t csf = colsum_scratch_floats((int)TN, 4 * H);
@@ -344,5 +503,7 @@ int layer_norm_lstm_backward(const LnLstmBwd& a, cudaStream_t s) {
   }
   return HASTE_B200_OK;
 }
+
+}  // namespace
 
 }  // namespace hb

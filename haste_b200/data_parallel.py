@@ -15,7 +15,11 @@ it is tested):
   launch-latency-sized collective per bucket instead of one per tensor);
 * `GradientBucket` is the flat buffer itself, handed to a backward op as its gradient
   outputs: the weight-gradient contractions and the bias column sums write straight into the
-  buffer that the collective then reduces, with no pack before it and no scatter after.
+  buffer that the collective then reduces, with no pack before it and no scatter after;
+* `attach` wires a whole network (`haste_b200.Stack` or single layers) for this: one bucket
+  per layer and direction, its all-reduce started the moment that layer's backward pass has
+  queued its weight-gradient contractions, so that the collective runs under the backward
+  pass of the layers below and only the last one is exposed.
 
 The reference has no multi-GPU path; its layers are used under the framework's own data
 parallel wrappers, which this mirrors.
@@ -24,7 +28,7 @@ import torch
 import torch.distributed as dist
 
 __all__ = ["shard", "dropconnect_mask", "broadcast_parameters", "all_reduce_tensors",
-           "all_reduce_gradients", "GradientBucket"]
+           "all_reduce_gradients", "GradientBucket", "attach", "DataParallel"]
 
 
 def _world(group=None):
@@ -191,3 +195,99 @@ def _numel(shape):
     for d in shape:
         n *= int(d)
     return n
+
+
+_CELL_OF_CLASS = {"LSTM": "lstm", "GRU": "gru", "IndRNN": "indrnn",
+                  "LayerNormLSTM": "layer_norm_lstm", "LayerNormGRU": "layer_norm_gru",
+                  "LayerNormIndRNN": "layer_norm_indrnn"}
+
+
+class _LayerHook:
+    """What a layer's autograd function sees of the data-parallel wiring: the bucket its
+    backward op writes into, and `gradients_ready`, called once that op has been queued."""
+
+    def __init__(self, owner, layer):
+        cell = _CELL_OF_CLASS[type(layer).__name__]
+        p = next(layer.parameters())
+        self.owner, self.layer = owner, layer
+        self.bucket = GradientBucket.for_cell(cell, layer.input_size, layer.hidden_size, p.dtype,
+                                              p.device)
+        self.recurrent_scale = None  # DropConnect mask / (1 - p) of the current step, if any
+        self.views = None            # parameter name -> view of the bucket
+        self.work = None
+
+    def gradients_ready(self, views):
+        self.views = views
+        self.owner.order.append(self)
+        if self.owner.overlap and self.owner.reduce:
+            self.work = self.bucket.all_reduce(self.owner.group, async_op=True)
+
+
+class DataParallel:
+    """Batch-sharded data parallelism for a network of haste_b200 layers.
+
+        dp = data_parallel.attach(net)          # after net.cuda(), inside an initialised group
+        for step in ...:
+            dp.zero_grad()
+            y = net(shard(x, rank, world)); loss(y).backward()
+            dp.finish()                         # gradients summed over the ranks, in p.grad
+            optimiser.step()
+
+    Every rank runs its slice of the batch; the parameter gradients of each layer and
+    direction are written by that layer's backward pass straight into one flat buffer, whose
+    all-reduce (NCCL: on the communicator's own stream) is issued as soon as the pass is queued
+    and therefore overlaps the backward passes of the layers below it.  `finish` makes the
+    current stream wait for the collectives and points every parameter's `.grad` at its summed
+    view.  With DropConnect the buffer holds the gradient of the masked recurrent kernel; the
+    mask (identical on every rank, see `dropconnect_mask`) is applied after the sum, which is
+    the same by linearity.  `overlap=False` issues the collectives in `finish` instead (to
+    measure what the overlap hides); `reduce=False` skips them.
+    """
+
+    def __init__(self, net, group=None, overlap=True, reduce=True):
+        self.group, self.overlap, self.reduce = group, overlap, reduce
+        self.hooks, self.order = [], []
+        for m in net.modules():
+            if type(m).__name__ in _CELL_OF_CLASS and hasattr(m, "_dp"):
+                hook = _LayerHook(self, m)
+                m._dp = hook
+                self.hooks.append(hook)
+        if not self.hooks:
+            raise ValueError("no haste_b200 layer found in the module")
+
+    def zero_grad(self):
+        """Zeroes the buckets (the backward ops accumulate into them) and drops the layers'
+        `.grad` references to them.  Call before each forward pass."""
+        self.order = []
+        for h in self.hooks:
+            h.bucket.reset()
+            h.views, h.work = None, None
+            for p in h.layer.parameters():
+                p.grad = None
+
+    def bucket_bytes(self):
+        return sum(h.bucket.flat.numel() * h.bucket.flat.element_size() for h in self.hooks)
+
+    def finish(self):
+        """Waits (on the current stream) for the gradient sums and installs them as `.grad`."""
+        for h in self.order:
+            if self.reduce and not self.overlap:
+                h.work = h.bucket.all_reduce(self.group, async_op=True)
+            if h.work is not None:
+                h.work.wait()
+                h.work = None
+            for name, view in h.views.items():
+                if name == "recurrent_kernel" and h.recurrent_scale is not None:
+                    view = view * h.recurrent_scale
+                getattr(h.layer, name).grad = view
+        self.order = []
+
+    def detach(self):
+        for h in self.hooks:
+            h.layer._dp = None
+
+
+def attach(net, group=None, overlap=True, reduce=True):
+    """Wires `net` (any module containing haste_b200 layers) for batch-sharded data
+    parallelism; see `DataParallel`."""
+    return DataParallel(net, group=group, overlap=overlap, reduce=reduce)

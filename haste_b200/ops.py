@@ -25,6 +25,18 @@ def _dtype(t):
                     f"got {t.dtype}")
 
 
+def _ln_lstm_dtype(t, saved):
+    """Library dtype of a LayerNormLSTM call: bfloat16 tensors with float32 saved activations
+    are the BF16_WIDE mode."""
+    d = _dtype(t)
+    if saved.dtype == t.dtype:
+        return d
+    if d == _C.BF16 and saved.dtype == torch.float32:
+        return _C.BF16_WIDE
+    raise RuntimeError("haste_b200: LayerNormLSTM saved activations must be float32 or the "
+                       "layer's own dtype")
+
+
 def _check(*tensors):
     dev, dt = tensors[0].device, tensors[0].dtype
     for t in tensors:
@@ -246,7 +258,7 @@ def indrnn_backward(x, kernel, recurrent_scale, bias, zoneout_mask, h, dh_new, t
 
 # ---------------------------------------------------------------- LayerNormLSTM
 def layer_norm_lstm_forward(training, zoneout_prob, x, h0, c0, kernel, recurrent_kernel, bias,
-                            gamma, gamma_h, beta_h, zoneout_mask):
+                            gamma, gamma_h, beta_h, zoneout_mask, saved_dtype=torch.float32):
     _check(x, h0, c0, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h, zoneout_mask)
     T, N, C, H = _dims_fwd(x, recurrent_kernel)
     with torch.cuda.device(x.device):
@@ -254,16 +266,22 @@ def layer_norm_lstm_forward(training, zoneout_prob, x, h0, c0, kernel, recurrent
         c = x.new_empty(T + 1, N, H)
         h[0] = h0
         c[0] = c0
-        act_Wx = x.new_empty(T, N, 4 * H)
-        act_Wx_norm = x.new_empty(T, N, 4 * H)
-        cache_Wx = x.new_empty(T, N, 2)
-        act_Rh = x.new_empty(T, N, 4 * H)
-        cache_Rh = x.new_empty(T, N, 2)
-        act_c_norm = x.new_empty(T, N, H)
-        cache_c = x.new_empty(T, N, 2)
-        tmp_Rh = x.new_empty(N, 4 * H)
+        # what the forward pass leaves for the backward pass is float32 whatever the layer's
+        # dtype: with bfloat16 tensors the op runs in the library's BF16_WIDE mode (see the
+        # header), because rounding these to bfloat16 alone costs 2e-2 .. 1e-1 of accuracy.
+        # saved_dtype=torch.bfloat16 selects the library's all-bfloat16 mode instead (the
+        # one a C++ caller with __nv_bfloat16 buffers gets).
+        sd = saved_dtype if x.dtype == torch.bfloat16 else x.dtype
+        act_Wx = x.new_empty(T, N, 4 * H, dtype=sd)
+        act_Wx_norm = x.new_empty(T, N, 4 * H, dtype=sd)
+        cache_Wx = x.new_empty(T, N, 2, dtype=sd)
+        act_Rh = x.new_empty(T, N, 4 * H, dtype=sd)
+        cache_Rh = x.new_empty(T, N, 2, dtype=sd)
+        act_c_norm = x.new_empty(T, N, H, dtype=sd)
+        cache_c = x.new_empty(T, N, 2, dtype=sd)
+        tmp_Rh = x.new_empty(N, 4 * H, dtype=sd)
         mp, zp = _mask_ptr(zoneout_prob, zoneout_mask)
-        _C.call("haste_b200_layer_norm_lstm_forward", _dtype(x), int(training), T, N, C, H,
+        _C.call("haste_b200_layer_norm_lstm_forward", _ln_lstm_dtype(x, act_Wx), int(training), T, N, C, H,
                 _p(kernel), _p(recurrent_kernel), _p(bias), _p(gamma[0]), _p(gamma[1]), _p(gamma_h),
                 _p(beta_h),
                 _p(x), _p(h), _p(c), _p(act_Wx), _p(act_Wx_norm), _p(cache_Wx), _p(act_Rh),
@@ -274,8 +292,9 @@ def layer_norm_lstm_forward(training, zoneout_prob, x, h0, c0, kernel, recurrent
 def layer_norm_lstm_backward(x, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h,
                              zoneout_mask, h, c, act_Wx, act_Wx_norm, cache_Wx, act_Rh, cache_Rh,
                              act_c_norm, cache_c, dh_new, dc_new, transposed=True, grads=None):
-    _check(x, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h, zoneout_mask, h, c, act_Wx,
-           act_Wx_norm, cache_Wx, act_Rh, cache_Rh, act_c_norm, cache_c, dh_new, dc_new)
+    _check(x, kernel, recurrent_kernel, bias, gamma, gamma_h, beta_h, zoneout_mask, h, c, dh_new,
+           dc_new)
+    _check(act_Wx, act_Wx_norm, cache_Wx, act_Rh, cache_Rh, act_c_norm, cache_c)
     H = h.shape[2]
     T, N, C, H = _dims_bwd(x, transposed, H)
     with torch.cuda.device(h.device):
@@ -288,7 +307,7 @@ def layer_norm_lstm_backward(x, kernel, recurrent_kernel, bias, gamma, gamma_h, 
         dbeta_h = _zeros(grads, h, *beta_h.shape)
         dh = h.new_zeros(N, H)
         dc = h.new_zeros(N, H)
-        _C.call("haste_b200_layer_norm_lstm_backward", _dtype(h), int(transposed), T, N, C, H,
+        _C.call("haste_b200_layer_norm_lstm_backward", _ln_lstm_dtype(h, act_Wx), int(transposed), T, N, C, H,
                 _p(kernel), _p(recurrent_kernel), _p(bias), _p(gamma[0]), _p(gamma[1]), _p(gamma_h),
                 _p(beta_h),
                 _p(x), _p(h), _p(c), _p(dh_new), _p(dc_new), _p(dx), _p(dW), _p(dR), _p(db),

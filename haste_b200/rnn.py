@@ -29,17 +29,30 @@ def _empty_mask(x):
     return x.new_empty(0, 0, 0)
 
 
+def _bucket(ctx):
+    """The flat gradient buffer of a data-parallel layer (haste_b200.data_parallel), if any."""
+    return ctx.dp.bucket if ctx.dp is not None else None
+
+
+def _gradients_ready(ctx, names, grads):
+    """Tells the data-parallel hook that this layer's parameter gradients are queued: it
+    starts their all-reduce now, while the layers below still run their backward passes."""
+    if ctx.dp is not None:
+        ctx.dp.gradients_ready(dict(zip(names, grads)))
+
+
 # --------------------------------------------------------------------------
 # autograd glue: forward saves exactly what backward needs; backward passes the
 # tensors in forward layout (no permute().contiguous() copies).
 # --------------------------------------------------------------------------
 class _LSTMFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, *inputs):
+    def forward(ctx, training, zoneout_prob, dp, *inputs):
         h, c, cache = ops.lstm_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[3:], h, c, cache)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
+        ctx.dp = dp
         return h, c
 
     @staticmethod
@@ -47,51 +60,57 @@ class _LSTMFunction(torch.autograd.Function):
         if not ctx.training:
             raise RuntimeError('LSTM backward can only be called in training mode')
         grads = ops.lstm_backward(*ctx.saved_tensors, grad_h.contiguous(), grad_c.contiguous(),
-                                  transposed=False)
-        return (None, None, *grads, None)
+                                  transposed=False, grads=_bucket(ctx))
+        _gradients_ready(ctx, ['kernel', 'recurrent_kernel', 'bias'], grads[3:])
+        return (None, None, None, *grads, None)
 
 
 class _GRUFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, *inputs):
+    def forward(ctx, training, zoneout_prob, dp, *inputs):
         h, cache = ops.gru_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[2:], h, cache)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
+        ctx.dp = dp
         return h
 
     @staticmethod
     def backward(ctx, grad_h):
         if not ctx.training:
             raise RuntimeError('GRU backward can only be called in training mode')
-        grads = ops.gru_backward(*ctx.saved_tensors, grad_h.contiguous(), transposed=False)
-        return (None, None, *grads, None)
+        grads = ops.gru_backward(*ctx.saved_tensors, grad_h.contiguous(), transposed=False, grads=_bucket(ctx))
+        _gradients_ready(ctx, ['kernel', 'recurrent_kernel', 'bias', 'recurrent_bias'], grads[2:])
+        return (None, None, None, *grads, None)
 
 
 class _IndRNNFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, *inputs):
+    def forward(ctx, training, zoneout_prob, dp, *inputs):
         h = ops.indrnn_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[2:], h)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
+        ctx.dp = dp
         return h
 
     @staticmethod
     def backward(ctx, grad_h):
         if not ctx.training:
             raise RuntimeError('IndRNN backward can only be called in training mode')
-        grads = ops.indrnn_backward(*ctx.saved_tensors, grad_h.contiguous(), transposed=False)
-        return (None, None, *grads, None)
+        grads = ops.indrnn_backward(*ctx.saved_tensors, grad_h.contiguous(), transposed=False, grads=_bucket(ctx))
+        _gradients_ready(ctx, ['kernel', 'recurrent_scale', 'bias'], grads[2:])
+        return (None, None, None, *grads, None)
 
 
 class _LayerNormLSTMFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, *inputs):
+    def forward(ctx, training, zoneout_prob, dp, *inputs):
         outputs = ops.layer_norm_lstm_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[3:], *outputs)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
+        ctx.dp = dp
         return outputs[0], outputs[1]
 
     @staticmethod
@@ -99,17 +118,19 @@ class _LayerNormLSTMFunction(torch.autograd.Function):
         if not ctx.training:
             raise RuntimeError('LayerNormLSTM backward can only be called in training mode')
         grads = ops.layer_norm_lstm_backward(*ctx.saved_tensors, grad_h.contiguous(),
-                                             grad_c.contiguous(), transposed=False)
-        return (None, None, *grads, None)
+                                             grad_c.contiguous(), transposed=False, grads=_bucket(ctx))
+        _gradients_ready(ctx, ['kernel', 'recurrent_kernel', 'bias', 'gamma', 'gamma_h', 'beta_h'], grads[3:])
+        return (None, None, None, *grads, None)
 
 
 class _LayerNormGRUFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, *inputs):
+    def forward(ctx, training, zoneout_prob, dp, *inputs):
         output = ops.layer_norm_gru_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[2:], *output)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
+        ctx.dp = dp
         return output[0]
 
     @staticmethod
@@ -117,17 +138,19 @@ class _LayerNormGRUFunction(torch.autograd.Function):
         if not ctx.training:
             raise RuntimeError('LayerNormGRU backward can only be called in training mode')
         grads = ops.layer_norm_gru_backward(*ctx.saved_tensors, grad_h.contiguous(),
-                                            transposed=False)
-        return (None, None, *grads, None)
+                                            transposed=False, grads=_bucket(ctx))
+        _gradients_ready(ctx, ['kernel', 'recurrent_kernel', 'bias', 'recurrent_bias', 'gamma'], grads[2:])
+        return (None, None, None, *grads, None)
 
 
 class _LayerNormIndRNNFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, *inputs):
+    def forward(ctx, training, zoneout_prob, dp, *inputs):
         output = ops.layer_norm_indrnn_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[2:], *output)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
+        ctx.dp = dp
         return output[0]
 
     @staticmethod
@@ -135,8 +158,9 @@ class _LayerNormIndRNNFunction(torch.autograd.Function):
         if not ctx.training:
             raise RuntimeError('LayerNormIndRNN backward can only be called in training mode')
         grads = ops.layer_norm_indrnn_backward(*ctx.saved_tensors, grad_h.contiguous(),
-                                               transposed=False)
-        return (None, None, *grads, None)
+                                               transposed=False, grads=_bucket(ctx))
+        _gradients_ready(ctx, ['kernel', 'recurrent_scale', 'bias', 'gamma'], grads[2:])
+        return (None, None, None, *grads, None)
 
 
 # --------------------------------------------------------------------------
@@ -177,6 +201,9 @@ class BaseRNN(nn.Module):
         self.batch_first = batch_first
         self.zoneout = zoneout
         self.return_state_sequence = return_state_sequence
+        # set by haste_b200.data_parallel.attach(): where this layer's backward pass leaves its
+        # parameter gradients and how they are summed over the ranks
+        self._dp = None
 
     def _permute(self, x):
         return x.permute(1, 0, 2) if self.batch_first else x
@@ -216,11 +243,18 @@ class BaseRNN(nn.Module):
         the mask into the recurrent-kernel gradient."""
         R = self.recurrent_kernel
         p = getattr(self, 'dropout', 0.0)
-        if dropconnect_mask is not None:
-            if not self.training or not p:
-                return R
-            return R * (dropconnect_mask.to(dtype=R.dtype, device=R.device) / (1.0 - p))
-        return F.dropout(R, p, self.training)
+        if not self.training or not p:
+            if self._dp is not None:
+                self._dp.recurrent_scale = None
+            return R
+        if dropconnect_mask is None:
+            # drawn like F.dropout(R, p, training) draws it; kept so that the gradient summed
+            # over data-parallel ranks can be scaled after the sum
+            dropconnect_mask = torch.empty_like(R).bernoulli_(1.0 - p)
+        scale = dropconnect_mask.to(dtype=R.dtype, device=R.device) / (1.0 - p)
+        if self._dp is not None:
+            self._dp.recurrent_scale = scale
+        return R * scale
 
     def _require_cuda(self):
         flags = [p.is_cuda for p in self.parameters()]
@@ -285,7 +319,7 @@ class LSTM(BaseRNN):
         shape = [1, input.shape[1], self.hidden_size]
         h0, c0 = self._get_state(input, state, (shape, shape))
         h, c = _LSTMFunction.apply(
-            self.training, self.zoneout, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
             c0[0].contiguous(), self.kernel.contiguous(),
             self._dropconnect(dropconnect_mask).contiguous(), self.bias.contiguous(),
             self._get_zoneout_mask(input, zoneout_mask).contiguous())
@@ -341,7 +375,7 @@ class GRU(BaseRNN):
         input = self._permute(input)
         h0 = self._get_state(input, state, [1, input.shape[1], self.hidden_size])
         h = _GRUFunction.apply(
-            self.training, self.zoneout, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
             self.kernel.contiguous(), self._dropconnect(dropconnect_mask).contiguous(),
             self.bias.contiguous(), self.recurrent_bias.contiguous(),
             self._get_zoneout_mask(input, zoneout_mask).contiguous())
@@ -371,7 +405,7 @@ class IndRNN(BaseRNN):
         input = self._permute(input)
         h0 = self._get_state(input, state, [1, input.shape[1], self.hidden_size])
         h = _IndRNNFunction.apply(
-            self.training, self.zoneout, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
             self.kernel.contiguous(), self.recurrent_scale.contiguous(), self.bias.contiguous(),
             self._get_zoneout_mask(input, zoneout_mask).contiguous())
         state = self._get_final_state(h, lengths)
@@ -412,7 +446,7 @@ class LayerNormLSTM(BaseRNN):
         shape = [1, input.shape[1], self.hidden_size]
         h0, c0 = self._get_state(input, state, (shape, shape))
         h, c = _LayerNormLSTMFunction.apply(
-            self.training, self.zoneout, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
             c0[0].contiguous(), self.kernel.contiguous(),
             self._dropconnect(dropconnect_mask).contiguous(), self.bias.contiguous(),
             self.gamma.contiguous(), self.gamma_h.contiguous(), self.beta_h.contiguous(),
@@ -450,7 +484,7 @@ class LayerNormGRU(BaseRNN):
         input = self._permute(input)
         h0 = self._get_state(input, state, [1, input.shape[1], self.hidden_size])
         h = _LayerNormGRUFunction.apply(
-            self.training, self.zoneout, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
             self.kernel.contiguous(), self._dropconnect(dropconnect_mask).contiguous(),
             self.bias.contiguous(), self.recurrent_bias.contiguous(), self.gamma.contiguous(),
             self._get_zoneout_mask(input, zoneout_mask).contiguous())
@@ -482,7 +516,7 @@ class LayerNormIndRNN(BaseRNN):
         input = self._permute(input)
         h0 = self._get_state(input, state, [1, input.shape[1], self.hidden_size])
         h = _LayerNormIndRNNFunction.apply(
-            self.training, self.zoneout, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
             self.kernel.contiguous(), self.recurrent_scale.contiguous(), self.bias.contiguous(),
             self.gamma.contiguous(), self._get_zoneout_mask(input, zoneout_mask).contiguous())
         state = self._get_final_state(h, lengths)

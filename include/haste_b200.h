@@ -44,7 +44,18 @@ enum {
 /* HASTE_B200_F16 (__half storage, fp32-grade arithmetic on exact bf16 (hi, lo) splits of the
  * stored values): GRU entry points and haste_b200_gemm only - the one reduced-precision type
  * the reference ships (lib/gru_forward_gpu.cu.cc:373). */
-enum { HASTE_B200_F32 = 0, HASTE_B200_BF16 = 1, HASTE_B200_F16 = 2 };
+enum { HASTE_B200_F32 = 0, HASTE_B200_BF16 = 1, HASTE_B200_F16 = 2,
+       /* LayerNormLSTM entry points only.  Tensors the caller exchanges with the layer are
+        * __nv_bfloat16 exactly as with HASTE_B200_BF16 (x, W, R, b, gamma*, beta_h, h, c,
+        * zoneout_mask, dh_new, dc_new and every gradient), but everything the forward pass
+        * leaves for the backward pass is FLOAT: act_Wx, act_Wx_norm, act_Rh, act_c_norm,
+        * tmp_Rh and the three caches must be float buffers of the documented shapes, and h and
+        * c are carried in fp32 from step to step (only the returned copies are rounded).
+        * Three LayerNorms per step amplify the rounding of a bf16-stored x.W, LN(x.W) or
+        * running h to 2e-2 .. 1e-1 of the result; this mode stays within 2e-2 of fp32
+        * arithmetic on the same bf16 inputs.  It runs the fp32 kernels on converted operands,
+        * i.e. at fp32 speed with bf16 interface traffic. */
+       HASTE_B200_BF16_WIDE = 3 };
 
 const char* haste_b200_last_error(void);
 const char* haste_b200_version(void);

@@ -115,3 +115,110 @@ def indrnn_backward(x, W, u, b, mask, h, dh_new):
          "indrnn_backward")
     torch.cuda.synchronize()
     return {"x": dx, "h0": dh, "W": dW, "u": du, "b": db}
+
+
+# ---- LayerNorm cells (gamma is the module's [2, G*H] parameter) -------------------------
+def layer_norm_lstm_forward(training, zp, x, h0, c0, W, R, b, gamma, gamma_h, beta_h, mask):
+    T, N, C = x.shape
+    H = R.shape[0]
+    h = x.new_zeros(T + 1, N, H); c = x.new_zeros(T + 1, N, H)
+    h[0] = h0; c[0] = c0
+    e = lambda *s: x.new_empty(*s)
+    saved = dict(act_Wx=e(T, N, 4 * H), act_Wx_norm=e(T, N, 4 * H), cache_Wx=e(T, N, 2),
+                 act_Rh=e(T, N, 4 * H), cache_Rh=e(T, N, 2), act_c_norm=e(T, N, H),
+                 cache_c=e(T, N, 2))
+    tmp = e(N, 4 * H)
+    torch.cuda.current_stream().synchronize()
+    _chk(lib().ref_layer_norm_lstm_forward(
+        int(training), T, N, C, H, _p(W), _p(R), _p(b), _p(gamma), _p(gamma_h), _p(beta_h), _p(x),
+        _p(h), _p(c), _p(saved["act_Wx"]), _p(saved["act_Wx_norm"]), _p(saved["cache_Wx"]),
+        _p(saved["act_Rh"]), _p(saved["cache_Rh"]), _p(saved["act_c_norm"]), _p(saved["cache_c"]),
+        _p(tmp), ctypes.c_float(zp if mask is not None else 0.0), _p(mask)), "layer_norm_lstm_forward")
+    torch.cuda.synchronize()
+    return h, c, saved
+
+
+def layer_norm_lstm_backward(x, W, R, b, gamma, gamma_h, beta_h, mask, h, c, saved, dh_new, dc_new):
+    T, N, C = x.shape
+    H = R.shape[0]
+    x_t = x.permute(2, 0, 1).contiguous(); W_t = W.t().contiguous(); R_t = R.t().contiguous()
+    z = lambda *s: x.new_zeros(*s)
+    dx = x.new_empty(T, N, C); dW = z(C, 4 * H); dR = z(H, 4 * H); db = z(4 * H)
+    dgamma = torch.zeros_like(gamma); dgh = torch.zeros_like(gamma_h); dbh = torch.zeros_like(beta_h)
+    dh = z(N, H); dc = z(N, H)
+    torch.cuda.current_stream().synchronize()
+    _chk(lib().ref_layer_norm_lstm_backward(
+        T, N, C, H, _p(W_t), _p(R_t), _p(b), _p(gamma), _p(gamma_h), _p(beta_h), _p(x_t), _p(h),
+        _p(c), _p(dh_new), _p(dc_new), _p(dx), _p(dW), _p(dR), _p(db), _p(dgamma), _p(dgh),
+        _p(dbh), _p(dh), _p(dc), _p(saved["act_Wx"]), _p(saved["act_Wx_norm"]),
+        _p(saved["cache_Wx"]), _p(saved["act_Rh"]), _p(saved["cache_Rh"]), _p(saved["act_c_norm"]),
+        _p(saved["cache_c"]), _p(mask)), "layer_norm_lstm_backward")
+    torch.cuda.synchronize()
+    return {"x": dx, "h0": dh, "c0": dc, "W": dW, "R": dR, "b": db, "gamma": dgamma,
+            "gamma_h": dgh, "beta_h": dbh}
+
+
+def layer_norm_gru_forward(training, zp, x, h0, W, R, bx, br, gamma, mask):
+    T, N, C = x.shape
+    H = R.shape[0]
+    h = x.new_zeros(T + 1, N, H); h[0] = h0
+    e = lambda *s: x.new_empty(*s)
+    saved = dict(v=e(T, N, 4 * H), act_Wx=e(T, N, 3 * H), cache_Wx=e(T, N, 2),
+                 act_Rh=e(T, N, 3 * H), cache_Rh=e(T, N, 2))
+    twn = e(T, N, 3 * H); trn = e(N, 3 * H)
+    torch.cuda.current_stream().synchronize()
+    _chk(lib().ref_layer_norm_gru_forward(
+        int(training), T, N, C, H, _p(W), _p(R), _p(bx), _p(br), _p(gamma), _p(x), _p(h),
+        _p(saved["v"]), _p(saved["act_Wx"]), _p(saved["cache_Wx"]), _p(twn), _p(saved["act_Rh"]),
+        _p(saved["cache_Rh"]), _p(trn), ctypes.c_float(zp if mask is not None else 0.0), _p(mask)),
+         "layer_norm_gru_forward")
+    torch.cuda.synchronize()
+    return h, saved
+
+
+def layer_norm_gru_backward(x, W, R, bx, br, gamma, mask, h, saved, dh_new):
+    T, N, C = x.shape
+    H = R.shape[0]
+    x_t = x.permute(2, 0, 1).contiguous(); W_t = W.t().contiguous(); R_t = R.t().contiguous()
+    z = lambda *s: x.new_zeros(*s)
+    dx = x.new_empty(T, N, C); dW = z(C, 3 * H); dR = z(H, 3 * H); dbx = z(3 * H); dbr = z(3 * H)
+    dgamma = torch.zeros_like(gamma); dh = z(N, H)
+    dp = x.new_empty(T, N, 3 * H); dq = x.new_empty(T, N, 3 * H)
+    torch.cuda.current_stream().synchronize()
+    _chk(lib().ref_layer_norm_gru_backward(
+        T, N, C, H, _p(W_t), _p(R_t), _p(bx), _p(br), _p(gamma), _p(x_t), _p(h), _p(saved["v"]),
+        _p(dh_new), _p(dx), _p(dW), _p(dR), _p(dbx), _p(dbr), _p(dgamma), _p(dh), _p(dp), _p(dq),
+        _p(saved["act_Wx"]), _p(saved["cache_Wx"]), _p(saved["act_Rh"]), _p(saved["cache_Rh"]),
+        _p(mask)), "layer_norm_gru_backward")
+    torch.cuda.synchronize()
+    return {"x": dx, "h0": dh, "W": dW, "R": dR, "bx": dbx, "br": dbr, "gamma": dgamma}
+
+
+def layer_norm_indrnn_forward(training, zp, x, h0, W, u, b, gamma, mask):
+    T, N, C = x.shape
+    H = W.shape[1]
+    h = x.new_zeros(T + 1, N, H); h[0] = h0
+    ws = x.new_empty(T, N, H)
+    saved = dict(act_Wx=x.new_empty(T, N, H), cache_Wx=x.new_empty(T, N, 2))
+    torch.cuda.current_stream().synchronize()
+    _chk(lib().ref_layer_norm_indrnn_forward(
+        int(training), T, N, C, H, _p(W), _p(u), _p(b), _p(gamma), _p(x), _p(h), _p(ws),
+        _p(saved["act_Wx"]), _p(saved["cache_Wx"]),
+        ctypes.c_float(zp if mask is not None else 0.0), _p(mask)), "layer_norm_indrnn_forward")
+    torch.cuda.synchronize()
+    return h, saved
+
+
+def layer_norm_indrnn_backward(x, W, u, b, gamma, mask, h, saved, dh_new):
+    T, N, C = x.shape
+    H = W.shape[1]
+    x_t = x.permute(2, 0, 1).contiguous(); W_t = W.t().contiguous()
+    dx = x.new_empty(T, N, C); dW = x.new_zeros(C, H); du = x.new_zeros(H); db = x.new_zeros(H)
+    dgamma = torch.zeros_like(gamma); dh = x.new_zeros(N, H); ws = x.new_empty(T, N, H)
+    torch.cuda.current_stream().synchronize()
+    _chk(lib().ref_layer_norm_indrnn_backward(
+        T, N, C, H, _p(W_t), _p(u), _p(b), _p(gamma), _p(x_t), _p(h), _p(dh_new), _p(dx), _p(dW),
+        _p(du), _p(db), _p(dgamma), _p(dh), _p(ws), _p(saved["act_Wx"]), _p(saved["cache_Wx"]),
+        _p(mask)), "layer_norm_indrnn_backward")
+    torch.cuda.synchronize()
+    return {"x": dx, "h0": dh, "W": dW, "u": du, "b": db, "gamma": dgamma}

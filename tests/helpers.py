@@ -15,12 +15,13 @@ TOL_BF16 = 2e-2
 # float16 storage (GRU only): the stored values are used exactly and accumulated in fp32, so
 # what remains is the rounding of stored results to 11 significant bits along the recurrence
 TOL_F16 = 5e-3
-# LayerNormLSTM with bf16 storage: the tensors the interface stores in bf16 (x.W, LN(x.W), h)
-# are rounded whatever the arithmetic, and the three LayerNorms amplify that rounding.  An
-# exact float64 evaluation that only rounds those stored tensors is already 2e-2 .. 4.5e-2
-# (outputs) and up to 6e-2 (parameter gradients) away from the unrounded oracle
-# (test_bf16_storage_floor.py), so the bar for this cell is set above that floor.
-TOL_BF16_LN_LSTM = 1e-1
+# LayerNormLSTM in the C ABI's all-bf16 mode (HASTE_B200_BF16: the caller's act_Wx,
+# act_Wx_norm and h buffers are bf16, as a C++ caller with __nv_bfloat16 buffers passes them):
+# those interface tensors are rounded whatever the arithmetic and three LayerNorms per step
+# amplify the rounding.  Exact float64 arithmetic that rounds nothing but them is already
+# 2e-2 .. 1e-1 from the unrounded oracle (test_bf16_storage_floor.py), so that mode alone has
+# this bar.  The Python layers use HASTE_B200_BF16_WIDE and meet TOL_BF16.
+TOL_BF16_ALL_STORAGE_LN_LSTM = 1e-1
 
 
 def golden_files(cell=None):
@@ -50,7 +51,7 @@ max_rel_err = oracle.max_rel_err
 # input dictionary, returning outputs and gradients under the oracle's names.
 # ---------------------------------------------------------------------------
 def run_cuda(cell, d, zoneout=0.0, dtype=torch.float32, transposed=False, training=True,
-             backward=True, device="cuda", grads=None):
+             backward=True, device="cuda", grads=None, fwd_kwargs=None):
     from haste_b200 import ops
     _, names, has_c = oracle.CELLS[cell]
     t = {k: (v.to(device=device, dtype=dtype).contiguous() if v is not None else None)
@@ -69,7 +70,7 @@ def run_cuda(cell, d, zoneout=0.0, dtype=torch.float32, transposed=False, traini
         ins = (x, t["h0"], t["W"], t["R"], t["bx"], t["br"], t["gamma"], mask)
     else:
         ins = (x, t["h0"], t["W"], t["u"], t["b"], t["gamma"], mask)
-    fwd = getattr(ops, cell + "_forward")(training, zoneout, *ins)
+    fwd = getattr(ops, cell + "_forward")(training, zoneout, *ins, **(fwd_kwargs or {}))
     fwd = fwd if isinstance(fwd, (list, tuple)) else [fwd]
     out = {"h": fwd[0]}
     if has_c:
@@ -110,3 +111,125 @@ def assert_close(got, want, tol, what=""):
     err = max_rel_err(got, want)
     assert err < tol, f"{what}: max rel err {err:.3e} >= {tol:.1e}"
     return err
+
+
+# ---------------------------------------------------------------------------
+# Stacked / bidirectional networks built from oracle layers (the reference's PyTorch API has
+# single layers only; composition follows frameworks/tf/base_rnn.py:115-121: the backward
+# direction runs on the time-reversed input and its output is reversed back, the next level
+# sees cat([fw, bw], -1)).
+# ---------------------------------------------------------------------------
+class _RoundForward(torch.autograd.Function):
+    """A tensor stored in bf16: rounded on the way forward, gradient passed through."""
+
+    @staticmethod
+    def forward(ctx, a):
+        return a.to(torch.bfloat16).to(a.dtype)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g
+
+
+class _RoundBackward(torch.autograd.Function):
+    """A gradient stored in bf16: identity forward, rounded on the way back."""
+
+    @staticmethod
+    def forward(ctx, a):
+        return a.view_as(a)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.to(torch.bfloat16).to(g.dtype)
+
+
+def seeded_masks(num_layers, dirs, T, N, H, gates, zoneout, dropconnect, base_seed=1234):
+    """Zoneout keep-masks [T,N,H] and DropConnect keep-masks [H,gates*H] per layer and
+    direction, each pair drawn on the CPU from torch.Generator(base_seed + layer*2 + dir)."""
+    masks = []
+    for l in range(num_layers):
+        level = []
+        for d_ in range(dirs):
+            g = torch.Generator().manual_seed(base_seed + l * 2 + d_)
+            m = {}
+            if zoneout:
+                m["zoneout_mask"] = torch.bernoulli(torch.full((T, N, H), 1.0 - zoneout), generator=g)
+            if dropconnect:
+                m["dropconnect_mask"] = torch.bernoulli(torch.full((H, gates * H), 1.0 - dropconnect),
+                                                        generator=g)
+            level.append(m)
+        masks.append(level)
+    return masks
+
+
+def oracle_stack(net, cell, x, dy, masks=None, dropconnect=0.0, zoneout=0.0, bf16=False,
+                 dtype=torch.float64):
+    """Runs the haste_b200.Stack `net` (cells of kind `cell`) as a composition of oracle
+    layers on the CPU with the network's own parameters; returns (y, dx, [per layer and
+    direction {parameter name: gradient}]) for the loss sum(y * dy).
+
+    bf16=True restates what bf16 storage means for a stack: every tensor that crosses a
+    layer's interface in bf16 is rounded there - the layer's output sequence, the gradient
+    handed to the layer below, and the DropConnect-masked recurrent kernel - while each
+    layer's own arithmetic stays exact.
+    """
+    fn, names, has_c = oracle.CELLS[cell]
+    pname = {"W": "kernel", "R": "recurrent_kernel", "b": "bias", "bx": "bias",
+             "br": "recurrent_bias", "u": "recurrent_scale", "gamma": "gamma",
+             "gamma_h": "gamma_h", "beta_h": "beta_h"}
+    xo = x.detach().to("cpu", dtype).requires_grad_(True)
+    inp, leaves = xo, []
+    for l, level in enumerate(net.layers):
+        outs = []
+        for d_, layer in enumerate(level):
+            p = {k: v.detach().to("cpu", dtype).requires_grad_(True)
+                 for k, v in layer.named_parameters()}
+            leaves.append(p)
+            m = masks[l][d_] if masks is not None else {}
+            xi = torch.flip(inp, [0]) if d_ == 1 else inp
+            if bf16:
+                xi = _RoundBackward.apply(xi)
+            N, H = xi.shape[1], layer.hidden_size
+            args = {"x": xi, "h0": torch.zeros(N, H, dtype=dtype), "c0": torch.zeros(N, H, dtype=dtype)}
+            for k in names:
+                if k in pname and pname[k] in p and k not in args:
+                    args[k] = p[pname[k]]
+            if "R" in args and dropconnect and "dropconnect_mask" in m:
+                if bf16:
+                    scale = (m["dropconnect_mask"].to(torch.bfloat16) / (1.0 - dropconnect)).to(dtype)
+                    args["R"] = _RoundForward.apply(args["R"] * scale)
+                else:
+                    scale = (m["dropconnect_mask"].float() / (1.0 - dropconnect)).to(dtype)
+                    args["R"] = args["R"] * scale
+            zm = m.get("zoneout_mask")
+            out = fn(True, zoneout if zm is not None else 0.0, *[args[k] for k in names],
+                     zm.to(dtype) if zm is not None else None)
+            h = out[0] if has_c else out
+            yo = h[1:]
+            if bf16:
+                yo = _RoundForward.apply(yo)
+            outs.append(torch.flip(yo, [0]) if d_ == 1 else yo)
+        inp = torch.cat(outs, -1) if len(outs) > 1 else outs[0]
+    (inp * dy.detach().to("cpu", dtype)).sum().backward()
+    dx = xo.grad
+    if bf16:
+        dx = dx.to(torch.bfloat16).to(dtype)
+    return inp.detach(), dx, [{k: v.grad for k, v in p.items()} for p in leaves]
+
+
+def compare_stack(net, y, dx, ref, tol, what):
+    """Outputs, input gradient and EVERY parameter gradient of every layer and direction of a
+    Stack against `oracle_stack`'s result; returns the worst error."""
+    ref_y, ref_dx, ref_grads = ref
+    worst = assert_close(y, ref_y, tol, f"{what} y")
+    worst = max(worst, assert_close(dx, ref_dx, tol, f"{what} dx"))
+    i = 0
+    for l, level in enumerate(net.layers):
+        for d_, layer in enumerate(level):
+            for k, v in layer.named_parameters():
+                got, want = v.grad, ref_grads[i][k]
+                if k == "gamma" and type(layer).__name__ == "LayerNormIndRNN":
+                    got, want = got[0], want[0]  # row 1 of gamma is unused by this cell
+                worst = max(worst, assert_close(got, want, tol, f"{what} layer {l} dir {d_} d{k}"))
+            i += 1
+    return worst

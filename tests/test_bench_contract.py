@@ -10,7 +10,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference",
-                        "--steps", "1", "--warmup", "1"], capture_output=True, text=True,
+                        "--steps", "1", "--warmup", "1", "--T", "100"], capture_output=True, text=True,
                        timeout=600, cwd=ROOT)
     assert r.returncode == 0, r.stderr
     lines = [l for l in r.stdout.splitlines() if l.strip()]
@@ -20,7 +20,8 @@ def test_reference_arm_prints_one_json_line_with_the_contract_keys():
     for key in ("metric", "value", "unit", "steps", "warmup", "ms_per_step", "scaling",
                 "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
         assert key in d, key
-    assert d["config"]["workload"].startswith("lstm_N64_C512_H512_T1000")
+    # (--T shortens the sequence for this test; the default is the full T=1000)
+    assert d["config"]["workload"].startswith("lstm_N64_C512_H512_T100_")
     assert d["cpu_baseline"]["kind"] == "port" and d["cpu_baseline"]["cores"] >= 1
     assert d["e2e"]["h2d_bytes_per_step"] == 0 and d["e2e"]["d2h_bytes_per_step"] == 0
     assert d["value"] > 0 and d["e2e"]["value"] == d["value"]

@@ -1,11 +1,20 @@
-"""Why LayerNormLSTM has its own bf16 bar: rounding only the tensors that the interface
-stores in bf16 and that feed the forward pass (x.W, LN(x.W), h), with all arithmetic exact
-(float64), already moves outputs and gradients by more than the generic 2e-2 bf16 bar.  No
-implementation with bf16 storage can be closer to the unrounded oracle than this."""
+"""Why LayerNormLSTM with bf16 tensors needs fp32 carries, shown with exact arithmetic.
+
+All arithmetic here is float64; the only error source is the bf16 rounding of a tensor that
+crosses the layer's interface in bf16.  Two facts follow:
+
+ * Rounding nothing but the running output `h` (the interface tensor every bf16 layer
+   returns, fed back into the next step) already moves outputs and gradients past the generic
+   2e-2 bf16 bar at the benchmark's shapes.  A recurrence that feeds the rounded `h` back
+   cannot meet that bar however exact its arithmetic: the library's BF16_WIDE mode (used by
+   the Python layers) therefore carries h in fp32 and rounds only the returned copy.
+ * In the C ABI's all-bf16 mode the caller's `act_Wx` and `act_Wx_norm` buffers are bf16
+   interface tensors as well; rounding those three stays below that mode's own bar.
+"""
 import torch
 
 import haste_oracle as oracle
-from helpers import TOL_BF16, TOL_BF16_LN_LSTM
+from helpers import TOL_BF16, TOL_BF16_ALL_STORAGE_LN_LSTM
 
 
 class _Stored(torch.autograd.Function):
@@ -20,20 +29,22 @@ class _Stored(torch.autograd.Function):
         return g
 
 
-def _run(d, T, N, C, H, stored_in_bf16):
-    r = _Stored.apply if stored_in_bf16 else (lambda a: a)
+def _run(d, T, N, C, H, rounded=()):
+    """The oracle's LayerNormLSTM with the tensors named in `rounded` ('h', 'wx', 'wxn')
+    rounded to bf16 where they are stored; the returned h is what a caller would see."""
+    r = lambda name: _Stored.apply if name in rounded else (lambda a: a)
     names = ["x", "W", "R", "b", "gamma", "gamma_h", "beta_h"]
     L = {k: d[k].clone().requires_grad_(True) for k in names}
     g = L["gamma"]
     h, c = d["h0"], d["c0"]
-    wx = r(L["x"].reshape(T * N, C) @ L["W"])                     # act_Wx
-    wxn = r(oracle.layer_norm(wx, g[0])).reshape(T, N, 4 * H)     # act_Wx_norm
+    wx = r("wx")(L["x"].reshape(T * N, C) @ L["W"])                     # act_Wx
+    wxn = r("wxn")(oracle.layer_norm(wx, g[0])).reshape(T, N, 4 * H)    # act_Wx_norm
     hs, cs = [h], [c]
     for t in range(T):
         v = oracle.layer_norm(h @ L["R"], g[1]) + wxn[t] + L["b"]
         i, gg, f, o = v.chunk(4, 1)
         c = torch.sigmoid(f) * c + torch.sigmoid(i) * torch.tanh(gg)
-        h = r(torch.sigmoid(o) * torch.tanh(oracle.layer_norm(c, L["gamma_h"], L["beta_h"])))
+        h = r("h")(torch.sigmoid(o) * torch.tanh(oracle.layer_norm(c, L["gamma_h"], L["beta_h"])))
         hs.append(h)
         cs.append(c)
     hs, cs = torch.stack(hs), torch.stack(cs)
@@ -48,23 +59,30 @@ def _inputs(T, N, C, H, seed):
             for k, v in d.items()}
 
 
-def test_storage_rounding_alone_exceeds_the_generic_bf16_bar():
-    T, N, C, H = 20, 64, 64, 512
-    d = _inputs(T, N, C, H, seed=H)
-    exact_h, exact_g = _run(d, T, N, C, H, False)
+def test_restatement_is_the_oracle():
+    T, N, C, H = 6, 4, 8, 16
+    d = _inputs(T, N, C, H, seed=1)
+    exact_h, exact_g = _run(d, T, N, C, H)
     ref_out, ref_g = oracle.forward_backward("layer_norm_lstm", d, zoneout=0.0)
-    # the restatement above is the oracle's math
     assert oracle.max_rel_err(exact_h, ref_out["h"]) < 1e-12
     assert oracle.max_rel_err(exact_g["W"], ref_g["W"]) < 1e-10
-    h, _ = _run(d, T, N, C, H, True)
-    floor = oracle.max_rel_err(h, exact_h)
-    assert TOL_BF16 < floor < TOL_BF16_LN_LSTM, floor
 
 
-def test_storage_rounding_floor_of_the_parameter_gradients():
-    T, N, C, H = 16, 32, 64, 64
-    d = _inputs(T, N, C, H, seed=77 + H)
-    _, exact_g = _run(d, T, N, C, H, False)
-    _, g = _run(d, T, N, C, H, True)
-    floor = max(oracle.max_rel_err(g[k], exact_g[k]) for k in g)
-    assert TOL_BF16 < floor < TOL_BF16_LN_LSTM, floor
+def test_feeding_back_a_bf16_rounded_h_alone_exceeds_the_bf16_bar():
+    # one layer of the 3-layer bidirectional LayerNormLSTM configuration, 50 of its 400 steps
+    T, N, C, H = 50, 64, 80, 512
+    d = _inputs(T, N, C, H, seed=3)
+    exact_h, exact_g = _run(d, T, N, C, H)
+    h, g = _run(d, T, N, C, H, rounded=("h",))
+    floor_h = oracle.max_rel_err(h, exact_h)
+    floor_g = max(oracle.max_rel_err(g[k], exact_g[k]) for k in g)
+    assert floor_h > TOL_BF16 and floor_g > TOL_BF16, (floor_h, floor_g)
+
+
+def test_all_bf16_storage_mode_floor():
+    T, N, C, H = 20, 64, 64, 512
+    d = _inputs(T, N, C, H, seed=H)
+    exact_h, exact_g = _run(d, T, N, C, H)
+    h, g = _run(d, T, N, C, H, rounded=("h", "wx", "wxn"))
+    floor = max([oracle.max_rel_err(h, exact_h)] + [oracle.max_rel_err(g[k], exact_g[k]) for k in g])
+    assert TOL_BF16 < floor < TOL_BF16_ALL_STORAGE_LN_LSTM, floor

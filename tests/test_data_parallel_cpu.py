@@ -91,9 +91,54 @@ def _rank_main(rank, port, cell, results):
                 assert torch.allclose(v, ref_g[k], rtol=1e-10, atol=1e-12), k
         with pytest.raises(ValueError):
             bucket.take(1 << 20)
+        _check_attach(rank)
         results[rank] = "ok"
     finally:
         dist.destroy_process_group()
+
+
+class GRU(torch.nn.Module):
+    """Stand-in with the attributes `data_parallel.attach` uses of a haste_b200.GRU (the real
+    layers need a GPU): its "backward pass" takes the gradient views from the bucket, adds a
+    rank-dependent value and reports them ready, like the autograd glue does."""
+
+    def __init__(self, C, H):
+        super().__init__()
+        self.input_size, self.hidden_size, self._dp = C, H, None
+        self.kernel = torch.nn.Parameter(torch.zeros(C, 3 * H, dtype=torch.float64))
+        self.recurrent_kernel = torch.nn.Parameter(torch.zeros(H, 3 * H, dtype=torch.float64))
+        self.bias = torch.nn.Parameter(torch.zeros(3 * H, dtype=torch.float64))
+        self.recurrent_bias = torch.nn.Parameter(torch.zeros(3 * H, dtype=torch.float64))
+
+    def fake_backward(self, value, scale=None):
+        names = ["kernel", "recurrent_kernel", "bias", "recurrent_bias"]
+        views = {k: self._dp.bucket.take(*getattr(self, k).shape) for k in names}
+        for v in views.values():
+            v.add_(value)
+        self._dp.recurrent_scale = scale
+        self._dp.gradients_ready(views)
+
+
+def _check_attach(rank):
+    """attach(): buckets per layer, all-reduce issued from the backward pass (or in finish()),
+    DropConnect scale applied after the sum, .grad aliases the bucket."""
+    from haste_b200 import data_parallel as dp
+    net = torch.nn.ModuleList([GRU(3, 4), GRU(8, 4)])
+    for overlap in (True, False):
+        d = dp.attach(net, overlap=overlap)
+        assert len(d.hooks) == 2 and d.bucket_bytes() > 0
+        for step in range(2):
+            d.zero_grad()
+            scale = torch.full((4, 12), 2.0, dtype=torch.float64)
+            net[1].fake_backward(float(rank + 1) * 10)           # upper layer finishes first
+            net[0].fake_backward(float(rank + 1), scale=scale)
+            d.finish()
+            assert torch.equal(net[1].kernel.grad, torch.full((8, 12), 30.0, dtype=torch.float64))
+            assert torch.equal(net[0].bias.grad, torch.full((12,), 3.0, dtype=torch.float64))
+            assert torch.equal(net[0].recurrent_kernel.grad, torch.full((4, 12), 6.0, dtype=torch.float64))
+            assert net[1].kernel.grad.data_ptr() == net[1]._dp.bucket.flat.data_ptr()
+        d.detach()
+        assert net[0]._dp is None
 
 
 @pytest.mark.parametrize("cell", ["lstm", "layer_norm_gru"])

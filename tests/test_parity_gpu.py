@@ -6,7 +6,8 @@ import pytest
 import torch
 
 import haste_oracle as oracle
-from helpers import (TOL_BF16, TOL_BF16_LN_LSTM, TOL_F16, TOL_F32, assert_close, golden_files, load_golden, run_cuda)
+from helpers import (TOL_BF16, TOL_BF16_ALL_STORAGE_LN_LSTM, TOL_F16, TOL_F32, assert_close,
+                     golden_files, load_golden, run_cuda)
 
 pytestmark = pytest.mark.gpu
 
@@ -66,8 +67,23 @@ def test_bf16_against_oracle(cell, shape):
           for k, v in d.items()}
     ref_out, ref_grads = oracle.forward_backward(cell, dq, zoneout=zoneout)
     out, grads = run_cuda(cell, dq, zoneout=zoneout, dtype=torch.bfloat16)
-    tol = TOL_BF16_LN_LSTM if cell == "layer_norm_lstm" else TOL_BF16
-    _compare(cell, dq, out, grads, ref_out, ref_grads, tol)
+    _compare(cell, dq, out, grads, ref_out, ref_grads, TOL_BF16)
+
+
+@pytest.mark.parametrize("shape", [(6, 3, 16, 24), (16, 32, 64, 64), (20, 64, 64, 512)],
+                         ids=lambda s: "T%d_N%d_C%d_H%d" % s)
+def test_layer_norm_lstm_all_bf16_storage_mode(shape):
+    """The C ABI's HASTE_B200_BF16 mode of LayerNormLSTM (every buffer bf16, what a C++ caller
+    with __nv_bfloat16 buffers gets): held to the bar that the rounding of those interface
+    buffers alone allows."""
+    T, N, C, H = shape
+    d = oracle.make_inputs("layer_norm_lstm", T, N, C, H, seed=77 + H, zoneout=0.25)
+    dq = {k: (v.to(torch.bfloat16).to(torch.float64) if v is not None else None)
+          for k, v in d.items()}
+    ref_out, ref_grads = oracle.forward_backward("layer_norm_lstm", dq, zoneout=0.25)
+    out, grads = run_cuda("layer_norm_lstm", dq, zoneout=0.25, dtype=torch.bfloat16,
+                          fwd_kwargs={"saved_dtype": torch.bfloat16})
+    _compare("layer_norm_lstm", dq, out, grads, ref_out, ref_grads, TOL_BF16_ALL_STORAGE_LN_LSTM)
 
 
 @pytest.mark.parametrize("cell", CELLS)
@@ -146,8 +162,7 @@ def test_persistent_path_bf16(cell, shape):
     ref_out, ref_grads = oracle.forward_backward(cell, dq, zoneout=0.1)
     out, grads = run_cuda(cell, dq, zoneout=0.1, dtype=torch.bfloat16)
     _C.sync_check(torch.cuda.current_stream().cuda_stream)
-    _compare(cell, dq, out, grads, ref_out, ref_grads,
-             TOL_BF16_LN_LSTM if cell == "layer_norm_lstm" else TOL_BF16)
+    _compare(cell, dq, out, grads, ref_out, ref_grads, TOL_BF16)
 
 
 @pytest.mark.parametrize("path", ["stepwise", "persistent"])

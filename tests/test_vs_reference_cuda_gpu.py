@@ -74,3 +74,50 @@ def test_indrnn_matches_reference_cuda(ref):
     h = ref.indrnn_forward(True, 0.1, t["x"], t["h0"], t["W"], t["u"], t["b"], t["mask"])
     g = ref.indrnn_backward(t["x"], t["W"], t["u"], t["b"], t["mask"], h, t["dh"])
     _check("indrnn", d, 0.1, h, g)
+
+
+@pytest.mark.parametrize("zoneout", [0.0, 0.2])
+@pytest.mark.parametrize("shape", [(12, 8, 16, 32), (30, 32, 80, 256)])
+def test_layer_norm_lstm_matches_reference_cuda(ref, shape, zoneout):
+    T, N, C, H = shape
+    d = oracle.make_inputs("layer_norm_lstm", T, N, C, H, seed=4, zoneout=zoneout)
+    t = _cuda(d)
+    h, c, saved = ref.layer_norm_lstm_forward(True, zoneout, t["x"], t["h0"], t["c0"], t["W"], t["R"],
+                                              t["b"], t["gamma"], t["gamma_h"], t["beta_h"], t["mask"])
+    g = ref.layer_norm_lstm_backward(t["x"], t["W"], t["R"], t["b"], t["gamma"], t["gamma_h"],
+                                     t["beta_h"], t["mask"], h, c, saved, t["dh"], t["dc"])
+    _check("layer_norm_lstm", d, zoneout, h, g, c)
+
+
+@pytest.mark.parametrize("zoneout", [0.0, 0.2])
+@pytest.mark.parametrize("shape", [(12, 8, 16, 32), (30, 32, 80, 256)])
+def test_layer_norm_gru_matches_reference_cuda(ref, shape, zoneout):
+    T, N, C, H = shape
+    d = oracle.make_inputs("layer_norm_gru", T, N, C, H, seed=5, zoneout=zoneout)
+    t = _cuda(d)
+    h, saved = ref.layer_norm_gru_forward(True, zoneout, t["x"], t["h0"], t["W"], t["R"], t["bx"],
+                                          t["br"], t["gamma"], t["mask"])
+    g = ref.layer_norm_gru_backward(t["x"], t["W"], t["R"], t["bx"], t["br"], t["gamma"], t["mask"],
+                                    h, saved, t["dh"])
+    _check("layer_norm_gru", d, zoneout, h, g)
+
+
+def test_layer_norm_indrnn_matches_reference_cuda(ref):
+    T, N, C, H = 40, 16, 64, 128
+    d = oracle.make_inputs("layer_norm_indrnn", T, N, C, H, seed=6, zoneout=0.1)
+    t = _cuda(d)
+    h, saved = ref.layer_norm_indrnn_forward(True, 0.1, t["x"], t["h0"], t["W"], t["u"], t["b"],
+                                             t["gamma"], t["mask"])
+    g = ref.layer_norm_indrnn_backward(t["x"], t["W"], t["u"], t["b"], t["gamma"], t["mask"], h,
+                                       saved, t["dh"])
+    # row 1 of gamma is unused by this cell on both sides
+    g["gamma"] = g["gamma"][0]
+    o_out, o_g = oracle.forward_backward("layer_norm_indrnn", d, zoneout=0.1)
+    out, grads = run_cuda("layer_norm_indrnn", d, zoneout=0.1)
+    grads["gamma"] = grads["gamma"][0]
+    o_g["gamma"] = o_g["gamma"][0]
+    for name, ours, theirs, exact in [("h", out["h"], h, o_out["h"])] + \
+            [("d" + k, grads[k], g[k], o_g[k]) for k in g]:
+        e_ours, e_ref = max_rel_err(ours, exact), max_rel_err(theirs, exact)
+        assert e_ours < TOL_F32, f"{name}: ours vs oracle {e_ours:.2e}"
+        assert max_rel_err(ours, theirs) < TOL_F32 + 2 * e_ref, name
