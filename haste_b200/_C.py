@@ -10,7 +10,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libhaste_b200.so")
 
 F32, BF16, F16, BF16_WIDE = 0, 1, 2, 3
-PATH_AUTO, PATH_STEPWISE, PATH_PERSISTENT = 0, 1, 2
+PATH_AUTO, PATH_STEPWISE, PATH_PERSISTENT, PATH_NO_TENSOR_CORE = 0, 1, 2, 3
 GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05 = 0, 1, 2
 
 _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
@@ -40,6 +40,7 @@ SIGNATURES = {
     "haste_b200_gemm": [_i] * 4 + [_p, _ll, _ll, _p, _ll, _ll, _p, _ll, _i, _p],
     "haste_b200_set_recurrence_path": [_i],
     "haste_b200_set_gemm_path": [_i],
+    "haste_b200_set_sm_budget": [_i],
     "haste_b200_sync_check": [_p],
     "haste_b200_profile_enable": [_i],
     "haste_b200_profile_read": [_p, _i],
@@ -86,6 +87,11 @@ def launch_count():
 
 def set_recurrence_path(path):
     call("haste_b200_set_recurrence_path", path)
+
+
+def set_sm_budget(sms):
+    """SMs one persistent recurrence launch may occupy (0 = all); see the header."""
+    call("haste_b200_set_sm_budget", int(sms))
 
 
 def set_gemm_path(path):

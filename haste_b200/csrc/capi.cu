@@ -9,7 +9,9 @@ const char* last_error();
 long long launch_count();
 static std::atomic<int> g_rec_path{HASTE_B200_PATH_AUTO};
 static std::atomic<int> g_gemm_path{HASTE_B200_GEMM_AUTO};
+static std::atomic<int> g_sm_budget{0};
 int recurrence_path() { return g_rec_path.load(); }
+int sm_budget() { return g_sm_budget.load(); }
 int gemm_path() { return g_gemm_path.load(); }
 }  // namespace hb
 
@@ -53,8 +55,13 @@ int haste_b200_sync_check(void* stream) {
 }
 
 int haste_b200_set_recurrence_path(int path) {
-  if (path < 0 || path > 2) return HASTE_B200_ERR_INVALID;
+  if (path < 0 || path > 3) return HASTE_B200_ERR_INVALID;
   g_rec_path.store(path);
+  return HASTE_B200_OK;
+}
+int haste_b200_set_sm_budget(int sms) {
+  if (sms < 0) return HASTE_B200_ERR_INVALID;
+  g_sm_budget.store(sms);
   return HASTE_B200_OK;
 }
 int haste_b200_set_gemm_path(int path) {

@@ -127,6 +127,10 @@ int lstm_backward_persistent(const LstmBwd& a, float* dh_carry, float* dc_carry,
 int gru_forward_persistent(const GruFwd& a, cudaStream_t s);
 int gru_backward_persistent(const GruBwd& a, float* dh_carry, const GradPlanes& planes,
                             cudaStream_t s);
+// Tensor-core recurrence for bf16 batches of about a hundred rows and more (rec_tc_gru.cu);
+// same contract, except that the backward kernel does not sum the bias gradients.
+int gru_forward_tc(const GruFwd& a, cudaStream_t s);
+int gru_backward_tc(const GruBwd& a, float* dh_carry, cudaStream_t s);
 // LayerNormLSTM: forward expects LN(x.W) in a.act_Wx_norm; backward adds the LayerNorm
 // parameter gradients of the recurrence into the fp32 accumulators acc = [dgamma_Rh 4H |
 // dgamma_h H | dbeta_h H]; planes.p / p2 receive the gate gradient and d(h.R).
@@ -153,6 +157,7 @@ inline int gemm_small(const GemmDesc& g, cudaStream_t s) {
 
 // Process-wide knobs (set through the C ABI).
 int recurrence_path();
+int sm_budget();  // 0: the whole GPU; else the SMs one recurrence launch may occupy
 int gemm_path();
 
 }  // namespace hb

@@ -23,125 +23,21 @@
 //
 // Replaces the cuBLAS calls of the reference (lib/blas.h:48-61 and the call sites in
 // lib/*_gpu.cu.cc).
-#include <cuda.h>
-#include <cudaTypedefs.h>
-
 #include <atomic>
-#include <mutex>
 
 #include "cells.cuh"
+#include "tcgen05.cuh"
 
 namespace hb {
 namespace {
+
+using namespace tc;
 
 constexpr int BM = 128, BN = 128, BK = 64;   // CTA tile; BK bf16 = one 128-byte swizzle row
 constexpr int UK = 16;                       // K of one tcgen05.mma (bf16)
 constexpr int TILE_BYTES = BM * BK * 2;      // one operand plane of one stage (A or B): 16 KiB
 constexpr int THREADS = 192;                 // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
 constexpr int TMEM_COLS = 2 * BN;            // two fp32 accumulators of BN columns
-constexpr long long SPIN_LIMIT_CYCLES = 4000000000LL;  // ~2 s at 2 GHz
-
-// ----------------------------------------------------------------------------
-// PTX wrappers
-// ----------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
-}
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait.  Returns false if the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* err_word, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  uint32_t it = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++it & 255u) == 0) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > SPIN_LIMIT_CYCLES) {
-        *abort_flag = 1;
-        *reinterpret_cast<volatile int*>(err_word) = code;
-        return false;
-      }
-    }
-  }
-  return true;
-}
-// Tile load: coordinates are (contiguous index, row index, plane).
-__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
-                                            int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes"
-      " [%0], [%1, {%3, %4, %5}], [%2];" ::"r"(dst),
-      "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() {
-  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_fence_after() {
-  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar)
-               : "memory");
-}
-__device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t desc_a, uint64_t desc_b,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}" ::"r"(d_tmem),
-      "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
-      : "memory");
-}
-__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32"
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15,"
-      " %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
-        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
-        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
-        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
-        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-      : "r"(taddr));
-}
-__device__ __forceinline__ void tc_wait_ld() {
-  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-}
-
-// Shared-memory matrix descriptor, 128-byte swizzle (layout type 2), descriptor version 1.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes,
-                                              uint32_t sbo_bytes) {
-  uint64_t d = 0;
-  d |= static_cast<uint64_t>((addr & 0x3FFFFu) >> 4);
-  d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFFu) << 16;
-  d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= 1ull << 46;
-  d |= 2ull << 61;
-  return d;
-}
 
 struct Params {
   int M, N, K;
@@ -162,7 +58,108 @@ struct Cfg {
   static constexpr int STAGE_BYTES = 2 * PLANES * TILE_BYTES;
   static constexpr int STAGES = NPROD == 1 ? 6 : (NPROD == 3 ? 3 : 2);
   static constexpr int SMEM = STAGES * STAGE_BYTES + 1024 /*align*/ + 256 /*barriers*/;
+  // fp32 storage: the tensor core adds every MMA result into the fp32 accumulator with
+  // truncation, a bias of about half an ulp per accumulation that always points the same way;
+  // over the few hundred accumulations of a long K it reaches 1e-5 of the result (measured:
+  // 1.2e-5 at K = 1024 with six products, where the operand planes themselves are exact to
+  // 2^-25).  The accumulator is therefore handed over every CHUNK k-blocks: the epilogue warps
+  // add it into fp32 registers with round-to-nearest while the MMA warp continues in the
+  // other accumulator.  0: one hand-over per tile (bf16 storage, where 2e-2 is the bar).
+  static constexpr int CHUNK = NPROD == 1 ? 0 : 2;
 };
+
+// Stores 32 consecutive columns (starting at nb) of row m of the result: r holds the fp32 bit
+// patterns.  Partial tile of a K split, or the final C in fp32 / bf16 / fp16, optionally
+// accumulating into what C holds.
+__device__ __forceinline__ void store_chunk(const Params& p, int sp, int m, int nb,
+                                      const uint32_t (&r)[32]) {
+  if (m < p.M && nb < p.N) {
+    if (p.partial) {
+      float* dst = p.partial + ((long long)sp * p.M + m) * p.N + nb;
+      if (nb + 32 <= p.N && (p.N & 3) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) =
+              make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                          __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+      } else {
+        for (int j = 0; j < 32 && nb + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
+      }
+    } else if (p.c_is_bf16) {
+      __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)m * p.ldc + nb;
+      if (nb + 32 <= p.N && (p.ldc & 7) == 0 &&
+          (reinterpret_cast<uintptr_t>(p.c) & 15) == 0) {
+        // 16-byte stores: eight bf16 per store, four per 32-column chunk
+#pragma unroll
+        for (int j = 0; j < 32; j += 8) {
+          float v[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
+          if (p.accumulate) {
+            const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
+            const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              if (p.c_is_bf16 == 2) {
+                const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ow[e]));
+                v[2 * e] += f.x;
+                v[2 * e + 1] += f.y;
+              } else {
+                v[2 * e] += __uint_as_float(ow[e] << 16);
+                v[2 * e + 1] += __uint_as_float(ow[e] & 0xFFFF0000u);
+              }
+            }
+          }
+          uint32_t w[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            if (p.c_is_bf16 == 2) {
+              __half2 t2 = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
+              w[e] = *reinterpret_cast<uint32_t*>(&t2);
+            } else {
+              __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
+              w[e] = *reinterpret_cast<uint32_t*>(&t2);
+            }
+          }
+          *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+      } else {
+        for (int j = 0; j < 32 && nb + j < p.N; ++j) {
+          float v = __uint_as_float(r[j]);
+          if (p.c_is_bf16 == 2) {
+            __half* hd = reinterpret_cast<__half*>(dst);
+            if (p.accumulate) v += __half2float(hd[j]);
+            hd[j] = __float2half_rn(v);
+          } else {
+            if (p.accumulate) v += __bfloat162float(dst[j]);
+            dst[j] = __float2bfloat16_rn(v);
+          }
+        }
+      }
+    } else {
+      float* dst = reinterpret_cast<float*>(p.c) + (long long)m * p.ldc + nb;
+      if (nb + 32 <= p.N && (p.ldc & 3) == 0 &&
+          (reinterpret_cast<uintptr_t>(p.c) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
+                                 __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+          if (p.accumulate) {
+            const float4 c0 = *reinterpret_cast<const float4*>(dst + j);
+            o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w;
+          }
+          *reinterpret_cast<float4*>(dst + j) = o;
+        }
+      } else {
+        for (int j = 0; j < 32 && nb + j < p.N; ++j) {
+          float v = __uint_as_float(r[j]);
+          if (p.accumulate) v += dst[j];
+          dst[j] = v;
+        }
+      }
+    }
+  }
+}
 
 template <int NPROD>
 __global__ void __launch_bounds__(THREADS, 1)
@@ -262,159 +259,109 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t b_lbo = p.b_mn_major ? TILE_BYTES / 2 : 16, b_kstep = p.b_mn_major ? 2048 : 32;
       uint32_t stage = 0, phase = 0;
       uint32_t acc_phase[2] = {0, 0};
-      int it = 0;
+      int cidx = 0;  // accumulator hand-overs so far: they alternate between the two buffers
       bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x, ++it) {
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
         const int sp = item / (p.tiles_n * p.tiles_m);
         const int kb0 = sp * p.kb_per_split;
         const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
-        const int acc = it & 1;
-        if (!mbar_wait(acce_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err, 2)) { ok = false; break; }
-        acc_phase[acc] ^= 1u;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
-        uint32_t first = 1;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err, 3)) { ok = false; break; }
+        int kb = kb0;
+        while (kb < kb1 && ok) {
+          const int acc = cidx & 1;
+          ++cidx;
+          if (!mbar_wait(acce_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err, 2)) { ok = false; break; }
+          acc_phase[acc] ^= 1u;
           tc_fence_after();
-          const uint32_t sa = base + stage * C::STAGE_BYTES;
-          const uint32_t sb = sa + C::PLANES * TILE_BYTES;
+          const uint32_t d_tmem = tmem_base + acc * BN;
+          const int kend = C::CHUNK ? min(kb1, kb + C::CHUNK) : kb1;
+          uint32_t first = 1;
+          for (; kb < kend; ++kb) {
+            if (!mbar_wait(full_bar(stage), phase, abort_flag, p.err, 3)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = base + stage * C::STAGE_BYTES;
+            const uint32_t sb = sa + C::PLANES * TILE_BYTES;
 #pragma unroll
-          for (int pr = 0; pr < NPROD; ++pr) {
-            // plane pairs, most significant first:
-            //   (0,0) (0,1) (1,0) | (1,1) (0,2) (2,0)      0 = hi, 1 = mid/lo, 2 = lo
-            const int ia = pr == 2 ? 1 : (pr == 3 ? 1 : (pr == 5 ? 2 : 0));
-            const int ib = pr == 1 ? 1 : (pr == 3 ? 1 : (pr == 4 ? 2 : 0));
-            const uint32_t pa = sa + ia * TILE_BYTES;
-            const uint32_t pb = sb + ib * TILE_BYTES;
+            for (int pr = 0; pr < NPROD; ++pr) {
+              // plane pairs, most significant first:
+              //   (0,0) (0,1) (1,0) | (1,1) (0,2) (2,0)      0 = hi, 1 = mid/lo, 2 = lo
+              const int ia = pr == 2 ? 1 : (pr == 3 ? 1 : (pr == 5 ? 2 : 0));
+              const int ib = pr == 1 ? 1 : (pr == 3 ? 1 : (pr == 4 ? 2 : 0));
+              const uint32_t pa = sa + ia * TILE_BYTES;
+              const uint32_t pb = sb + ib * TILE_BYTES;
 #pragma unroll
-            for (int ks = 0; ks < BK / UK; ++ks) {
-              const uint64_t da = smem_desc(pa + ks * a_kstep, a_lbo, 1024);
-              const uint64_t db = smem_desc(pb + ks * b_kstep, b_lbo, 1024);
-              tc_mma_bf16(d_tmem, da, db, idesc, first ? 0u : 1u);
-              first = 0;
+              for (int ks = 0; ks < BK / UK; ++ks) {
+                const uint64_t da = smem_desc(pa + ks * a_kstep, a_lbo, 1024);
+                const uint64_t db = smem_desc(pb + ks * b_kstep, b_lbo, 1024);
+                tc_mma_bf16(d_tmem, da, db, idesc, first ? 0u : 1u);
+                first = 0;
+              }
             }
+            tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
           }
-          tc_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          if (ok) tc_commit(accf_bar(acc));  // this chunk of the accumulation is complete
         }
-        if (ok) tc_commit(accf_bar(acc));  // accumulator complete
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
     uint32_t acc_phase[2] = {0, 0};
-    int it = 0;
+    int cidx = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total_items; item += gridDim.x, ++it) {
+    for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
       const int tn = item % p.tiles_n;
       const int tm = (item / p.tiles_n) % p.tiles_m;
       const int sp = item / (p.tiles_n * p.tiles_m);
-      const int acc = it & 1;
-      if (ok) ok = mbar_wait(accf_bar(acc), acc_phase[acc], abort_flag, p.err, 4);
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      acc_phase[acc] ^= 1u;
-      tc_fence_after();
+      const int kb0 = sp * p.kb_per_split;
+      const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+      const int nchunks = C::CHUNK ? (kb1 - kb0 + C::CHUNK - 1) / C::CHUNK : 1;
       const int m = tm * BM + quad * 32 + lane;
       const int n0 = tn * BN;
-      const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+      // running sums of this thread's row of the tile (only with chunked hand-over)
+      float sum[C::CHUNK ? BN : 1];
+#pragma unroll
+      for (int j = 0; j < (C::CHUNK ? BN : 1); ++j) sum[j] = 0.f;
+      for (int c = 0; c < nchunks; ++c) {
+        const int acc = cidx & 1;
+        ++cidx;
+        if (ok) ok = mbar_wait(accf_bar(acc), acc_phase[acc], abort_flag, p.err, 4);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        acc_phase[acc] ^= 1u;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+        if (C::CHUNK) {
+#pragma unroll
+          for (int ch = 0; ch < BN / 32; ++ch) {
+            uint32_t r[32];
+            tc_ld32(taddr + ch * 32, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sum[(C::CHUNK ? ch * 32 : 0) + j] += __uint_as_float(r[j]);
+          }
+        } else {
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        uint32_t r[32];
-        tc_ld32(taddr + ch * 32, r);
-        tc_wait_ld();
-        const int nb = n0 + ch * 32;
-        if (m < p.M && nb < p.N) {
-          if (p.partial) {
-            float* dst = p.partial + ((long long)sp * p.M + m) * p.N + nb;
-            if (nb + 32 <= p.N && (p.N & 3) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) =
-                    make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-            } else {
-              for (int j = 0; j < 32 && nb + j < p.N; ++j) dst[j] = __uint_as_float(r[j]);
-            }
-          } else if (p.c_is_bf16) {
-            __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(p.c) + (long long)m * p.ldc + nb;
-            if (nb + 32 <= p.N && (p.ldc & 7) == 0 &&
-                (reinterpret_cast<uintptr_t>(p.c) & 15) == 0) {
-              // 16-byte stores: eight bf16 per store, four per 32-column chunk
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                float v[8];
-#pragma unroll
-                for (int e = 0; e < 8; ++e) v[e] = __uint_as_float(r[j + e]);
-                if (p.accumulate) {
-                  const uint4 old = *reinterpret_cast<const uint4*>(dst + j);
-                  const uint32_t ow[4] = {old.x, old.y, old.z, old.w};
-#pragma unroll
-                  for (int e = 0; e < 4; ++e) {
-                    if (p.c_is_bf16 == 2) {
-                      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&ow[e]));
-                      v[2 * e] += f.x;
-                      v[2 * e + 1] += f.y;
-                    } else {
-                      v[2 * e] += __uint_as_float(ow[e] << 16);
-                      v[2 * e + 1] += __uint_as_float(ow[e] & 0xFFFF0000u);
-                    }
-                  }
-                }
-                uint32_t w[4];
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  if (p.c_is_bf16 == 2) {
-                    __half2 t2 = __floats2half2_rn(v[2 * e], v[2 * e + 1]);
-                    w[e] = *reinterpret_cast<uint32_t*>(&t2);
-                  } else {
-                    __nv_bfloat162 t2 = __floats2bfloat162_rn(v[2 * e], v[2 * e + 1]);
-                    w[e] = *reinterpret_cast<uint32_t*>(&t2);
-                  }
-                }
-                *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-              }
-            } else {
-              for (int j = 0; j < 32 && nb + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]);
-                if (p.c_is_bf16 == 2) {
-                  __half* hd = reinterpret_cast<__half*>(dst);
-                  if (p.accumulate) v += __half2float(hd[j]);
-                  hd[j] = __float2half_rn(v);
-                } else {
-                  if (p.accumulate) v += __bfloat162float(dst[j]);
-                  dst[j] = __float2bfloat16_rn(v);
-                }
-              }
-            }
-          } else {
-            float* dst = reinterpret_cast<float*>(p.c) + (long long)m * p.ldc + nb;
-            if (nb + 32 <= p.N && (p.ldc & 3) == 0 &&
-                (reinterpret_cast<uintptr_t>(p.c) & 15) == 0) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]),
-                                       __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                if (p.accumulate) {
-                  const float4 c0 = *reinterpret_cast<const float4*>(dst + j);
-                  o.x += c0.x; o.y += c0.y; o.z += c0.z; o.w += c0.w;
-                }
-                *reinterpret_cast<float4*>(dst + j) = o;
-              }
-            } else {
-              for (int j = 0; j < 32 && nb + j < p.N; ++j) {
-                float v = __uint_as_float(r[j]);
-                if (p.accumulate) v += dst[j];
-                dst[j] = v;
-              }
-            }
+          for (int ch = 0; ch < BN / 32; ++ch) {
+            uint32_t r[32];
+            tc_ld32(taddr + ch * 32, r);
+            tc_wait_ld();
+            store_chunk(p, sp, m, n0 + ch * 32, r);
           }
         }
+        tc_fence_before();
+        mbar_arrive(acce_bar(acc));
       }
-      tc_fence_before();
-      mbar_arrive(acce_bar(acc));
+      if (!ok) break;
+      if (C::CHUNK) {
+#pragma unroll
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          uint32_t r[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[(C::CHUNK ? ch * 32 : 0) + j]);
+          store_chunk(p, sp, m, n0 + ch * 32, r);
+        }
+      }
     }
   }
 
@@ -519,35 +466,6 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ part, int splits,
 // ----------------------------------------------------------------------------
 // Host side
 // ----------------------------------------------------------------------------
-PFN_cuTensorMapEncodeTiled encode_fn() {
-  static PFN_cuTensorMapEncodeTiled fn = nullptr;
-  static std::once_flag once;
-  std::call_once(once, [] {
-    void* f = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &f, cudaEnableDefault, &q) ==
-            cudaSuccess && q == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<PFN_cuTensorMapEncodeTiled>(f);
-    cudaGetLastError();
-  });
-  return fn;
-}
-
-// bf16 tensor map over `planes` matrices of `outer` rows x `inner` contiguous elements
-// (leading dimension ld, planes plane_stride elements apart).
-bool make_map(CUtensorMap* map, const void* ptr, long long inner, long long outer, long long ld,
-              long long plane_stride, int planes, int box_inner, int box_outer) {
-  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)planes};
-  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, (cuuint64_t)(planes > 1 ? plane_stride : ld * outer) * 2};
-  cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = encode_fn()(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims,
-                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS;
-}
-
 struct Operand {
   bool mn_major;          // contiguous along M (A) or N (B)
   long long ld;           // elements between consecutive outer indices

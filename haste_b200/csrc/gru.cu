@@ -194,7 +194,10 @@ int gru_forward(const GruFwd& a, cudaStream_t s) {
     HB_TRY(gemm(g, s));
   }
   ProfScope p(PH_REC_FWD, s);
-  int st_ = a.h_out ? HASTE_B200_ERR_UNSUPPORTED : gru_forward_persistent(a, s);
+  // large bf16 batches: the tensor-core recurrence; small batches: the register-resident one
+  int st_ = gru_forward_tc(a, s);
+  if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
+  st_ = a.h_out ? HASTE_B200_ERR_UNSUPPORTED : gru_forward_persistent(a, s);
   if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
   if (a.dtype == HASTE_B200_F32) return gru_forward_stepwise<float>(a, s);
   if (a.dtype == HASTE_B200_F16) return gru_forward_stepwise<__half>(a, s);
@@ -235,10 +238,19 @@ int gru_backward(const GruBwd& a, cudaStream_t s) {
   int st_;
   {
     ProfScope p(PH_REC_BWD, s);
-    st_ = a.iterate ? HASTE_B200_ERR_UNSUPPORTED
-                    : gru_backward_persistent(a, dh_carry, planes, s);
-    have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
-    persistent_ran = st_ == HASTE_B200_OK;
+    st_ = gru_backward_tc(a, dh_carry, s);
+    if (st_ == HASTE_B200_OK) {
+      // the tensor-core kernel leaves the recurrent contribution of the last processed step
+      // (t = 0) out of dh: dh += dq_0 . R^T
+      GemmDesc gd{a.dtype, HASTE_B200_F32, N, H, 3 * H, a.dq, 3LL * H, 1, a.R,
+                  a.transposed_inputs ? H : 1, a.transposed_inputs ? 1 : 3LL * H, dh_carry, H, 1};
+      st_ = gemm_small(gd, s);
+    } else if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
+      st_ = a.iterate ? HASTE_B200_ERR_UNSUPPORTED
+                      : gru_backward_persistent(a, dh_carry, planes, s);
+      have_planes = st_ == HASTE_B200_OK && planes.p != nullptr;
+      persistent_ran = st_ == HASTE_B200_OK;
+    }
     if (st_ == HASTE_B200_ERR_UNSUPPORTED) {
     st_ = (a.dtype == HASTE_B200_F32)   ? gru_backward_stepwise<float>(a, dh_carry, s)
           : (a.dtype == HASTE_B200_F16) ? gru_backward_stepwise<__half>(a, dh_carry, s)

@@ -20,13 +20,29 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from . import ops
+from . import _C, ops
 
 __all__ = ["LSTM", "GRU", "IndRNN", "LayerNormLSTM", "LayerNormGRU", "LayerNormIndRNN", "Stack"]
 
 
 def _empty_mask(x):
     return x.new_empty(0, 0, 0)
+
+
+class _sm_budget:
+    """While active, one persistent recurrence launch occupies at most `sms` SMs (0: no
+    limit), so that the two directions of a bidirectional level are co-resident."""
+
+    def __init__(self, sms):
+        self.sms = sms
+
+    def __enter__(self):
+        if self.sms:
+            _C.set_sm_budget(self.sms)
+
+    def __exit__(self, *exc):
+        if self.sms:
+            _C.set_sm_budget(0)
 
 
 def _bucket(ctx):
@@ -47,8 +63,10 @@ def _gradients_ready(ctx, names, grads):
 # --------------------------------------------------------------------------
 class _LSTMFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, dp, *inputs):
-        h, c, cache = ops.lstm_forward(training, zoneout_prob, *inputs)
+    def forward(ctx, training, zoneout_prob, opts, *inputs):
+        dp, ctx.sm_budget = opts
+        with _sm_budget(ctx.sm_budget):
+            h, c, cache = ops.lstm_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[3:], h, c, cache)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
@@ -59,16 +77,19 @@ class _LSTMFunction(torch.autograd.Function):
     def backward(ctx, grad_h, grad_c):
         if not ctx.training:
             raise RuntimeError('LSTM backward can only be called in training mode')
-        grads = ops.lstm_backward(*ctx.saved_tensors, grad_h.contiguous(), grad_c.contiguous(),
-                                  transposed=False, grads=_bucket(ctx))
+        with _sm_budget(ctx.sm_budget):
+            grads = ops.lstm_backward(*ctx.saved_tensors, grad_h.contiguous(), grad_c.contiguous(),
+                                      transposed=False, grads=_bucket(ctx))
         _gradients_ready(ctx, ['kernel', 'recurrent_kernel', 'bias'], grads[3:])
         return (None, None, None, *grads, None)
 
 
 class _GRUFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, dp, *inputs):
-        h, cache = ops.gru_forward(training, zoneout_prob, *inputs)
+    def forward(ctx, training, zoneout_prob, opts, *inputs):
+        dp, ctx.sm_budget = opts
+        with _sm_budget(ctx.sm_budget):
+            h, cache = ops.gru_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[2:], h, cache)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
@@ -79,15 +100,18 @@ class _GRUFunction(torch.autograd.Function):
     def backward(ctx, grad_h):
         if not ctx.training:
             raise RuntimeError('GRU backward can only be called in training mode')
-        grads = ops.gru_backward(*ctx.saved_tensors, grad_h.contiguous(), transposed=False, grads=_bucket(ctx))
+        with _sm_budget(ctx.sm_budget):
+            grads = ops.gru_backward(*ctx.saved_tensors, grad_h.contiguous(), transposed=False, grads=_bucket(ctx))
         _gradients_ready(ctx, ['kernel', 'recurrent_kernel', 'bias', 'recurrent_bias'], grads[2:])
         return (None, None, None, *grads, None)
 
 
 class _IndRNNFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, dp, *inputs):
-        h = ops.indrnn_forward(training, zoneout_prob, *inputs)
+    def forward(ctx, training, zoneout_prob, opts, *inputs):
+        dp, ctx.sm_budget = opts
+        with _sm_budget(ctx.sm_budget):
+            h = ops.indrnn_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[2:], h)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
@@ -98,15 +122,18 @@ class _IndRNNFunction(torch.autograd.Function):
     def backward(ctx, grad_h):
         if not ctx.training:
             raise RuntimeError('IndRNN backward can only be called in training mode')
-        grads = ops.indrnn_backward(*ctx.saved_tensors, grad_h.contiguous(), transposed=False, grads=_bucket(ctx))
+        with _sm_budget(ctx.sm_budget):
+            grads = ops.indrnn_backward(*ctx.saved_tensors, grad_h.contiguous(), transposed=False, grads=_bucket(ctx))
         _gradients_ready(ctx, ['kernel', 'recurrent_scale', 'bias'], grads[2:])
         return (None, None, None, *grads, None)
 
 
 class _LayerNormLSTMFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, dp, *inputs):
-        outputs = ops.layer_norm_lstm_forward(training, zoneout_prob, *inputs)
+    def forward(ctx, training, zoneout_prob, opts, *inputs):
+        dp, ctx.sm_budget = opts
+        with _sm_budget(ctx.sm_budget):
+            outputs = ops.layer_norm_lstm_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[3:], *outputs)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
@@ -117,16 +144,19 @@ class _LayerNormLSTMFunction(torch.autograd.Function):
     def backward(ctx, grad_h, grad_c):
         if not ctx.training:
             raise RuntimeError('LayerNormLSTM backward can only be called in training mode')
-        grads = ops.layer_norm_lstm_backward(*ctx.saved_tensors, grad_h.contiguous(),
-                                             grad_c.contiguous(), transposed=False, grads=_bucket(ctx))
+        with _sm_budget(ctx.sm_budget):
+            grads = ops.layer_norm_lstm_backward(*ctx.saved_tensors, grad_h.contiguous(),
+                                                 grad_c.contiguous(), transposed=False, grads=_bucket(ctx))
         _gradients_ready(ctx, ['kernel', 'recurrent_kernel', 'bias', 'gamma', 'gamma_h', 'beta_h'], grads[3:])
         return (None, None, None, *grads, None)
 
 
 class _LayerNormGRUFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, dp, *inputs):
-        output = ops.layer_norm_gru_forward(training, zoneout_prob, *inputs)
+    def forward(ctx, training, zoneout_prob, opts, *inputs):
+        dp, ctx.sm_budget = opts
+        with _sm_budget(ctx.sm_budget):
+            output = ops.layer_norm_gru_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[2:], *output)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
@@ -137,16 +167,19 @@ class _LayerNormGRUFunction(torch.autograd.Function):
     def backward(ctx, grad_h):
         if not ctx.training:
             raise RuntimeError('LayerNormGRU backward can only be called in training mode')
-        grads = ops.layer_norm_gru_backward(*ctx.saved_tensors, grad_h.contiguous(),
-                                            transposed=False, grads=_bucket(ctx))
+        with _sm_budget(ctx.sm_budget):
+            grads = ops.layer_norm_gru_backward(*ctx.saved_tensors, grad_h.contiguous(),
+                                                transposed=False, grads=_bucket(ctx))
         _gradients_ready(ctx, ['kernel', 'recurrent_kernel', 'bias', 'recurrent_bias', 'gamma'], grads[2:])
         return (None, None, None, *grads, None)
 
 
 class _LayerNormIndRNNFunction(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, training, zoneout_prob, dp, *inputs):
-        output = ops.layer_norm_indrnn_forward(training, zoneout_prob, *inputs)
+    def forward(ctx, training, zoneout_prob, opts, *inputs):
+        dp, ctx.sm_budget = opts
+        with _sm_budget(ctx.sm_budget):
+            output = ops.layer_norm_indrnn_forward(training, zoneout_prob, *inputs)
         ctx.save_for_backward(inputs[0], *inputs[2:], *output)
         ctx.mark_non_differentiable(inputs[-1])
         ctx.training = training
@@ -157,8 +190,9 @@ class _LayerNormIndRNNFunction(torch.autograd.Function):
     def backward(ctx, grad_h):
         if not ctx.training:
             raise RuntimeError('LayerNormIndRNN backward can only be called in training mode')
-        grads = ops.layer_norm_indrnn_backward(*ctx.saved_tensors, grad_h.contiguous(),
-                                               transposed=False, grads=_bucket(ctx))
+        with _sm_budget(ctx.sm_budget):
+            grads = ops.layer_norm_indrnn_backward(*ctx.saved_tensors, grad_h.contiguous(),
+                                                   transposed=False, grads=_bucket(ctx))
         _gradients_ready(ctx, ['kernel', 'recurrent_scale', 'bias', 'gamma'], grads[2:])
         return (None, None, None, *grads, None)
 
@@ -204,6 +238,9 @@ class BaseRNN(nn.Module):
         # set by haste_b200.data_parallel.attach(): where this layer's backward pass leaves its
         # parameter gradients and how they are summed over the ranks
         self._dp = None
+        # SMs one recurrence launch of this layer may occupy (0: all); Stack gives each
+        # direction of a bidirectional level half of the GPU
+        self._sm_budget = 0
 
     def _permute(self, x):
         return x.permute(1, 0, 2) if self.batch_first else x
@@ -319,7 +356,7 @@ class LSTM(BaseRNN):
         shape = [1, input.shape[1], self.hidden_size]
         h0, c0 = self._get_state(input, state, (shape, shape))
         h, c = _LSTMFunction.apply(
-            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, (self._dp, self._sm_budget), input.contiguous(), h0[0].contiguous(),
             c0[0].contiguous(), self.kernel.contiguous(),
             self._dropconnect(dropconnect_mask).contiguous(), self.bias.contiguous(),
             self._get_zoneout_mask(input, zoneout_mask).contiguous())
@@ -375,7 +412,7 @@ class GRU(BaseRNN):
         input = self._permute(input)
         h0 = self._get_state(input, state, [1, input.shape[1], self.hidden_size])
         h = _GRUFunction.apply(
-            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, (self._dp, self._sm_budget), input.contiguous(), h0[0].contiguous(),
             self.kernel.contiguous(), self._dropconnect(dropconnect_mask).contiguous(),
             self.bias.contiguous(), self.recurrent_bias.contiguous(),
             self._get_zoneout_mask(input, zoneout_mask).contiguous())
@@ -405,7 +442,7 @@ class IndRNN(BaseRNN):
         input = self._permute(input)
         h0 = self._get_state(input, state, [1, input.shape[1], self.hidden_size])
         h = _IndRNNFunction.apply(
-            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, (self._dp, self._sm_budget), input.contiguous(), h0[0].contiguous(),
             self.kernel.contiguous(), self.recurrent_scale.contiguous(), self.bias.contiguous(),
             self._get_zoneout_mask(input, zoneout_mask).contiguous())
         state = self._get_final_state(h, lengths)
@@ -446,7 +483,7 @@ class LayerNormLSTM(BaseRNN):
         shape = [1, input.shape[1], self.hidden_size]
         h0, c0 = self._get_state(input, state, (shape, shape))
         h, c = _LayerNormLSTMFunction.apply(
-            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, (self._dp, self._sm_budget), input.contiguous(), h0[0].contiguous(),
             c0[0].contiguous(), self.kernel.contiguous(),
             self._dropconnect(dropconnect_mask).contiguous(), self.bias.contiguous(),
             self.gamma.contiguous(), self.gamma_h.contiguous(), self.beta_h.contiguous(),
@@ -484,7 +521,7 @@ class LayerNormGRU(BaseRNN):
         input = self._permute(input)
         h0 = self._get_state(input, state, [1, input.shape[1], self.hidden_size])
         h = _LayerNormGRUFunction.apply(
-            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, (self._dp, self._sm_budget), input.contiguous(), h0[0].contiguous(),
             self.kernel.contiguous(), self._dropconnect(dropconnect_mask).contiguous(),
             self.bias.contiguous(), self.recurrent_bias.contiguous(), self.gamma.contiguous(),
             self._get_zoneout_mask(input, zoneout_mask).contiguous())
@@ -516,7 +553,7 @@ class LayerNormIndRNN(BaseRNN):
         input = self._permute(input)
         h0 = self._get_state(input, state, [1, input.shape[1], self.hidden_size])
         h = _LayerNormIndRNNFunction.apply(
-            self.training, self.zoneout, self._dp, input.contiguous(), h0[0].contiguous(),
+            self.training, self.zoneout, (self._dp, self._sm_budget), input.contiguous(), h0[0].contiguous(),
             self.kernel.contiguous(), self.recurrent_scale.contiguous(), self.bias.contiguous(),
             self.gamma.contiguous(), self._get_zoneout_mask(input, zoneout_mask).contiguous())
         state = self._get_final_state(h, lengths)
@@ -529,16 +566,19 @@ class Stack(nn.Module):
     Time-major input `[T,N,C]`.  A bidirectional level runs a forward layer on the
     sequence and a second layer on the time-reversed sequence, reverses that layer's
     output back, and feeds `cat([fw, bw], -1)` to the next level; the two directions
-    of a level are issued on two CUDA streams so that they overlap on the GPU.
+    of a level are issued on two CUDA streams, and (`concurrent_directions`, the default)
+    each direction's persistent recurrence kernel is limited to half of the GPU's SMs so that
+    the two are co-resident and really run at the same time.
     Returns the last level's output (`[T,N,H]` or `[T,N,2H]`).
     `masks`, if given, is a list (per level) of lists (per direction) of dicts with
     optional keys `zoneout_mask` / `dropconnect_mask`.
     """
 
     def __init__(self, cell, input_size, hidden_size, num_layers=1, bidirectional=False,
-                 **cell_kwargs):
+                 concurrent_directions=True, **cell_kwargs):
         super().__init__()
         self.bidirectional = bidirectional
+        self.concurrent_directions = concurrent_directions
         self.num_layers = num_layers
         dirs = 2 if bidirectional else 1
         layers = []
@@ -548,6 +588,7 @@ class Stack(nn.Module):
                                          for _ in range(dirs)]))
         self.layers = nn.ModuleList(layers)
         self._side = None
+        self._budget_set = False
 
     def forward(self, x, masks=None):
         for l, level in enumerate(self.layers):
@@ -557,6 +598,14 @@ class Stack(nn.Module):
                 continue
             if self._side is None:
                 self._side = torch.cuda.Stream(device=x.device)
+            if not self._budget_set and self.concurrent_directions:
+                # half of the GPU per direction: the two directions' persistent kernels, issued
+                # on two streams, then run at the same time instead of one after the other
+                sms = torch.cuda.get_device_properties(x.device).multi_processor_count // 2
+                for lv in self.layers:
+                    for layer in lv:
+                        layer._sm_budget = sms
+                self._budget_set = True
             main = torch.cuda.current_stream()
             # the side stream starts after everything queued so far (x included) and makes its
             # own reversed copy, so no kernel of the backward-direction layer can run ahead

@@ -65,9 +65,15 @@ const char* haste_b200_version(void);
 enum {
   HASTE_B200_PATH_AUTO = 0,
   HASTE_B200_PATH_STEPWISE = 1,   /* one launch sequence per time step */
-  HASTE_B200_PATH_PERSISTENT = 2  /* one persistent kernel per layer pass */
+  HASTE_B200_PATH_PERSISTENT = 2, /* one persistent kernel per layer pass */
+  HASTE_B200_PATH_NO_TENSOR_CORE = 3 /* automatic, but without the tcgen05 recurrence */
 };
 int haste_b200_set_recurrence_path(int path);
+/* Limits the number of SMs one persistent recurrence launch of the calling process occupies
+ * (0 = the whole GPU, the default).  With half the GPU per launch the two directions of a
+ * bidirectional layer, issued on two streams, are co-resident and run concurrently.  Honoured by
+ * the tensor-core GRU recurrence; no reference counterpart. */
+int haste_b200_set_sm_budget(int sms);
 enum { HASTE_B200_GEMM_AUTO = 0, HASTE_B200_GEMM_SIMT = 1, HASTE_B200_GEMM_TCGEN05 = 2 };
 int haste_b200_set_gemm_path(int path);
 /* Number of kernels this library has launched in the calling process. */

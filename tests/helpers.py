@@ -217,19 +217,32 @@ def oracle_stack(net, cell, x, dy, masks=None, dropconnect=0.0, zoneout=0.0, bf1
     return inp.detach(), dx, [{k: v.grad for k, v in p.items()} for p in leaves]
 
 
-def compare_stack(net, y, dx, ref, tol, what):
+def compare_stack(net, y, dx, ref, tol, what, ref_native=None):
     """Outputs, input gradient and EVERY parameter gradient of every layer and direction of a
-    Stack against `oracle_stack`'s result; returns the worst error."""
+    Stack against `oracle_stack`'s result; returns the worst error.
+
+    `ref_native`, if given, is the same oracle evaluated in the reference's own working
+    precision (float32).  A deep normalised stack amplifies float32 rounding: where the
+    reference's own float32 path is itself further than `tol` from the float64 result, no
+    float32 implementation can be closer, and the bar for that tensor becomes twice the
+    reference path's own distance (the same rule as for the reference's CUDA build)."""
     ref_y, ref_dx, ref_grads = ref
-    worst = assert_close(y, ref_y, tol, f"{what} y")
-    worst = max(worst, assert_close(dx, ref_dx, tol, f"{what} dx"))
+
+    def bar(native, exact):
+        return tol if native is None else max(tol, 2.0 * max_rel_err(native, exact))
+
+    worst = assert_close(y, ref_y, bar(ref_native and ref_native[0], ref_y), f"{what} y")
+    worst = max(worst, assert_close(dx, ref_dx, bar(ref_native and ref_native[1], ref_dx), f"{what} dx"))
     i = 0
     for l, level in enumerate(net.layers):
         for d_, layer in enumerate(level):
             for k, v in layer.named_parameters():
                 got, want = v.grad, ref_grads[i][k]
+                nat = ref_native[2][i][k] if ref_native else None
                 if k == "gamma" and type(layer).__name__ == "LayerNormIndRNN":
                     got, want = got[0], want[0]  # row 1 of gamma is unused by this cell
-                worst = max(worst, assert_close(got, want, tol, f"{what} layer {l} dir {d_} d{k}"))
+                    nat = nat[0] if nat is not None else None
+                worst = max(worst, assert_close(got, want, bar(nat, want),
+                                                f"{what} layer {l} dir {d_} d{k}"))
             i += 1
     return worst

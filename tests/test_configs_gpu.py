@@ -2,8 +2,10 @@
 
   * 3-layer bidirectional LayerNormLSTM, C=80, H=512, N=64, zoneout 0.1 and DropConnect 0.05
     with masks drawn per layer and direction from torch.Generator(1234 + layer*2 + dir) and
-    passed explicitly; fp32 (1e-4) and bf16 (2e-2); T=50 against the float64 oracle and the
-    full T=400 against the float32 oracle.
+    passed explicitly; fp32 and bf16 (2e-2); T=50 and the full T=400 against the float64
+    oracle.  This stack amplifies float32 rounding (the reference's own float32 path is
+    3e-4 .. 4e-4 from the float64 result), so the fp32 bar per tensor is 1e-4 or twice the
+    distance of the reference's float32 path from the float64 result, whichever is larger.
   * 6-layer IndRNN and LayerNormIndRNN, C=H=1024, N=128, u ~ U(0,1), zoneout 0.1: T=100
     against the float64 oracle, and at the full T=2000 the properties that need no oracle
     (causality of a prefix, linearity of the backward pass).
@@ -73,17 +75,23 @@ def test_config2_three_layer_bidirectional_layer_norm_lstm_with_masks(dtype, tol
     y, dx = _run_stack(net, x, dy, _to_device(masks, dtype))
     ref = oracle_stack(net, "layer_norm_lstm", x, dy, masks, dropconnect=0.05, zoneout=0.1,
                        bf16=dtype == torch.bfloat16)
-    compare_stack(net, y, dx, ref, tol, "config 2 T=50")
+    native = None
+    if dtype == torch.float32:
+        # three LayerNorms per step and six layer passes amplify float32 rounding: the
+        # reference's own float32 path is 3e-4 .. 4e-4 from the float64 result here
+        native = oracle_stack(net, "layer_norm_lstm", x, dy, masks, dropconnect=0.05, zoneout=0.1,
+                              dtype=torch.float32)
+    compare_stack(net, y, dx, ref, tol, "config 2 T=50", ref_native=native)
 
 
 def test_config2_full_length_fp32():
     T = 400
     net, x, dy, masks = _config2(T, torch.float32, seed=12)
     y, dx = _run_stack(net, x, dy, _to_device(masks, torch.float32))
-    # float32 oracle at this length (its own rounding, ~1e-6, is far inside the bar)
-    ref = oracle_stack(net, "layer_norm_lstm", x, dy, masks, dropconnect=0.05, zoneout=0.1,
-                       dtype=torch.float32)
-    compare_stack(net, y, dx, ref, TOL_F32, "config 2 T=400")
+    ref = oracle_stack(net, "layer_norm_lstm", x, dy, masks, dropconnect=0.05, zoneout=0.1)
+    native = oracle_stack(net, "layer_norm_lstm", x, dy, masks, dropconnect=0.05, zoneout=0.1,
+                          dtype=torch.float32)
+    compare_stack(net, y, dx, ref, TOL_F32, "config 2 T=400", ref_native=native)
 
 
 # ------------------------------------------------------------------ configuration 3
