@@ -37,7 +37,8 @@ constexpr int BM = 128, BN = 128, BK = 64;   // CTA tile; BK bf16 = one 128-byte
 constexpr int UK = 16;                       // K of one tcgen05.mma (bf16)
 constexpr int TILE_BYTES = BM * BK * 2;      // one operand plane of one stage (A or B): 16 KiB
 constexpr int THREADS = 192;                 // warp 0 TMA, warp 1 MMA, warps 2..5 epilogue
-constexpr int TMEM_COLS = 2 * BN;            // two fp32 accumulators of BN columns
+constexpr int NACC = 4;                      // fp32 accumulators of BN columns in tensor memory
+constexpr int TMEM_COLS = NACC * BN;         // (all 512 columns: one CTA per SM)
 
 struct Params {
   int M, N, K;
@@ -65,7 +66,9 @@ struct Cfg {
   // 2^-25).  The accumulator is therefore handed over every CHUNK k-blocks: the epilogue warps
   // add it into fp32 registers with round-to-nearest while the MMA warp continues in the
   // other accumulator.  0: one hand-over per tile (bf16 storage, where 2e-2 is the bar).
-  static constexpr int CHUNK = NPROD == 1 ? 0 : 2;
+  // Four accumulators take turns, so the MMA warp runs up to three chunks ahead of the
+  // epilogue; a chunk is about 1.6 us of MMA work either way.
+  static constexpr int CHUNK = NPROD == 1 ? 0 : (NPROD == 3 ? 4 : 2);
 };
 
 // Stores 32 consecutive columns (starting at nb) of row m of the result: r holds the fp32 bit
@@ -170,13 +173,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
   uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + C::STAGES * C::STAGE_BYTES);
-  // barrier slots: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  // barrier slots: full[STAGES], empty[STAGES], acc_full[NACC], acc_empty[NACC]
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
   auto accf_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + a); };
-  auto acce_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + 2 + a); };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 4);
+  auto acce_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + NACC + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 2 * NACC);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -186,7 +189,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < NACC; ++a) {
       mbar_init(accf_bar(a), 1);
       mbar_init(acce_bar(a), 128);
     }
@@ -258,7 +261,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t a_lbo = p.a_mn_major ? TILE_BYTES / 2 : 16, a_kstep = p.a_mn_major ? 2048 : 32;
       const uint32_t b_lbo = p.b_mn_major ? TILE_BYTES / 2 : 16, b_kstep = p.b_mn_major ? 2048 : 32;
       uint32_t stage = 0, phase = 0;
-      uint32_t acc_phase[2] = {0, 0};
+      uint32_t acc_phase[NACC] = {0, 0, 0, 0};
       int cidx = 0;  // accumulator hand-overs so far: they alternate between the two buffers
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
@@ -267,7 +270,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
         int kb = kb0;
         while (kb < kb1 && ok) {
-          const int acc = cidx & 1;
+          const int acc = cidx % NACC;
           ++cidx;
           if (!mbar_wait(acce_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err, 2)) { ok = false; break; }
           acc_phase[acc] ^= 1u;
@@ -306,7 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
-    uint32_t acc_phase[2] = {0, 0};
+    uint32_t acc_phase[NACC] = {0, 0, 0, 0};
     int cidx = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
@@ -323,7 +326,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 #pragma unroll
       for (int j = 0; j < (C::CHUNK ? BN : 1); ++j) sum[j] = 0.f;
       for (int c = 0; c < nchunks; ++c) {
-        const int acc = cidx & 1;
+        const int acc = cidx % NACC;
         ++cidx;
         if (ok) ok = mbar_wait(accf_bar(acc), acc_phase[acc], abort_flag, p.err, 4);
         ok = __all_sync(0xffffffffu, ok);

@@ -450,9 +450,15 @@ struct TcGeometry {
 
 // Shapes this path takes: bf16, H a multiple of 64 up to 1024 (the resident slice of R and a
 // useful ring must fit shared memory), at least 96 batch rows (below that the register
-// kernels are faster), everything 16-byte aligned.
-bool tc_geometry(int N, int H, bool fwd, TcGeometry* g) {
-  if (H % 64 != 0 || H < 64 || H > 1024 || N < 96) return false;
+// kernels are faster) and at most two row tiles per CTA: every CTA of a row group streams
+// the group's whole h (or dq), H / 16 copies of it per step out of L2, which is what bounds
+// the step from a few hundred rows per GPU on - there the per-step contraction + pointwise
+// launches of the step-wise path, with their full-size tiles, are faster (measured at
+// H = 1024: forward 9.4 / 10.3 / 11.8 us per step at 128 / 256 / 512 rows against 9.3
+// (register kernel) / 18.4 / 20.5 us; backward 20.6 / 22.4 / 30.4 against 16.4 / 18.6 / 24.6).
+// `half` asks for the geometry under the SM budget (concurrent directions); without it, or
+// when the budget would need more than two tiles per CTA, the whole GPU is used.
+bool tc_geometry_for(int N, int H, bool fwd, int sms, TcGeometry* g) {
   const int K = fwd ? H : 3 * H;
   const size_t r_bytes = (size_t)(K / BK) * (fwd ? 48 : 16) * 128;
   const size_t fixed = 1024 /*alignment*/ + r_bytes + 1024 /*barriers, bias*/;
@@ -462,20 +468,33 @@ bool tc_geometry(int N, int H, bool fwd, TcGeometry* g) {
   g->stages = stages;
   g->smem = fixed + (size_t)stages * A_STAGE;
   g->nHS = H / UC;
-  const int budget = sm_budget() > 0 ? min(sm_budget(), sm_count()) : sm_count();
-  const int groups_max = budget / g->nHS;
+  const int groups_max = sms / g->nHS;
   if (groups_max < 1) return false;
   // 64-row tiles when that still gives one tile per CTA (more CTAs, less to stream per CTA)
   for (int rb = 64; rb <= 128; rb *= 2) {
     const int tiles = ceil_div(N, rb);
     const int mt = ceil_div(tiles, groups_max);
     if (rb == 64 && mt > 1) continue;
+    if (mt > 2) return false;
     g->RB = rb;
     g->MT = mt;
     g->nRG = ceil_div(tiles, mt);
     return true;
   }
   return false;
+}
+
+// `budgeted` reports whether the geometry honours the SM budget (then the two directions of a
+// bidirectional layer are co-resident).
+bool tc_geometry(int N, int H, bool fwd, TcGeometry* g, bool* budgeted) {
+  *budgeted = false;
+  if (H % 64 != 0 || H < 64 || H > 1024 || N < 96) return false;
+  const int budget = sm_budget();
+  if (budget > 0 && budget < sm_count() && tc_geometry_for(N, H, fwd, budget, g)) {
+    *budgeted = true;
+    return true;
+  }
+  return tc_geometry_for(N, H, fwd, sm_count(), g);
 }
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
@@ -530,9 +549,10 @@ int tc_scratch(int tiles, TcParams* p, cudaStream_t s) {
 // shape is not this path's.
 int gru_forward_tc(const GruFwd& a, cudaStream_t s) {
   TcGeometry g;
+  bool budgeted = false;
   if (a.dtype != HASTE_B200_BF16 || recurrence_path() == HASTE_B200_PATH_STEPWISE ||
       recurrence_path() == HASTE_B200_PATH_NO_TENSOR_CORE || a.h_out ||
-      !encode_fn() || !tc_geometry(a.N, a.H, true, &g))
+      !encode_fn() || !tc_geometry(a.N, a.H, true, &g, &budgeted))
     return HASTE_B200_ERR_UNSUPPORTED;
   if (!aligned16(a.R) || !aligned16(a.tmp_Wx) || !aligned16(a.h) || !aligned16(a.v) ||
       !aligned16(a.zoneout_mask) || !aligned16(a.bx) || !aligned16(a.br))
@@ -556,9 +576,15 @@ int gru_forward_tc(const GruFwd& a, cudaStream_t s) {
 // (the caller adds dq_0 . R^T).  Bias gradients are NOT summed here.
 int gru_backward_tc(const GruBwd& a, float* dh_carry, cudaStream_t s) {
   TcGeometry g;
+  bool budgeted = false;
   if (a.dtype != HASTE_B200_BF16 || recurrence_path() == HASTE_B200_PATH_STEPWISE ||
       recurrence_path() == HASTE_B200_PATH_NO_TENSOR_CORE || a.iterate ||
-      !encode_fn() || !tc_geometry(a.N, a.H, false, &g))
+      !encode_fn() || !tc_geometry(a.N, a.H, false, &g, &budgeted))
+    return HASTE_B200_ERR_UNSUPPORTED;
+  // On its own this kernel is slower than the register kernel / the step-wise path (see
+  // tc_geometry_for); it pays when it lets the two directions of a layer run at the same time,
+  // or when the caller asks for the persistent path explicitly.
+  if (!budgeted && recurrence_path() != HASTE_B200_PATH_PERSISTENT)
     return HASTE_B200_ERR_UNSUPPORTED;
   if (!aligned16(a.R) || !aligned16(a.h) || !aligned16(a.v) || !aligned16(a.dh_new) ||
       !aligned16(a.dp) || !aligned16(a.dq) || !aligned16(a.zoneout_mask) || !aligned16(dh_carry))

@@ -217,6 +217,35 @@ def oracle_stack(net, cell, x, dy, masks=None, dropconnect=0.0, zoneout=0.0, bf1
     return inp.detach(), dx, [{k: v.grad for k, v in p.items()} for p in leaves]
 
 
+def oracle_stack_forward(net, cell, x, masks, dropconnect, zoneout, dtype):
+    """Forward pass only of `oracle_stack` (no autograd graph: long sequences stay cheap)."""
+    fn, names, has_c = oracle.CELLS[cell]
+    pname = {"W": "kernel", "R": "recurrent_kernel", "b": "bias", "bx": "bias",
+             "br": "recurrent_bias", "u": "recurrent_scale", "gamma": "gamma",
+             "gamma_h": "gamma_h", "beta_h": "beta_h"}
+    inp = x.detach().to("cpu", dtype)
+    for l, level in enumerate(net.layers):
+        outs = []
+        for d_, layer in enumerate(level):
+            p = {k: v.detach().to("cpu", dtype) for k, v in layer.named_parameters()}
+            m = masks[l][d_] if masks is not None else {}
+            xi = torch.flip(inp, [0]) if d_ == 1 else inp
+            N, H = xi.shape[1], layer.hidden_size
+            args = {"x": xi, "h0": torch.zeros(N, H, dtype=dtype), "c0": torch.zeros(N, H, dtype=dtype)}
+            for k in names:
+                if k in pname and pname[k] in p and k not in args:
+                    args[k] = p[pname[k]]
+            if "R" in args and dropconnect and "dropconnect_mask" in m:
+                args["R"] = args["R"] * (m["dropconnect_mask"].float() / (1.0 - dropconnect)).to(dtype)
+            zm = m.get("zoneout_mask")
+            out = fn(True, zoneout if zm is not None else 0.0, *[args[k] for k in names],
+                     zm.to(dtype) if zm is not None else None)
+            yo = (out[0] if has_c else out)[1:]
+            outs.append(torch.flip(yo, [0]) if d_ == 1 else yo)
+        inp = torch.cat(outs, -1) if len(outs) > 1 else outs[0]
+    return inp
+
+
 def compare_stack(net, y, dx, ref, tol, what, ref_native=None):
     """Outputs, input gradient and EVERY parameter gradient of every layer and direction of a
     Stack against `oracle_stack`'s result; returns the worst error.

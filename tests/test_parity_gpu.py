@@ -165,30 +165,41 @@ def test_persistent_path_bf16(cell, shape):
     _compare(cell, dq, out, grads, ref_out, ref_grads, TOL_BF16)
 
 
-# large bf16 batches take the tensor-core recurrence (tcgen05 step product, TMA-streamed h / dq):
-# 64-row and 128-row tiles, one and several tiles per CTA, ragged last tiles, several row groups
-TC_SHAPES = [(20, 128, 64, 1024), (20, 256, 48, 512), (20, 200, 32, 256), (16, 700, 32, 1024),
-             (16, 1024, 64, 1024), (24, 96, 16, 64)]
+# large bf16 batches can take the tensor-core recurrence (tcgen05 step product, TMA-streamed
+# h / dq): 64-row and 128-row tiles, one and two tiles per CTA, ragged last tiles, several row
+# groups; with and without the SM budget that makes two directions co-resident.  The forward
+# pass takes it by itself; the backward pass when a budget is set or the persistent path is
+# requested.
+TC_SHAPES = [(20, 128, 64, 1024, 0), (20, 256, 48, 512, 0), (20, 200, 32, 256, 0),
+             (16, 700, 32, 512, 0), (16, 512, 64, 1024, 0), (24, 96, 16, 64, 0),
+             (12, 128, 64, 1024, 74), (12, 256, 32, 1024, 74), (10, 300, 32, 512, 74)]
 
 
 @pytest.mark.parametrize("transposed", [False, True])
-@pytest.mark.parametrize("shape", TC_SHAPES, ids=lambda s: "T%d_N%d_C%d_H%d" % s)
+@pytest.mark.parametrize("shape", TC_SHAPES, ids=lambda s: "T%d_N%d_C%d_H%d_sms%d" % s)
 def test_gru_tensor_core_recurrence_bf16(shape, transposed):
     from haste_b200 import _C
-    T, N, C, H = shape
+    T, N, C, H, budget = shape
     d = oracle.make_inputs("gru", T, N, C, H, seed=N + H, zoneout=0.1)
     dq = {k: (v.to(torch.bfloat16).to(torch.float64) if v is not None else None)
           for k, v in d.items()}
     ref_out, ref_grads = oracle.forward_backward("gru", dq, zoneout=0.1)
-    n0 = _C.launch_count()
-    out, grads = run_cuda("gru", dq, zoneout=0.1, dtype=torch.bfloat16, transposed=transposed)
-    _C.sync_check(torch.cuda.current_stream().cuda_stream)
-    assert _C.launch_count() - n0 < 48  # one launch per pass, nothing per time step
-    _compare("gru", dq, out, grads, ref_out, ref_grads, TOL_BF16)
-    # inference (no gate cache, expectation form of zoneout)
-    ref_inf = oracle.forward("gru", dq, training=False, zoneout=0.1)[0]
-    out_inf, _ = run_cuda("gru", dq, zoneout=0.1, dtype=torch.bfloat16, training=False, backward=False)
-    assert_close(out_inf["h"], ref_inf, TOL_BF16, "inference h")
+    _C.set_sm_budget(budget)
+    _C.set_recurrence_path(_C.PATH_PERSISTENT)
+    try:
+        n0 = _C.launch_count()
+        out, grads = run_cuda("gru", dq, zoneout=0.1, dtype=torch.bfloat16, transposed=transposed)
+        _C.sync_check(torch.cuda.current_stream().cuda_stream)
+        assert _C.launch_count() - n0 < 48  # one launch per pass, nothing per time step
+        _compare("gru", dq, out, grads, ref_out, ref_grads, TOL_BF16)
+        # inference (no gate cache, expectation form of zoneout)
+        ref_inf = oracle.forward("gru", dq, training=False, zoneout=0.1)[0]
+        out_inf, _ = run_cuda("gru", dq, zoneout=0.1, dtype=torch.bfloat16, training=False,
+                              backward=False)
+        assert_close(out_inf["h"], ref_inf, TOL_BF16, "inference h")
+    finally:
+        _C.set_sm_budget(0)
+        _C.set_recurrence_path(_C.PATH_AUTO)
 
 
 @pytest.mark.parametrize("path", ["stepwise", "persistent"])
