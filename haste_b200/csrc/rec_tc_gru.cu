@@ -53,6 +53,8 @@ constexpr int MAX_SMEM = 227 * 1024;
 
 struct TcParams {
   int T, N, H, nHS, MT, RB, training, has_zoneout, r_transposed;
+  int stage_bytes;     // RB * 128: one stage of the ring holds one k-block of RB rows
+  int ring_bytes;      // stages * stage_bytes, plus padding up to a whole 128-row tile
   float zoneout_prob;
   const bf16* R;       // forward: [H,3H]; backward: [H,3H] or R_t [3H,H]
   const bf16* bx;      // forward
@@ -152,7 +154,9 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
   const uint32_t r_bytes = (uint32_t)KB * R_TILE;
   const uint32_t ring = base + r_bytes;  // r_bytes is a multiple of 1024
   uint8_t* ring_ptr = aligned + r_bytes;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ring_ptr + (size_t)stages * A_STAGE);
+  // (a 64-row stage is read by the 128-row MMA together with the stage behind it - rows whose
+  // results nobody uses - so the ring is padded by half a tile at its end)
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ring_ptr + p.ring_bytes);
   const uint32_t bar0 = smem_u32(bars);
   auto full_bar = [&](int s) { return bar0 + 8u * s; };
   auto empty_bar = [&](int s) { return bar0 + 8u * (stages + s); };
@@ -188,7 +192,7 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   // ---- streamed-operand ring: zero once, so that rows a 64-row box never writes are zeros
-  for (int i = threadIdx.x; i < stages * A_STAGE / 16; i += TC_THREADS)
+  for (int i = threadIdx.x; i < p.ring_bytes / 16; i += TC_THREADS)
     reinterpret_cast<uint4*>(ring_ptr)[i] = make_uint4(0u, 0u, 0u, 0u);
   // ---- resident operand: this CTA's slice of R, K-major and swizzled
   if (FWD) {
@@ -257,7 +261,7 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
           for (int kb = 0; kb < KB; ++kb) {
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.err, 52)) { ok = false; break; }
             mbar_expect_tx(full_bar(stage), box_bytes);
-            tma_load_3d(ring + stage * A_STAGE, &map_a, full_bar(stage), kb * BK, row, 0);
+            tma_load_3d(ring + stage * p.stage_bytes, &map_a, full_bar(stage), kb * BK, row, 0);
             if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
           }
         }
@@ -285,7 +289,7 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
           for (int kb = 0; kb < KB; ++kb) {
             if (!mbar_wait(full_bar(stage), phase, s_abort, p.err, 54)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t sa = ring + stage * A_STAGE;
+            const uint32_t sa = ring + stage * p.stage_bytes;
             const uint32_t sb = base + (uint32_t)kb * R_TILE;
 #pragma unroll
             for (int ks = 0; ks < BK / 16; ++ks)
@@ -445,7 +449,7 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
 // ---- host side ---------------------------------------------------------------------------
 struct TcGeometry {
   int nHS, nRG, MT, RB, stages;
-  size_t smem;
+  size_t ring, smem;
 };
 
 // Shapes this path takes: bf16, H a multiple of 64 up to 1024 (the resident slice of R and a
@@ -463,10 +467,6 @@ bool tc_geometry_for(int N, int H, bool fwd, int sms, TcGeometry* g) {
   const size_t r_bytes = (size_t)(K / BK) * (fwd ? 48 : 16) * 128;
   const size_t fixed = 1024 /*alignment*/ + r_bytes + 1024 /*barriers, bias*/;
   if (fixed + 2 * (size_t)A_STAGE > (size_t)MAX_SMEM) return false;
-  int stages = (int)(((size_t)MAX_SMEM - fixed) / A_STAGE);
-  if (stages > 8) stages = 8;
-  g->stages = stages;
-  g->smem = fixed + (size_t)stages * A_STAGE;
   g->nHS = H / UC;
   const int groups_max = sms / g->nHS;
   if (groups_max < 1) return false;
@@ -479,6 +479,14 @@ bool tc_geometry_for(int N, int H, bool fwd, int sms, TcGeometry* g) {
     g->RB = rb;
     g->MT = mt;
     g->nRG = ceil_div(tiles, mt);
+    // ring: as many stages of one k-block (rb rows x 128 bytes) as shared memory holds, up
+    // to 16; bytes in flight are what the streaming rate of a step is made of
+    const size_t stage = (size_t)rb * 128, pad = A_STAGE - stage;
+    int stages = (int)(((size_t)MAX_SMEM - fixed - pad) / stage);
+    if (stages > 16) stages = 16;
+    g->stages = stages;
+    g->ring = stages * stage + pad;
+    g->smem = fixed + g->ring;
     return true;
   }
   return false;
@@ -563,6 +571,7 @@ int gru_forward_tc(const GruFwd& a, cudaStream_t s) {
   const bool zo = a.zoneout_prob != 0.0f && a.zoneout_mask != nullptr;
   TcParams p{};
   p.T = a.T; p.N = a.N; p.H = a.H; p.nHS = g.nHS; p.MT = g.MT; p.RB = g.RB;
+  p.stage_bytes = g.RB * 128; p.ring_bytes = (int)g.ring;
   p.training = a.training; p.has_zoneout = zo ? 1 : 0; p.zoneout_prob = a.zoneout_prob;
   p.R = (const bf16*)a.R; p.bx = (const bf16*)a.bx; p.br = (const bf16*)a.br;
   p.Wx = (const bf16*)a.tmp_Wx; p.mask = (const bf16*)a.zoneout_mask;
@@ -594,6 +603,7 @@ int gru_backward_tc(const GruBwd& a, float* dh_carry, cudaStream_t s) {
     return HASTE_B200_ERR_UNSUPPORTED;
   TcParams p{};
   p.T = a.T; p.N = a.N; p.H = a.H; p.nHS = g.nHS; p.MT = g.MT; p.RB = g.RB;
+  p.stage_bytes = g.RB * 128; p.ring_bytes = (int)g.ring;
   p.has_zoneout = a.zoneout_mask ? 1 : 0; p.r_transposed = a.transposed_inputs;
   p.R = (const bf16*)a.R; p.mask = (const bf16*)a.zoneout_mask;
   p.h = (bf16*)const_cast<void*>(a.h); p.v = (bf16*)const_cast<void*>(a.v);

@@ -94,6 +94,21 @@ template <int SPLIT> __device__ __forceinline__ uint32_t hword_encode(float x, u
 template <int SPLIT> __device__ __forceinline__ bool hword_ready(uint32_t w, uint32_t tag) {
   return SPLIT == 2 ? fword_ready(w, tag) : xword_ready(w, tag);
 }
+// Gate functions of the LayerNorm cells.  With fp32 storage the accurate expf / tanhf: three
+// normalisations per step amplify a relative error of 1e-6 (the ex2.approx-based fast forms)
+// a hundredfold over a few dozen steps, which is most of the distance between these kernels
+// and the reference's float32 path on the 3-layer bidirectional configuration.  bf16 storage
+// keeps the fast forms (its bar is 2e-2).
+template <int SPLIT> __device__ __forceinline__ float ln_sigmoid(float x) {
+  return SPLIT == 2 ? 1.0f / (1.0f + expf(-x)) : sigmoid_fast(x);
+}
+template <int SPLIT> __device__ __forceinline__ float ln_tanh(float x) {
+  if (SPLIT != 2) return tanh_fast(x);
+  // 1 - 2 / (1 + e^{2x}) with the accurate expf and a true division: absolute error ~1e-7
+  const float e = expf(2.0f * fminf(fmaxf(x, -15.0f), 15.0f));
+  return 1.0f - 2.0f / (1.0f + e);
+}
+
 // x = p[0] + p[1] + p[2], each the bf16 rounding of what the previous ones left.
 __device__ __forceinline__ void split3_bf16(float x, float (&p)[3]) {
   p[0] = __bfloat162float(__float2bfloat16_rn(x));
@@ -503,10 +518,10 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
   #pragma unroll
           for (int g = 0; g < G; ++g)
             pre[g] = (rh[mt][g] - mean1) * inv1 * g1[g] + wxr[mt][g] + bias[g];
-          const float i = sigmoid_fast(pre[0]);
-          const float gg = tanh_fast(pre[1]);
-          const float f = sigmoid_fast(pre[2]);
-          const float o = sigmoid_fast(pre[G - 1]);
+          const float i = ln_sigmoid<SPLIT>(pre[0]);
+          const float gg = ln_tanh<SPLIT>(pre[1]);
+          const float f = ln_sigmoid<SPLIT>(pre[2]);
+          const float o = ln_sigmoid<SPLIT>(pre[G - 1]);
           const float c_new = f * c_reg[mt] + i * gg;
           og[mt] = o;
           cnew[mt] = c_new;
@@ -539,7 +554,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
             *reinterpret_cast<volatile int*>(&s_abort) = 1;
           chan_combine(sa, sb, ul, p.nHS, H, U, mean3, inv3);
           const float c_norm = (cnew[mt] - mean3) * inv3 * gh + bh;
-          float h_new = og[mt] * tanh_fast(c_norm);
+          float h_new = og[mt] * ln_tanh<SPLIT>(c_norm);
           if (p.has_zoneout)
             h_new = p.training ? zoneout<true>(h_new, h_reg[mt], p.zoneout_prob, mk[mt])
                                : zoneout<false>(h_new, h_reg[mt], p.zoneout_prob, mk[mt]);
@@ -575,10 +590,10 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
           float rn[G];
   #pragma unroll
           for (int g = 0; g < G; ++g) rn[g] = (rh[mt][g] - mean1) * inv1 * g1[g] + bias2[g];
-          const float z = sigmoid_fast(wxr[mt][0] + bias[0] + rn[0]);
-          const float r = sigmoid_fast(wxr[mt][1] + bias[1] + rn[1]);
+          const float z = ln_sigmoid<SPLIT>(wxr[mt][0] + bias[0] + rn[0]);
+          const float r = ln_sigmoid<SPLIT>(wxr[mt][1] + bias[1] + rn[1]);
           const float qg = rn[2];
-          const float gg = tanh_fast(wxr[mt][2] + bias[2] + r * qg);
+          const float gg = ln_tanh<SPLIT>(wxr[mt][2] + bias[2] + r * qg);
           float h_new = z * h_reg[mt] + (1.0f - z) * gg;
           if (p.has_zoneout)
             h_new = p.training ? zoneout<true>(h_new, h_reg[mt], p.zoneout_prob, mk[mt])
@@ -848,7 +863,7 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
           }
           dh_c[mt] = keep;
           const float o = gv[mt][3];
-          const float c_tanh = tanh_fast(cnv[mt]);
+          const float c_tanh = ln_tanh<SPLIT>(cnv[mt]);
           d_o[mt] = d_sigmoid(o) * (c_tanh * dh_total);
           const float dcn_ = d_tanh(c_tanh) * (o * dh_total);  // gradient w.r.t. LayerNorm(c')
           acc_gh += cx3[mt] * inv3[mt] * dcn_;
