@@ -276,6 +276,9 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
       uint32_t acc_phase[2] = {0, 0};
       int n_acc = 0;
       bool ok = true;
+      const uint64_t a_desc0 = smem_desc(ring, 16, 1024);
+      const uint64_t b_desc0 = smem_desc(base, 16, 1024);
+      const uint64_t a_stage_inc = (uint64_t)(p.stage_bytes >> 4);
       for (int it = 0; it < p.T && ok; ++it) {
         if (!FWD && it == 0) continue;
         for (int mt = 0; mt < p.MT && ok; ++mt) {
@@ -286,16 +289,22 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
           acc_phase[acc] ^= 1u;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+          // Descriptors differ only in their 14-bit start-address field (bytes >> 4): one add
+          // per MMA instead of rebuilding them - with N = 16 or 48 an instruction is a few
+          // dozen cycles of tensor work, so the issuing thread's own instruction count is
+          // what bounds the k-loop.
+          uint64_t bd = b_desc0;
+#pragma unroll 1
           for (int kb = 0; kb < KB; ++kb) {
             if (!mbar_wait(full_bar(stage), phase, s_abort, p.err, 54)) { ok = false; break; }
             tc_fence_after();
-            const uint32_t sa = ring + stage * p.stage_bytes;
-            const uint32_t sb = base + (uint32_t)kb * R_TILE;
-#pragma unroll
-            for (int ks = 0; ks < BK / 16; ++ks)
-              tc_mma_bf16(d_tmem, smem_desc(sa + ks * 32, 16, 1024), smem_desc(sb + ks * 32, 16, 1024),
-                          idesc, (kb | ks) ? 1u : 0u);
+            const uint64_t ad = a_desc0 + (uint64_t)stage * a_stage_inc;
+            tc_mma_bf16(d_tmem, ad, bd, idesc, kb ? 1u : 0u);
+            tc_mma_bf16(d_tmem, ad + 2, bd + 2, idesc, 1u);
+            tc_mma_bf16(d_tmem, ad + 4, bd + 4, idesc, 1u);
+            tc_mma_bf16(d_tmem, ad + 6, bd + 6, idesc, 1u);
             tc_commit(empty_bar(stage));
+            bd += R_TILE >> 4;
             if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
           }
           if (ok) tc_commit(accf_bar(acc));
