@@ -431,28 +431,48 @@ __global__ void __launch_bounds__(THREADS, 1) ln_fwd_kernel(const LnFwdParams p)
         float acc[NT][4];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        // fp32 storage, six products in three passes over the K range, smallest terms first.
+        // The tensor core adds each product into the fp32 accumulator with truncation (about
+        // half an ulp of the accumulator, always the same way); with the passes ordered like
+        // this only the last pass's KSW accumulations happen at the full magnitude of the
+        // result, instead of all 6 * KSW of them.
+        if (SPLIT == 2) {
 #pragma unroll
-        for (int ks = 0; ks < (HB_DBG(p, 2) ? 0 : KSW); ++ks) {
-          const int row = lane & 15;
-          const int kcol = warp * KW + ks * 16 + (lane >> 4) * 8;
-          uint32_t a0[4], a1[4], a2[4];
-          ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), a0);
-          if (SPLIT == 2) {
-            ldmatrix_x4(smem_u32(a_hi + a_plane + (size_t)row * AROW + kcol), a1);
-            ldmatrix_x4(smem_u32(a_hi + (PA - 1) * a_plane + (size_t)row * AROW + kcol), a2);
-          }
+          for (int pass = 0; pass < (HB_DBG(p, 2) ? 0 : 3); ++pass) {
 #pragma unroll
-          for (int nt = 0; nt < NT; ++nt) {
-            if (SPLIT == 2) {
-              // six products, smallest first: everything above 2^-24 of the result
-              const uint32_t* bq = b2f + ((((size_t)warp * NT + nt) * KSW + ks) * 2) * 32 + lane;
-              mma_bf16(acc[nt], a0, bq[0], bq[32]);
-              mma_bf16(acc[nt], a2, rf[0][nt][ks][0], rf[0][nt][ks][1]);
-              mma_bf16(acc[nt], a1, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
-              mma_bf16(acc[nt], a0, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
-              mma_bf16(acc[nt], a1, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+            for (int ks = 0; ks < KSW; ++ks) {
+              const int row = lane & 15;
+              const int kcol = warp * KW + ks * 16 + (lane >> 4) * 8;
+              uint32_t a0[4], a1[4], a2[4];
+              ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), a0);
+              if (pass < 2) ldmatrix_x4(smem_u32(a_hi + a_plane + (size_t)row * AROW + kcol), a1);
+              if (pass == 0)
+                ldmatrix_x4(smem_u32(a_hi + (PA - 1) * a_plane + (size_t)row * AROW + kcol), a2);
+#pragma unroll
+              for (int nt = 0; nt < NT; ++nt) {
+                if (pass == 0) {  // terms of relative size 2^-16
+                  const uint32_t* bq = b2f + ((((size_t)warp * NT + nt) * KSW + ks) * 2) * 32 + lane;
+                  mma_bf16(acc[nt], a0, bq[0], bq[32]);
+                  mma_bf16(acc[nt], a2, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+                  mma_bf16(acc[nt], a1, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+                } else if (pass == 1) {  // 2^-8
+                  mma_bf16(acc[nt], a0, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+                  mma_bf16(acc[nt], a1, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+                } else {
+                  mma_bf16(acc[nt], a0, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+                }
+              }
             }
-            mma_bf16(acc[nt], a0, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+          }
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < (HB_DBG(p, 2) ? 0 : KSW); ++ks) {
+            const int row = lane & 15;
+            const int kcol = warp * KW + ks * 16 + (lane >> 4) * 8;
+            uint32_t a0[4];
+            ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), a0);
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) mma_bf16(acc[nt], a0, rf[0][nt][ks][0], rf[0][nt][ks][1]);
           }
         }
         float* pb = part + (size_t)pbuf * WARPS * 16 * PROW;
@@ -1025,29 +1045,44 @@ __global__ void __launch_bounds__(THREADS, 1) ln_bwd_kernel(const LnBwdParams p)
         float acc[NTW][4];
 #pragma unroll
         for (int nt = 0; nt < NTW; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+        if (SPLIT == 2) {
+          // three passes, smallest terms first (see the forward kernel)
 #pragma unroll
-        for (int ks = 0; ks < (HB_DBG(p, 2) ? 0 : KS); ++ks) {
-          const int row = mt * 16 + (lane & 15);
-          const int kcol = ks * 16 + (lane >> 4) * 8;
-          uint32_t a0[4], a1[4], a2[4];
-          ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), a0);
-          if (SPLIT == 2) {
-            ldmatrix_x4(smem_u32(a_hi + a_plane + (size_t)row * AROW + kcol), a1);
-            ldmatrix_x4(smem_u32(a_hi + (PA - 1) * a_plane + (size_t)row * AROW + kcol), a2);
+          for (int pass = (HB_DBG(p, 8) ? 1 : 0); pass < (HB_DBG(p, 2) ? 0 : 3); ++pass) {
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks) {
+              const int row = mt * 16 + (lane & 15);
+              const int kcol = ks * 16 + (lane >> 4) * 8;
+              uint32_t a0[4], a1[4], a2[4];
+              ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), a0);
+              if (pass < 2) ldmatrix_x4(smem_u32(a_hi + a_plane + (size_t)row * AROW + kcol), a1);
+              if (pass == 0)
+                ldmatrix_x4(smem_u32(a_hi + (PA - 1) * a_plane + (size_t)row * AROW + kcol), a2);
+#pragma unroll
+              for (int nt = 0; nt < NTW; ++nt) {
+                if (pass == 0) {
+                  const uint32_t* bq = b2f + ((((size_t)warp * NTW + nt) * KS + ks) * 2) * 32 + lane;
+                  mma_bf16(acc[nt], a0, bq[0], bq[32]);
+                  mma_bf16(acc[nt], a2, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+                  mma_bf16(acc[nt], a1, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+                } else if (pass == 1) {
+                  mma_bf16(acc[nt], a0, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
+                  mma_bf16(acc[nt], a1, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+                } else {
+                  mma_bf16(acc[nt], a0, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+                }
+              }
+            }
           }
+        } else {
 #pragma unroll
-          for (int nt = 0; nt < NTW; ++nt) {
-            if (SPLIT == 2 && !HB_DBG(p, 8)) {
-              const uint32_t* bq = b2f + ((((size_t)warp * NTW + nt) * KS + ks) * 2) * 32 + lane;
-              mma_bf16(acc[nt], a0, bq[0], bq[32]);
-              mma_bf16(acc[nt], a2, rf[0][nt][ks][0], rf[0][nt][ks][1]);
-              mma_bf16(acc[nt], a1, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
-            }
-            if (SPLIT == 2) {
-              mma_bf16(acc[nt], a0, rf[SPLIT - 1][nt][ks][0], rf[SPLIT - 1][nt][ks][1]);
-              mma_bf16(acc[nt], a1, rf[0][nt][ks][0], rf[0][nt][ks][1]);
-            }
-            mma_bf16(acc[nt], a0, rf[0][nt][ks][0], rf[0][nt][ks][1]);
+          for (int ks = 0; ks < (HB_DBG(p, 2) ? 0 : KS); ++ks) {
+            const int row = mt * 16 + (lane & 15);
+            const int kcol = ks * 16 + (lane >> 4) * 8;
+            uint32_t a0[4];
+            ldmatrix_x4(smem_u32(a_hi + (size_t)row * AROW + kcol), a0);
+#pragma unroll
+            for (int nt = 0; nt < NTW; ++nt) mma_bf16(acc[nt], a0, rf[0][nt][ks][0], rf[0][nt][ks][1]);
           }
         }
 #pragma unroll
