@@ -711,11 +711,15 @@ def run_config4(args):
                    concurrent_directions=not args.sequential_directions).to(dev).to(dtype)
     net.train()
     data_parallel.broadcast_parameters(net)
-    g = torch.Generator().manual_seed(99)
-    x_all = torch.randn(T, n_global, C, generator=g).to(dtype)
-    dy_all = torch.randn(T, n_global, 2 * H, generator=g).to(dtype)
-    x = data_parallel.shard(x_all, rank, world).to(dev).requires_grad_(True)
-    dy = data_parallel.shard(dy_all, rank, world).to(dev)
+    # the whole global batch is drawn on every rank's own GPU from the same seed (identical
+    # devices give identical values), then cut: no host-side generation of gigabytes
+    g = torch.Generator(device=dev).manual_seed(99)
+    x_all = torch.randn(T, n_global, C, generator=g, device=dev).to(dtype)
+    dy_all = torch.randn(T, n_global, 2 * H, generator=g, device=dev).to(dtype)
+    x = data_parallel.shard(x_all, rank, world).clone().requires_grad_(True)
+    dy = data_parallel.shard(dy_all, rank, world).clone()
+    if world > 1 and (rank != 0 or args.no_dp_parity):
+        del x_all, dy_all
     steps, warmup = args.steps, max(args.warmup, 3)
 
     def make_step(dp):
@@ -773,8 +777,8 @@ def run_config4(args):
     if world > 1 and rank == 0 and not args.no_dp_parity:
         for p in net.parameters():
             p.grad = None
-        xf = x_all.to(dev).requires_grad_(True)
-        net(xf).backward(dy_all.to(dev))
+        xf = x_all.requires_grad_(True)
+        net(xf).backward(dy_all)
         torch.cuda.synchronize()
         dp_err = 0.0
         for k, v in net.named_parameters():
