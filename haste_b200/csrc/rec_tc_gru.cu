@@ -29,7 +29,9 @@
 //   process error word are set, all roles leave their loops, tensor memory is released and
 //   the host reports HASTE_B200_ERR_TIMEOUT.
 //
-// Warp roles (192 threads): warp 0 TMA producer, warp 1 MMA issuer, warps 2-5 epilogue.
+// Warp roles: warp 0 TMA producer (four lanes issue), warps 1..NI MMA issuers (a tcgen05.mma
+// of this shape occupies its issuing thread for ~65 cycles, 2-3x its tensor-pipe time, so NI
+// threads issue the k-blocks in turn, each into its own accumulator), then four epilogue warps.
 // Replaces the per-step cuBLAS call + pointwise kernel of the reference
 // (lib/gru_forward_gpu.cu.cc:214-308,345-363, lib/gru_backward_gpu.cu.cc:252-320) for
 // bf16 batches of about a hundred rows and more; math as in lib/gru_forward_gpu.cu.cc:27-85
@@ -41,14 +43,25 @@ namespace hb {
 namespace {
 
 using namespace tc;
-using rec::sigmoid_fast;
-using rec::tanh_fast;
 typedef __nv_bfloat16 bf16;
+
+// Gate functions of this bf16-only path: one MUFU.TANH each (relative error 2^-11, a
+// fraction of a bf16 ulp; the parity bar of bf16 storage is 2e-2).
+__device__ __forceinline__ float tanh_fast(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float sigmoid_fast(float x) { return fmaf(0.5f, tanh_fast(0.5f * x), 0.5f); }
 
 constexpr int UC = 16;                 // hidden units per CTA
 constexpr int BK = 64;                 // K elements per TMA box / swizzle row (128 bytes)
 constexpr int A_STAGE = 128 * BK * 2;  // one streamed stage: 128 rows x 128 bytes
-constexpr int TC_THREADS = 192;
+#ifndef HB_TC_NI
+#define HB_TC_NI 4
+#endif
+constexpr int NI = HB_TC_NI;           // MMA-issuing warps (k-blocks go to them in turn)
+constexpr int TC_THREADS = 32 * (1 + NI + 4);  // warp 0 TMA, warps 1..NI MMA, then 4 epilogue warps
 constexpr int MAX_SMEM = 227 * 1024;
 
 struct TcParams {
@@ -70,7 +83,20 @@ struct TcParams {
   unsigned int* cnt;   // [row tiles] arrival counters, zeroed before launch
   int* abort_flag;     // device-global, zeroed before launch
   int* err;            // process error word
+#ifdef HASTE_B200_TIMING_EXPERIMENTS
+  long long* stamps;   // [T][16] clock64 stamps of CTA 0, tile 0 (timing-experiment builds only)
+#endif
 };
+
+#ifdef HASTE_B200_TIMING_EXPERIMENTS
+#define HB_STAMP(p, it, mt, slot)                                            \
+  do {                                                                       \
+    if ((p).stamps && blockIdx.x == 0 && (mt) == 0)                          \
+      (p).stamps[(size_t)(it) * 16 + (slot)] = clock64();                     \
+  } while (0)
+#else
+#define HB_STAMP(p, it, mt, slot) do {} while (0)
+#endif
 
 __device__ __forceinline__ unsigned int ld_acquire_u32(const unsigned int* p) {
   unsigned int v;
@@ -135,6 +161,33 @@ __device__ __forceinline__ void st16(bf16* p, const float (&x)[16]) {
   *reinterpret_cast<uint4*>(p + 8) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
+// 8 consecutive bf16 as one 16-byte load, and element u of such a group as a float
+__device__ __forceinline__ uint4 ldq(const bf16* p) { return *reinterpret_cast<const uint4*>(p); }
+__device__ __forceinline__ float bfq(const uint4& q, int u) {
+  const uint32_t w = (u >> 1) == 0 ? q.x : ((u >> 1) == 1 ? q.y : ((u >> 1) == 2 ? q.z : q.w));
+  return (u & 1) ? __uint_as_float(w & 0xFFFF0000u) : __uint_as_float(w << 16);
+}
+
+// 8 consecutive bf16 (16 bytes, 16-byte aligned) <-> floats
+__device__ __forceinline__ void ld8(const bf16* p, float (&x)[8]) {
+  const uint4 a = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {a.x, a.y, a.z, a.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    x[2 * i] = __uint_as_float(w[i] << 16);
+    x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+  }
+}
+__device__ __forceinline__ void st8(bf16* p, const float (&x)[8]) {
+  uint32_t w[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    __nv_bfloat162 t2 = __floats2bfloat162_rn(x[2 * i], x[2 * i + 1]);
+    w[i] = *reinterpret_cast<uint32_t*>(&t2);
+  }
+  *reinterpret_cast<uint4*>(p) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
 // Byte offset of element (row n, k) inside one K-major, 128-byte-swizzled k-block tile
 // (rows of 64 bf16 = 128 bytes; 16-byte chunk c of row n sits at chunk c ^ (n & 7)).
 __device__ __forceinline__ uint32_t swz_off(int n, int kk) {
@@ -170,15 +223,16 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
   const int hs = blockIdx.x % p.nHS, rg = blockIdx.x / p.nHS;
   const int u0 = hs * UC;
   constexpr int ACC_COLS = NB <= 32 ? 32 : 64;   // tensor-memory columns per accumulator
-  constexpr uint32_t TMEM_COLS = 2 * ACC_COLS;
+  constexpr uint32_t TMEM_COLS = 2 * NI * ACC_COLS;  // two buffers x one accumulator per issuer
 
   if (threadIdx.x == 0) {
+    asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
     for (int s = 0; s < stages; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int a = 0; a < 2; ++a) {
-      mbar_init(accf_bar(a), 1);
+      mbar_init(accf_bar(a), NI);
       mbar_init(acce_bar(a), 128);
     }
     *s_abort = 0;
@@ -242,8 +296,13 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
+    // PL lanes issue the k-blocks of a tile in turn (lane l takes k-blocks l, l + PL, ...): a
+    // cp.async.bulk.tensor holds its issuing thread for about 0.1 us, which would otherwise
+    // be the rate of the whole ring.
+    constexpr int PL = 4;
+    constexpr unsigned PMASK = (1u << PL) - 1u;
+    if (lane < PL) {
+      uint32_t g0 = 0;  // k-blocks issued before this tile (the same in every lane)
       bool ok = true;
       const uint32_t box_bytes = (uint32_t)p.RB * 128u;
       for (int it = 0; it < p.T && ok; ++it) {
@@ -253,26 +312,33 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
           if (tile >= tiles_total) break;
           // forward step it reads h_it (published it times); backward iteration it reads the
           // dq of iteration it-1 (published it times as well)
-          if (it > 0 && !wait_count(p.cnt + tile, arrivals * (unsigned int)it, s_abort, p, 51,
-                                    it, tile)) { ok = false; break; }
+          if (it > 0 && lane == 0)
+            ok = wait_count(p.cnt + tile, arrivals * (unsigned int)it, s_abort, p, 51, it, tile);
+          __syncwarp(PMASK);  // lane 0's acquire is ordered before the other lanes' loads
+          HB_STAMP(p, it, mt, 0);  // the step's operand is published
           fence_proxy_async_all();
           const int trow = FWD ? it : (p.T - it);  // time slot of the streamed tensor
           const int row = trow * N + tile * p.RB;
-          for (int kb = 0; kb < KB; ++kb) {
+          for (int kb = lane; kb < KB && ok; kb += PL) {
+            const uint32_t g = g0 + (uint32_t)kb;
+            const uint32_t stage = g % (uint32_t)stages, phase = (g / (uint32_t)stages) & 1u;
             if (!mbar_wait(empty_bar(stage), phase ^ 1u, s_abort, p.err, 52)) { ok = false; break; }
             mbar_expect_tx(full_bar(stage), box_bytes);
             tma_load_3d(ring + stage * p.stage_bytes, &map_a, full_bar(stage), kb * BK, row, 0);
-            if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
           }
+          g0 += (uint32_t)KB;
+          ok = __all_sync(PMASK, ok);  // all producer lanes leave together
+          HB_STAMP(p, it, mt, 1);  // all TMA loads of the tile issued
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
+  } else if (warp <= NI) {
+    // ------------------------------------------------------------------ MMA issuers
     if (lane == 0) {
+      const int iss = warp - 1;  // this issuer takes k-blocks iss, iss + NI, ...
       const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NB >> 3) << 17) |
                              ((uint32_t)(128 >> 4) << 24);
-      uint32_t stage = 0, phase = 0;
+      uint32_t g0 = 0;  // k-blocks consumed before this tile
       uint32_t acc_phase[2] = {0, 0};
       int n_acc = 0;
       bool ok = true;
@@ -288,25 +354,26 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
           if (!mbar_wait(acce_bar(acc), acc_phase[acc] ^ 1u, s_abort, p.err, 53)) { ok = false; break; }
           acc_phase[acc] ^= 1u;
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + acc * ACC_COLS;
+          const uint32_t d_tmem = tmem_base + (acc * NI + iss) * ACC_COLS;
           // Descriptors differ only in their 14-bit start-address field (bytes >> 4): one add
-          // per MMA instead of rebuilding them - with N = 16 or 48 an instruction is a few
-          // dozen cycles of tensor work, so the issuing thread's own instruction count is
-          // what bounds the k-loop.
-          uint64_t bd = b_desc0;
+          // per MMA instead of rebuilding them.
 #pragma unroll 1
-          for (int kb = 0; kb < KB; ++kb) {
+          for (int kb = iss; kb < KB; kb += NI) {
+            const uint32_t g = g0 + (uint32_t)kb;
+            const uint32_t stage = g % (uint32_t)stages, phase = (g / (uint32_t)stages) & 1u;
             if (!mbar_wait(full_bar(stage), phase, s_abort, p.err, 54)) { ok = false; break; }
             tc_fence_after();
+            if (kb == 0) HB_STAMP(p, it, mt, 2);  // first k-block has landed
             const uint64_t ad = a_desc0 + (uint64_t)stage * a_stage_inc;
-            tc_mma_bf16(d_tmem, ad, bd, idesc, kb ? 1u : 0u);
+            const uint64_t bd = b_desc0 + (uint64_t)kb * (R_TILE >> 4);
+            tc_mma_bf16(d_tmem, ad, bd, idesc, kb >= NI ? 1u : 0u);
             tc_mma_bf16(d_tmem, ad + 2, bd + 2, idesc, 1u);
             tc_mma_bf16(d_tmem, ad + 4, bd + 4, idesc, 1u);
             tc_mma_bf16(d_tmem, ad + 6, bd + 6, idesc, 1u);
             tc_commit(empty_bar(stage));
-            bd += R_TILE >> 4;
-            if (++stage == (uint32_t)stages) { stage = 0; phase ^= 1u; }
           }
+          g0 += (uint32_t)KB;
+          if (iss == 0) HB_STAMP(p, it, mt, 3);  // last MMA issued
           if (ok) tc_commit(accf_bar(acc));
         }
       }
@@ -328,118 +395,161 @@ gru_tc_kernel(const __grid_constant__ CUtensorMap map_a, const TcParams p, const
         const bool valid = r < p.RB && n < N;
         const bool have_acc = FWD || it > 0;
         const long long o0 = (long long)n * H + u0;
-        // ---- inputs that do not depend on the recurrence
-        float in0[16], in1[16], in2[16], in3[16], hp[16], mk[16], dhn[16], carry[16];
+        // The 16 units are handled in two halves of 8 and the step inputs stay packed (bf16
+        // pairs) until they are used, so that the live state of a thread stays within its
+        // share of the register file (nine warps per CTA).
+        // ---- inputs that do not depend on the recurrence: issued before the wait below
+        uint4 in0[2], in1[2], in2[2], in3[2], hp[2], mk[2], dhn[2];
+        float carry[2][8];
         if (valid) {
-          if (FWD) {
-            const bf16* wx = p.Wx + ((long long)t * N + n) * 3 * H + u0;
-            ld16(wx, in0);
-            ld16(wx + H, in1);
-            ld16(wx + 2 * H, in2);
-            ld16(p.h + (long long)t * NH + o0, hp);
-            if (p.has_zoneout && p.training) ld16(p.mask + (long long)t * NH + o0, mk);
-          } else {
-            const bf16* vt = p.v + ((long long)t * N + n) * 4 * H + u0;
-            ld16(vt, in0);
-            ld16(vt + H, in1);
-            ld16(vt + 2 * H, in2);
-            ld16(vt + 3 * H, in3);
-            ld16(p.h + (long long)t * NH + o0, hp);
-            ld16(p.dh_new + (long long)(t + 1) * NH + o0, dhn);
-            if (p.has_zoneout) ld16(p.mask + (long long)t * NH + o0, mk);
-            const float4* cp = reinterpret_cast<const float4*>(p.dh_carry + o0);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float4 f = cp[i];
-              carry[4 * i] = f.x; carry[4 * i + 1] = f.y; carry[4 * i + 2] = f.z; carry[4 * i + 3] = f.w;
+          for (int hf = 0; hf < 2; ++hf) {
+            const int uo = hf * 8;
+            if (FWD) {
+              const bf16* wx = p.Wx + ((long long)t * N + n) * 3 * H + u0 + uo;
+              in0[hf] = ldq(wx);
+              in1[hf] = ldq(wx + H);
+              in2[hf] = ldq(wx + 2 * H);
+              hp[hf] = ldq(p.h + (long long)t * NH + o0 + uo);
+              if (p.has_zoneout && p.training) mk[hf] = ldq(p.mask + (long long)t * NH + o0 + uo);
+            } else {
+              const bf16* vt = p.v + ((long long)t * N + n) * 4 * H + u0 + uo;
+              in0[hf] = ldq(vt);
+              in1[hf] = ldq(vt + H);
+              in2[hf] = ldq(vt + 2 * H);
+              in3[hf] = ldq(vt + 3 * H);
+              hp[hf] = ldq(p.h + (long long)t * NH + o0 + uo);
+              dhn[hf] = ldq(p.dh_new + (long long)(t + 1) * NH + o0 + uo);
+              if (p.has_zoneout) mk[hf] = ldq(p.mask + (long long)t * NH + o0 + uo);
+              const float4* cp = reinterpret_cast<const float4*>(p.dh_carry + o0 + uo);
+              const float4 f0 = cp[0], f1 = cp[1];
+              carry[hf][0] = f0.x; carry[hf][1] = f0.y; carry[hf][2] = f0.z; carry[hf][3] = f0.w;
+              carry[hf][4] = f1.x; carry[hf][5] = f1.y; carry[hf][6] = f1.z; carry[hf][7] = f1.w;
             }
           }
         }
-        // ---- the step product from tensor memory
-        uint32_t a0[16], a1[16], a2[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) a0[i] = a1[i] = a2[i] = 0u;
+        // ---- wait for the step product
+        int acc = 0;
         if (have_acc) {
-          const int acc = n_acc & 1;
+          acc = n_acc & 1;
           ++n_acc;
           bool got = mbar_wait(accf_bar(acc), acc_phase[acc], s_abort, p.err, 55);
           got = __all_sync(0xffffffffu, got);
           if (!got) { ok = false; break; }
           acc_phase[acc] ^= 1u;
           tc_fence_after();
-          const uint32_t taddr = tmem_base + acc * ACC_COLS + ((uint32_t)(quad * 32) << 16);
-          tc_ld16(taddr, a0);
-          if (FWD) {
-            tc_ld16(taddr + 16, a1);
-            tc_ld16(taddr + 32, a2);
-          }
-          tc_wait_ld();
-          tc_fence_before();
-          mbar_arrive(acce_bar(acc));
+          if (warp == NI + 1 && lane == 0) HB_STAMP(p, it, mt, 4);  // accumulator complete
         }
-        // ---- gate math; first the stores the next step streams (h / dq), then the publish,
-        // then the stores nothing on the chain waits for (gate cache, dp, carry)
-        float o0v[16], o1v[16], o2v[16], o3v[16];  // fwd: z, r, g, q   bwd: dp_z, dp_r, dp_g, dq_g
-        if (valid) {
-          if (FWD) {
-            float hn[16];
+        const uint32_t taddr = tmem_base + acc * NI * ACC_COLS + ((uint32_t)(quad * 32) << 16);
 #pragma unroll
-            for (int u = 0; u < 16; ++u) {
-              const float z = sigmoid_fast(in0[u] + __uint_as_float(a0[u]) + s_bias[u] + s_bias[48 + u]);
-              const float rr = sigmoid_fast(in1[u] + __uint_as_float(a1[u]) + s_bias[16 + u] + s_bias[64 + u]);
-              const float qg = __uint_as_float(a2[u]) + s_bias[80 + u];
-              const float g = tanh_fast(in2[u] + rr * qg + s_bias[32 + u]);
-              float x = z * hp[u] + (1.0f - z) * g;
-              if (p.has_zoneout)
-                x = p.training ? zoneout<true>(x, hp[u], p.zoneout_prob, mk[u])
-                               : zoneout<false>(x, hp[u], p.zoneout_prob, 0.f);
-              hn[u] = x; o0v[u] = z; o1v[u] = rr; o2v[u] = g; o3v[u] = qg;
-            }
-            st16(p.h + (long long)(t + 1) * NH + o0, hn);
-          } else {
+        for (int hf = 0; hf < 2; ++hf) {
+          const int uo = hf * 8;
+          // this half's columns of the accumulators (one per issuer), summed
+          float s0[8], s1[8], s2[8];
 #pragma unroll
-            for (int u = 0; u < 16; ++u) {
-              const float z = in0[u], rr = in1[u], g = in2[u], qg = in3[u];
-              float dh_total = dhn[u] + carry[u] + __uint_as_float(a0[u]);
-              float keep = 0.f;
-              if (p.has_zoneout) {
-                keep = (1.0f - mk[u]) * dh_total;
-                dh_total = mk[u] * dh_total;
+          for (int i = 0; i < 8; ++i) s0[i] = s1[i] = s2[i] = 0.f;
+          if (have_acc) {
+            // the issuers' accumulators, GRP of them per wait (all loads of a group in flight)
+            constexpr int GRP = FWD ? 2 : NI;
+#pragma unroll
+            for (int g0 = 0; g0 < NI; g0 += GRP) {
+              uint32_t b0[GRP][8], b1[GRP][8], b2[GRP][8];
+#pragma unroll
+              for (int k = 0; k < GRP; ++k) {
+                const int i2 = g0 + k;
+                if (i2 < NI && KB > i2) {
+                  tc_ld8(taddr + i2 * ACC_COLS + uo, b0[k]);
+                  if (FWD) {
+                    tc_ld8(taddr + i2 * ACC_COLS + 16 + uo, b1[k]);
+                    tc_ld8(taddr + i2 * ACC_COLS + 32 + uo, b2[k]);
+                  }
+                }
               }
-              const float dg = (1.0f - z) * dh_total;
-              const float dz = (hp[u] - g) * dh_total;
-              const float dp_g = d_tanh(g) * dg;
-              o0v[u] = d_sigmoid(z) * dz;
-              o1v[u] = d_sigmoid(rr) * (dp_g * qg);
-              o2v[u] = dp_g;
-              o3v[u] = dp_g * rr;
-              carry[u] = keep + z * dh_total;
-            }
-            const long long w0 = ((long long)t * N + n) * 3 * H + u0;
-            st16(p.dq + w0, o0v); st16(p.dq + w0 + H, o1v); st16(p.dq + w0 + 2 * H, o3v);
-          }
-        }
-        // publish: the stores above become visible to the other CTAs' TMA loads, then the
-        // warp's arrival is counted (rows beyond the batch store nothing but still arrive)
-        fence_proxy_async_all();
-        __threadfence();
-        __syncwarp();
-        if (lane == 0) red_release_add(p.cnt + tile, 1u);
-        if (valid) {
-          if (FWD) {
-            if (p.training && p.v) {
-              bf16* vt = p.v + ((long long)t * N + n) * 4 * H + u0;
-              st16(vt, o0v); st16(vt + H, o1v); st16(vt + 2 * H, o2v); st16(vt + 3 * H, o3v);
-            }
-          } else {
-            const long long w0 = ((long long)t * N + n) * 3 * H + u0;
-            st16(p.dp + w0, o0v); st16(p.dp + w0 + H, o1v); st16(p.dp + w0 + 2 * H, o2v);
-            float4* cp = reinterpret_cast<float4*>(p.dh_carry + o0);
+              tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
-              cp[i] = make_float4(carry[4 * i], carry[4 * i + 1], carry[4 * i + 2], carry[4 * i + 3]);
+              for (int k = 0; k < GRP; ++k) {
+                const int i2 = g0 + k;
+                if (i2 < NI && KB > i2) {
+#pragma unroll
+                  for (int i = 0; i < 8; ++i) {
+                    s0[i] += __uint_as_float(b0[k][i]);
+                    if (FWD) {
+                      s1[i] += __uint_as_float(b1[k][i]);
+                      s2[i] += __uint_as_float(b2[k][i]);
+                    }
+                  }
+                }
+              }
+            }
+            if (hf == 1) {  // both halves are in registers: the accumulator buffer is free
+              tc_fence_before();
+              mbar_arrive(acce_bar(acc));
+              if (warp == NI + 1 && lane == 0) HB_STAMP(p, it, mt, 5);
+            }
+          }
+          if (valid) {
+            if (FWD) {
+              float hn[8], vz[8], vr[8], vg[8], vq[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const float hprev = bfq(hp[hf], u);
+                const float z = sigmoid_fast(bfq(in0[hf], u) + s0[u] + s_bias[uo + u] + s_bias[48 + uo + u]);
+                const float rr = sigmoid_fast(bfq(in1[hf], u) + s1[u] + s_bias[16 + uo + u] + s_bias[64 + uo + u]);
+                const float qg = s2[u] + s_bias[80 + uo + u];
+                const float g = tanh_fast(bfq(in2[hf], u) + rr * qg + s_bias[32 + uo + u]);
+                float x = z * hprev + (1.0f - z) * g;
+                if (p.has_zoneout)
+                  x = p.training ? zoneout<true>(x, hprev, p.zoneout_prob, bfq(mk[hf], u))
+                                 : zoneout<false>(x, hprev, p.zoneout_prob, 0.f);
+                hn[u] = x; vz[u] = z; vr[u] = rr; vg[u] = g; vq[u] = qg;
+              }
+              st8(p.h + (long long)(t + 1) * NH + o0 + uo, hn);  // the next step streams it
+              if (p.training && p.v) {
+                bf16* vt = p.v + ((long long)t * N + n) * 4 * H + u0 + uo;
+                st8(vt, vz); st8(vt + H, vr); st8(vt + 2 * H, vg); st8(vt + 3 * H, vq);
+              }
+            } else {
+              float dpz[8], dpr[8], dpg[8], dqg[8];
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const float z = bfq(in0[hf], u), rr = bfq(in1[hf], u), g = bfq(in2[hf], u),
+                            qg = bfq(in3[hf], u);
+                float dh_total = bfq(dhn[hf], u) + carry[hf][u] + s0[u];
+                float keep = 0.f;
+                if (p.has_zoneout) {
+                  const float m = bfq(mk[hf], u);
+                  keep = (1.0f - m) * dh_total;
+                  dh_total = m * dh_total;
+                }
+                const float dg = (1.0f - z) * dh_total;
+                const float dz = (bfq(hp[hf], u) - g) * dh_total;
+                const float dp_g = d_tanh(g) * dg;
+                dpz[u] = d_sigmoid(z) * dz;
+                dpr[u] = d_sigmoid(rr) * (dp_g * qg);
+                dpg[u] = dp_g;
+                dqg[u] = dp_g * rr;
+                carry[hf][u] = keep + z * dh_total;
+              }
+              const long long w0 = ((long long)t * N + n) * 3 * H + u0 + uo;
+              st8(p.dq + w0, dpz); st8(p.dq + w0 + H, dpr); st8(p.dq + w0 + 2 * H, dqg);  // streamed next
+              st8(p.dp + w0, dpz); st8(p.dp + w0 + H, dpr); st8(p.dp + w0 + 2 * H, dpg);
+              float4* cp = reinterpret_cast<float4*>(p.dh_carry + o0 + uo);
+              cp[0] = make_float4(carry[hf][0], carry[hf][1], carry[hf][2], carry[hf][3]);
+              cp[1] = make_float4(carry[hf][4], carry[hf][5], carry[hf][6], carry[hf][7]);
+            }
           }
         }
+        if (warp == NI + 1 && lane == 0) HB_STAMP(p, it, mt, 6);  // gate math done, h / dq stored
+        // ---- publish.  The warp barrier orders every lane's stores before lane 0's fence, the
+        // fence makes them visible GPU-wide (cumulatively), the release counts the warp's
+        // arrival; only lane 0 waits for the fence, the other lanes go on to the next step's
+        // loads.  Rows beyond the batch store nothing but still arrive.
+        __syncwarp();
+        if (lane == 0) {
+          __threadfence();
+          red_release_add(p.cnt + tile, 1u);
+        }
+        if (warp == NI + 1 && lane == 0) HB_STAMP(p, it, mt, 7);  // published
       }
     }
   }
@@ -544,6 +654,11 @@ int launch_tc(const CUtensorMap& map, TcParams& p, const TcGeometry& g, cudaStre
   return HASTE_B200_OK;
 }
 
+#ifdef HASTE_B200_TIMING_EXPERIMENTS
+long long* g_stamps = nullptr;
+int g_stamp_steps = 0;
+#endif
+
 // Zeroed scratch: abort flag + one arrival counter per row tile.
 int tc_scratch(int tiles, TcParams* p, cudaStream_t s) {
   const size_t bytes = Arena::pad(4096) + Arena::pad((size_t)tiles * 4);
@@ -557,6 +672,12 @@ int tc_scratch(int tiles, TcParams* p, cudaStream_t s) {
   p->cnt = cnt;
   p->err = device_error_word();
   HB_REQUIRE(p->err, "error word");
+#ifdef HASTE_B200_TIMING_EXPERIMENTS
+  if (!g_stamps) cudaMalloc(&g_stamps, (size_t)4096 * 16 * sizeof(long long));
+  cudaMemsetAsync(g_stamps, 0, (size_t)4096 * 16 * sizeof(long long), s);
+  p->stamps = p->T <= 4096 ? g_stamps : nullptr;
+  g_stamp_steps = p->T;
+#endif
   return HASTE_B200_OK;
 }
 
@@ -599,11 +720,6 @@ int gru_backward_tc(const GruBwd& a, float* dh_carry, cudaStream_t s) {
       recurrence_path() == HASTE_B200_PATH_NO_TENSOR_CORE || a.iterate ||
       !encode_fn() || !tc_geometry(a.N, a.H, false, &g, &budgeted))
     return HASTE_B200_ERR_UNSUPPORTED;
-  // On its own this kernel is slower than the register kernel / the step-wise path (see
-  // tc_geometry_for); it pays when it lets the two directions of a layer run at the same time,
-  // or when the caller asks for the persistent path explicitly.
-  if (!budgeted && recurrence_path() != HASTE_B200_PATH_PERSISTENT)
-    return HASTE_B200_ERR_UNSUPPORTED;
   if (!aligned16(a.R) || !aligned16(a.h) || !aligned16(a.v) || !aligned16(a.dh_new) ||
       !aligned16(a.dp) || !aligned16(a.dq) || !aligned16(a.zoneout_mask) || !aligned16(dh_carry))
     return HASTE_B200_ERR_UNSUPPORTED;
@@ -621,5 +737,17 @@ int gru_backward_tc(const GruBwd& a, float* dh_carry, cudaStream_t s) {
   HB_TRY(tc_scratch(ceil_div(a.N, g.RB), &p, s));
   return launch_tc<16, false>(map, p, g, s);
 }
+
+#ifdef HASTE_B200_TIMING_EXPERIMENTS
+// Timing-experiment builds only: the clock64 stamps the last tensor-core recurrence launch
+// left (CTA 0, tile 0; eight per step), copied to host memory.
+extern "C" int haste_b200_debug_read_stamps(long long* out, int max_steps) {
+  if (!g_stamps) return 0;
+  const int n = g_stamp_steps < max_steps ? g_stamp_steps : max_steps;
+  cudaDeviceSynchronize();
+  cudaMemcpy(out, g_stamps, (size_t)n * 16 * sizeof(long long), cudaMemcpyDeviceToHost);
+  return n;
+}
+#endif
 
 }  // namespace hb
