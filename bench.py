@@ -328,8 +328,8 @@ def main():
     # capture of each kernel at T=200 (dram__bytes_read.sum + dram__bytes_write.sum over
     # the 200 steps).  Every step touches its own slice of the activations once, so a
     # launch's traffic is this times T.
-    ncu_bytes_per_step = {"recurrence_fwd": (109.377024e6 + 108.569600e6) / 200,
-                          "recurrence_bwd": (188.644096e6 + 166.822912e6) / 200}
+    ncu_bytes_per_step = {"recurrence_fwd": (109.424896e6 + 103.794944e6) / 200,
+                          "recurrence_bwd": (188.525568e6 + 169.723648e6) / 200}
     dom = max(phases, key=phases.get)
     if dom in alg_bytes:
         ach = alg_bytes[dom] / (phases[dom] * 1e-3) / 1e9

@@ -7,7 +7,8 @@ import ctypes
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libhaste_b200.so")
+# HASTE_B200_LIBRARY selects another build of the library (a debug or experiment build)
+LIB_PATH = os.environ.get("HASTE_B200_LIBRARY") or os.path.join(_HERE, "libhaste_b200.so")
 
 F32, BF16, F16, BF16_WIDE = 0, 1, 2, 3
 PATH_AUTO, PATH_STEPWISE, PATH_PERSISTENT, PATH_NO_TENSOR_CORE = 0, 1, 2, 3

@@ -63,5 +63,40 @@ def build(force=False, verbose=False):
     return LIB
 
 
+TORCH_EXT_SRC = os.path.join(HERE, "torch_ext", "haste_pytorch_lib.cc")
+TORCH_EXT = os.path.join(HERE, "torch_ext", "haste_pytorch_lib.so")
+
+
+def build_torch_ext(force=False):
+    """Compiles the pybind11 module `haste_pytorch_lib` (the reference's extension name) against
+    the installed torch and links it to libhaste_b200.so, in-tree."""
+    import sysconfig
+    import torch
+    from torch.utils import cpp_extension as ce
+    lib = build()
+    header = os.path.join(HERE, "..", "include", "haste_b200.h")
+    if (not force and os.path.exists(TORCH_EXT)
+            and os.path.getmtime(TORCH_EXT) > max(os.path.getmtime(TORCH_EXT_SRC),
+                                                  os.path.getmtime(header))):
+        return TORCH_EXT
+    cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
+    incs = ce.include_paths() + [sysconfig.get_paths()["include"], os.path.join(HERE, "..", "include"),
+                                 os.path.join(cuda_home, "include")]
+    tlib = os.path.join(os.path.dirname(torch.__file__), "lib")
+    cmd = [os.environ.get("CXX", "g++"), "-O2", "-std=c++17", "-fPIC", "-shared",
+           "-DTORCH_EXTENSION_NAME=haste_pytorch_lib", "-DTORCH_API_INCLUDE_EXTENSION_H",
+           f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+           *[f"-I{i}" for i in incs], TORCH_EXT_SRC, "-o", TORCH_EXT,
+           f"-L{tlib}", "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch", "-ltorch_python",
+           f"-L{os.path.dirname(lib)}", "-lhaste_b200",
+           f"-Wl,-rpath,{tlib}", "-Wl,-rpath,$ORIGIN/.."]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"torch extension build failed:\n{r.stdout}\n{r.stderr}")
+    return TORCH_EXT
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--torch-ext" in sys.argv:
+        print(build_torch_ext(force="--force" in sys.argv))

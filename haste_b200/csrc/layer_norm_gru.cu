@@ -157,15 +157,12 @@ int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s) {
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 3 * H, a.dp, 3LL * H, 1, a.W, tr ? C : 1,
               tr ? 1 : 3LL * H, a.dx, C, 0};
-  gx.precise = 1;
   HB_TRY(gemm(gx, s));
   GemmDesc gr{a.dtype, a.dtype, H, 3 * H, (int)TN, a.h, 1, H, a.act_Rh, 3LL * H, 1, a.dR,
               3LL * H, 1};
-  gr.precise = 1;
   HB_TRY(gemm(gr, s));
   GemmDesc gw{a.dtype, a.dtype, C, 3 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.dp, 3LL * H, 1,
               a.dW, 3LL * H, 1};
-  gw.precise = 1;
   HB_TRY(gemm(gw, s));
   return HASTE_B200_OK;
 }

@@ -482,21 +482,18 @@ int backward_core(const LnLstmBwd& a, cudaStream_t s) {
   const bool tr = a.transposed_inputs != 0;
   GemmDesc gw{a.dtype, a.dtype, C, 4 * H, (int)TN, a.x, tr ? TN : 1, tr ? 1 : C, a.act_Wx,
               4LL * H, 1, a.dW, 4LL * H, 1};
-  gw.precise = 1;
   {
     ProfScope p(PH_WGRAD, s);
     HB_TRY(gemm(gw, s));
   }
   GemmDesc gr{a.dtype, a.dtype, H, 4 * H, (int)TN, a.h, 1, H, a.act_Rh, 4LL * H, 1, a.dR,
               4LL * H, 1};
-  gr.precise = 1;
   {
     ProfScope p(PH_WGRAD, s);
     HB_TRY(gemm(gr, s));
   }
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, 4 * H, a.act_Wx, 4LL * H, 1, a.W, tr ? C : 1,
               tr ? 1 : 4LL * H, a.dx, C, 0};
-  gx.precise = 1;
   {
     ProfScope p(PH_DGRAD, s);
     HB_TRY(gemm(gx, s));

@@ -51,8 +51,14 @@ max_rel_err = oracle.max_rel_err
 # input dictionary, returning outputs and gradients under the oracle's names.
 # ---------------------------------------------------------------------------
 def run_cuda(cell, d, zoneout=0.0, dtype=torch.float32, transposed=False, training=True,
-             backward=True, device="cuda", grads=None, fwd_kwargs=None):
+             backward=True, device="cuda", grads=None, fwd_kwargs=None, lib=None):
+    """Runs one layer through the twelve tensor-level ops: those of `haste_b200.ops`, or of
+    `lib` - the compiled `haste_pytorch_lib` module, which has the reference's exact
+    signatures (pre-transposed backward inputs, no keyword arguments)."""
     from haste_b200 import ops
+    compiled = lib is not None
+    if compiled:
+        ops, transposed = lib, True
     _, names, has_c = oracle.CELLS[cell]
     t = {k: (v.to(device=device, dtype=dtype).contiguous() if v is not None else None)
          for k, v in d.items()}
@@ -103,7 +109,10 @@ def run_cuda(cell, d, zoneout=0.0, dtype=torch.float32, transposed=False, traini
     else:
         args = (xx, W, rec, t["b"], t["gamma"], mask, fwd[0], *saved, t["dh"])
         gn = ["x", "h0", "W", "u", "b", "gamma"]
-    got = getattr(ops, cell + "_backward")(*args, transposed=transposed, grads=grads)
+    if compiled:
+        got = getattr(ops, cell + "_backward")(*args)
+    else:
+        got = getattr(ops, cell + "_backward")(*args, transposed=transposed, grads=grads)
     return out, dict(zip(gn, got))
 
 
