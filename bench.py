@@ -7,8 +7,12 @@ One "step" is one forward + backward pass of one LSTM layer over one synthetic b
 C ABI.  The metric is batch*steps per second = N*T / time(fwd+bwd).  Prints ONE JSON line.
 
  * `value`      inputs resident in HBM, CUDA-event timed over exactly K steps.
- * `e2e`        the same step driven from pinned HOST buffers: every step copies x
-                host->device and reads the final state and bias gradient back.
+ * `e2e`        the same step driven from pinned HOST buffers: every step copies x and
+                the incoming gradient dy host->device (overlapped with compute by the
+                streamed ops) and reads the final state and bias gradient back.  The
+                process is first bound to the CPUs local to its GPU (NVML affinity
+                query), so the pinned buffers are NUMA-local; `h2d_gbs_per_rank` is
+                each rank's plain copy rate with all ranks copying at once.
  * `roofline`   dominant kernel (by summed device time, measured live with the
                 library's per-phase CUDA events): algorithmic HBM bytes per launch /
                 its mean duration, against the measured copy bandwidth.
@@ -50,6 +54,31 @@ def make_weights(C, H, device, dtype, seed=0):
     return [t.to(device=device, dtype=dtype) for t in (W, R, b)]
 
 
+def bind_near_gpu(index):
+    """Restricts this process to the CPUs NVML reports as local to GPU `index` (a read-only
+    query), so that the pinned host buffers allocated afterwards land on that GPU's NUMA node
+    and the copy-issuing thread runs next to them.  Returns the number of CPUs kept (0: not
+    bound)."""
+    try:
+        import pynvml as nv
+        nv.nvmlInit()
+        uuid = str(torch.cuda.get_device_properties(index).uuid)
+        try:
+            h = nv.nvmlDeviceGetHandleByUUID(("GPU-" + uuid).encode())
+        except Exception:
+            h = nv.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = nv.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = {64 * i + b for i, w in enumerate(mask) for b in range(64) if (int(w) >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if not cpus:
+            return 0
+        os.sched_setaffinity(0, cpus)
+        return len(cpus)
+    except Exception:
+        return 0
+
+
 class ClockSampler:
     """Samples SM clocks / throttle reasons with nvidia-smi while the timed region runs."""
 
@@ -60,40 +89,46 @@ class ClockSampler:
     def __init__(self, index):
         self.index, self.samples, self.stop = index, [], threading.Event()
         self.thread = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self):
+        self.nv = self.handle = None
         # NVML (read-only queries) gives a sample every few milliseconds; nvidia-smi, at one
-        # process per sample, is the fallback.
+        # process per sample, is the fallback.  NVML is set up here, outside the timed region.
         try:
             import pynvml as nv
             nv.nvmlInit()
-            h = nv.nvmlDeviceGetHandleByIndex(self.index)
-            bits = [("hw_slowdown", nv.nvmlClocksEventReasonHwSlowdown),
-                    ("hw_thermal_slowdown", nv.nvmlClocksEventReasonHwThermalSlowdown),
-                    ("sw_thermal_slowdown", nv.nvmlClocksEventReasonSwThermalSlowdown),
-                    ("sw_power_cap", nv.nvmlClocksEventReasonSwPowerCap)]
-            mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
-            while not self.stop.is_set():
-                r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
-                self.samples.append([str(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), str(mx)] +
-                                    ["Active" if r & b else "Not Active" for _, b in bits])
-                self.stop.wait(0.005)
-            return
+            self.handle = nv.nvmlDeviceGetHandleByIndex(index)
+            self.bits = [nv.nvmlClocksEventReasonHwSlowdown, nv.nvmlClocksEventReasonHwThermalSlowdown,
+                         nv.nvmlClocksEventReasonSwThermalSlowdown, nv.nvmlClocksEventReasonSwPowerCap]
+            self.max_mhz = nv.nvmlDeviceGetMaxClockInfo(self.handle, nv.NVML_CLOCK_SM)
+            self.nv = nv
         except Exception:
-            pass
+            self.nv = None
+
+    def _sample(self):
+        if self.nv is not None:
+            nv, h = self.nv, self.handle
+            r = nv.nvmlDeviceGetCurrentClocksEventReasons(h)
+            self.samples.append([str(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)), str(self.max_mhz)] +
+                                ["Active" if r & b else "Not Active" for b in self.bits])
+            return
+        out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                              "--format=csv,noheader,nounits"], capture_output=True,
+                             text=True, timeout=5).stdout.strip()
+        if out:
+            self.samples.append([p.strip() for p in out.split(",")])
+
+    def _run(self):
         while not self.stop.is_set():
             try:
-                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                      "--format=csv,noheader,nounits"], capture_output=True,
-                                     text=True, timeout=5).stdout.strip()
-                if out:
-                    self.samples.append([p.strip() for p in out.split(",")])
+                self._sample()
             except Exception:
                 pass
-            self.stop.wait(0.2)
+            self.stop.wait(0.005 if self.nv is not None else 0.2)
 
     def __enter__(self):
         self.thread.start()
+        t0 = time.perf_counter()  # the sampler is running before the timed region starts
+        while not self.samples and time.perf_counter() - t0 < 1.0:
+            time.sleep(0.001)
         return self
 
     def __exit__(self, *a):
@@ -227,9 +262,11 @@ def main():
     dtype = torch.float32 if args.dtype == "f32" else torch.bfloat16
     W, R, b = make_weights(C, H, dev, dtype)
     g = torch.Generator().manual_seed(100 + rank)
+    cpus_bound = bind_near_gpu(local)  # before the pinned buffers are allocated
     x_host = torch.randn(T, N, C, generator=g).to(dtype).pin_memory()
     x = x_host.to(dev)
-    dy = torch.cat([torch.zeros(1, N, H), torch.randn(T, N, H, generator=g)]).to(dev, dtype)
+    dy_host = torch.cat([torch.zeros(1, N, H), torch.randn(T, N, H, generator=g)]).to(dtype).pin_memory()
+    dy = dy_host.to(dev)
     dc = torch.zeros(T + 1, N, H, device=dev, dtype=dtype)
     h0 = torch.zeros(N, H, device=dev, dtype=dtype)
     nomask = torch.empty(0, 0, 0, device=dev, dtype=dtype)
@@ -247,11 +284,13 @@ def main():
         return h, db
 
     def e2e_step():
-        # host-resident input: the public streamed-input op overlaps the copy with compute
+        # host-resident input and incoming gradient: the public streamed ops overlap both
+        # copies with compute (x piece by piece under the forward pass, dy under it as well,
+        # latest steps first, consumed piece by piece by the backward pass)
         h, c, cache, x_dev = ops.lstm_forward_from_host(True, 0.0, x_host, h0, h0, W, R, b, nomask)
         bucket.reset()
-        dx, dh, dc0, dW, dR, db = ops.lstm_backward(x_dev, W, R, b, nomask, h, c, cache, dy, dc,
-                                                    transposed=False, grads=bucket)
+        dx, dh, dc0, dW, dR, db = ops.lstm_backward_from_host(x_dev, W, R, b, nomask, h, c, cache,
+                                                              dy_host, dc, grads=bucket)
         bucket.all_reduce()
         res_host[:N * H].copy_(h[-1].reshape(-1), non_blocking=True)
         res_host[N * H:].copy_(db, non_blocking=True)
@@ -281,6 +320,26 @@ def main():
     for _ in range(2):
         e2e_step()
     barrier()
+
+    # host-to-device rate of this rank while every rank copies at once (the ranks share the
+    # host's memory and PCIe paths): the plain copy of x, best of three
+    stage = torch.empty_like(x)
+    h2d = []
+    for _ in range(3):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        stage.copy_(x_host, non_blocking=True)
+        e1.record()
+        torch.cuda.synchronize()
+        h2d.append(x_host.numel() * x_host.element_size() / (e0.elapsed_time(e1) * 1e-3) / 1e9)
+    del stage
+    h2d_rates = [max(h2d)]
+    if world > 1:
+        t = torch.tensor([max(h2d)], device=dev)
+        allr = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(allr, t)
+        h2d_rates = [float(v.item()) for v in allr]
 
     launches0 = _C.launch_count()
     with ClockSampler(local) as clocks:
@@ -353,8 +412,12 @@ def main():
         "config": {"workload": f"lstm_N{N}_C{C}_H{H}_T{T}_{args.dtype}_fwd_bwd",
                    "per_gpu_batch": N, "l2": "inputs larger than L2 (x 131 MB, cache 524 MB)",
                    "grad_allreduce": world > 1},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": x_host.numel() * es,
-                "d2h_bytes_per_step": res_host.numel() * es},
+        "e2e": {"value": e2e_value, "unit": UNIT,
+                "h2d_bytes_per_step": (x_host.numel() + dy_host.numel()) * es,
+                "d2h_bytes_per_step": res_host.numel() * es,
+                "inputs_from_host": ["x", "dy"],
+                "h2d_gbs_per_rank": [round(v, 1) for v in h2d_rates],
+                "cpus_bound_near_gpu": cpus_bound},
         "gpu_launches": int(launches),
         "clocks": clocks.summary(),
         "roofline": roof,

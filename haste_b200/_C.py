@@ -12,7 +12,7 @@ LIB_PATH = os.environ.get("HASTE_B200_LIBRARY") or os.path.join(_HERE, "libhaste
 
 F32, BF16, F16, BF16_WIDE = 0, 1, 2, 3
 PATH_AUTO, PATH_STEPWISE, PATH_PERSISTENT, PATH_NO_TENSOR_CORE = 0, 1, 2, 3
-GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05 = 0, 1, 2
+GEMM_AUTO, GEMM_SIMT, GEMM_TCGEN05, GEMM_TCGEN05_SINGLE = 0, 1, 2, 3
 
 _i, _f, _p, _ll = ctypes.c_int, ctypes.c_float, ctypes.c_void_p, ctypes.c_longlong
 

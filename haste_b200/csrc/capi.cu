@@ -65,7 +65,7 @@ int haste_b200_set_sm_budget(int sms) {
   return HASTE_B200_OK;
 }
 int haste_b200_set_gemm_path(int path) {
-  if (path < 0 || path > 2) return HASTE_B200_ERR_INVALID;
+  if (path < 0 || path > 3) return HASTE_B200_ERR_INVALID;
   g_gemm_path.store(path);
   return HASTE_B200_OK;
 }

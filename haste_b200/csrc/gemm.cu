@@ -10,7 +10,7 @@ int gemm(const GemmDesc& g, cudaStream_t stream) {
   if (path != HASTE_B200_GEMM_SIMT) {
     const int st_ = gemm_sm100(g, stream);
     if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
-    if (path == HASTE_B200_GEMM_TCGEN05) return st_;  // forced: report rather than fall through
+    if (path == HASTE_B200_GEMM_TCGEN05 || path == HASTE_B200_GEMM_TCGEN05_SINGLE) return st_;  // forced: report rather than fall through
   }
   return gemm_simt(g, stream);
 }

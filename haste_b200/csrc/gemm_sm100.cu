@@ -68,6 +68,7 @@ struct Cfg {
   // other accumulator.  0: one hand-over per tile (bf16 storage, where 2e-2 is the bar).
   // Four accumulators take turns, so the MMA warp runs up to three chunks ahead of the
   // epilogue; a chunk is about 1.6 us of MMA work either way.
+  // (Twice these chunk lengths fails the fp32 parity test of the three-layer LayerNormLSTM stack.)
   static constexpr int CHUNK = NPROD == 1 ? 0 : (NPROD == 3 ? 4 : 2);
 };
 
@@ -261,7 +262,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       const uint32_t a_lbo = p.a_mn_major ? TILE_BYTES / 2 : 16, a_kstep = p.a_mn_major ? 2048 : 32;
       const uint32_t b_lbo = p.b_mn_major ? TILE_BYTES / 2 : 16, b_kstep = p.b_mn_major ? 2048 : 32;
       uint32_t stage = 0, phase = 0;
-      uint32_t acc_phase[NACC] = {0, 0, 0, 0};
+      uint32_t acc_phase = 0;  // one parity bit per accumulator
       int cidx = 0;  // accumulator hand-overs so far: they alternate between the two buffers
       bool ok = true;
       for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
@@ -272,8 +273,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
         while (kb < kb1 && ok) {
           const int acc = cidx % NACC;
           ++cidx;
-          if (!mbar_wait(acce_bar(acc), acc_phase[acc] ^ 1u, abort_flag, p.err, 2)) { ok = false; break; }
-          acc_phase[acc] ^= 1u;
+          if (!mbar_wait(acce_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag, p.err, 2)) { ok = false; break; }
+          acc_phase ^= 1u << acc;
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + acc * BN;
           const int kend = C::CHUNK ? min(kb1, kb + C::CHUNK) : kb1;
@@ -309,7 +310,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   } else {
     // ------------------------------------------------------------------ epilogue
     const int quad = warp & 3;  // tensor-memory lane quadrant this warp may read
-    uint32_t acc_phase[NACC] = {0, 0, 0, 0};
+    uint32_t acc_phase = 0;  // one parity bit per accumulator
     int cidx = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
@@ -328,10 +329,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
       for (int c = 0; c < nchunks; ++c) {
         const int acc = cidx % NACC;
         ++cidx;
-        if (ok) ok = mbar_wait(accf_bar(acc), acc_phase[acc], abort_flag, p.err, 4);
+        if (ok) ok = mbar_wait(accf_bar(acc), (acc_phase >> acc) & 1u, abort_flag, p.err, 4);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        acc_phase[acc] ^= 1u;
+        acc_phase ^= 1u << acc;
         tc_fence_after();
         const uint32_t taddr = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
         if (C::CHUNK) {
@@ -374,6 +375,245 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
   if (warp == 1) {
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
                  "r"((uint32_t)TMEM_COLS)
+                 : "memory");
+  }
+}
+
+// ---- the same contraction on CTA pairs ------------------------------------------------------
+// The single-CTA kernel above runs at (shared-memory ring bytes) / (load latency): a 128 x 128
+// tile needs 32 KB of operands per 64-wide k-block and product, about twice what the ring can
+// have in flight per unit of tensor-pipe time.  Here two CTAs of a cluster share a 256 x 256
+// tile (tcgen05.mma.cta_group::2, M = 256): each CTA loads its own 128 rows of A and its own
+// 128-column half of B - the same two 16 KB boxes per plane as above - and the tensor cores of
+// both SMs read both halves of B, so every loaded byte feeds twice the arithmetic.  Each CTA's
+// tensor memory holds its 128 rows x 256 columns of the accumulator (two accumulators of 256
+// columns).  CTA 0 of the pair issues all MMAs; its full barriers count the bytes of both
+// CTAs' loads (the loads name the barrier through cta_group::2, no multicast anywhere), its
+// commits arrive on the empty and accumulator-full barriers of both CTAs, and both CTAs'
+// epilogue warps (eight per CTA: four lane quadrants x two column halves) arrive on its
+// accumulator-empty barriers.
+constexpr int PAIR_THREADS = 320;        // warp 0 TMA, warp 1 MMA / tensor memory, warps 2..9 epilogue
+constexpr int PBN = 256;                 // columns of the pair's tile and of one accumulator
+constexpr int PBM = 256;                 // rows of the pair's tile (128 per CTA)
+constexpr int PAIR_NACC = 2;
+constexpr int PAIR_EPI_WARPS = 8;
+
+// (Ten warps put three on two of the SM's four sub-partitions, 16384 registers each, so 168
+// registers per thread is the most a 320-thread CTA can have; the epilogue therefore drains the
+// accumulator 16 columns at a time.)
+template <int NPROD>
+__global__ void __launch_bounds__(PAIR_THREADS, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                         const __grid_constant__ CUtensorMap map_b, const Params p) {
+  using C = Cfg<NPROD>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* aligned = smem_raw + (base - smem_u32(smem_raw));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(aligned + C::STAGES * C::STAGE_BYTES);
+  // barrier slots: full[STAGES], empty[STAGES], acc_full[2], acc_empty[2]
+  const uint32_t bar0 = smem_u32(bars);
+  auto full_bar = [&](int s) { return bar0 + 8u * s; };
+  auto empty_bar = [&](int s) { return bar0 + 8u * (C::STAGES + s); };
+  auto accf_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + a); };
+  auto acce_bar = [&](int a) { return bar0 + 8u * (2 * C::STAGES + PAIR_NACC + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * C::STAGES + 2 * PAIR_NACC);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();  // 0 issues the MMAs
+  const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < C::STAGES; ++s) {
+      mbar_init(full_bar(s), 1);   // CTA 0's producer; the bytes of both CTAs' loads
+      mbar_init(empty_bar(s), 1);  // one commit
+    }
+    for (int a = 0; a < PAIR_NACC; ++a) {
+      mbar_init(accf_bar(a), 1);
+      mbar_init(acce_bar(a), 2 * PAIR_EPI_WARPS);  // one arrival per epilogue warp of both CTAs
+    }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    // collective over the pair: the same warp of both CTAs, the same shared-memory slot
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(
+                     smem_u32(tmem_slot)),
+                 "r"((uint32_t)(PAIR_NACC * PBN))
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int total_items = p.tiles_m * p.tiles_n * p.splits;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int item = pair; item < total_items && ok; item += npairs) {
+        const int tn = item % p.tiles_n;
+        const int tm = (item / p.tiles_n) % p.tiles_m;
+        const int sp = item / (p.tiles_n * p.tiles_m);
+        const int kb0 = sp * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        const int m0 = tm * PBM + (int)rank * BM, n0 = tn * PBN + (int)rank * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.err, 11)) { ok = false; break; }
+          if (rank == 0) mbar_expect_tx(full_bar(stage), 2 * C::STAGE_BYTES);
+          const uint32_t fb = mapa_u32(full_bar(stage), 0);
+          const uint32_t sa = base + stage * C::STAGE_BYTES;
+          const uint32_t sb = sa + C::PLANES * TILE_BYTES;
+          const int k0 = kb * BK;
+#pragma unroll
+          for (int pl = 0; pl < C::PLANES; ++pl) {
+            const uint32_t da = sa + pl * TILE_BYTES, db = sb + pl * TILE_BYTES;
+            if (p.a_mn_major) {  // two boxes of 64 (m) x 64 (k)
+              tma_load_3d_pair(da, &map_a, fb, m0, k0, pl);
+              tma_load_3d_pair(da + TILE_BYTES / 2, &map_a, fb, m0 + 64, k0, pl);
+            } else {             // one box of 64 (k) x 128 (m)
+              tma_load_3d_pair(da, &map_a, fb, k0, m0, pl);
+            }
+            if (p.b_mn_major) {
+              tma_load_3d_pair(db, &map_b, fb, n0, k0, pl);
+              tma_load_3d_pair(db + TILE_BYTES / 2, &map_b, fb, n0 + 64, k0, pl);
+            } else {
+              tma_load_3d_pair(db, &map_b, fb, k0, n0, pl);
+            }
+          }
+          if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer (CTA 0 only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = (1u << 4) | (1u << 7) | (1u << 10) |
+                             ((uint32_t)p.a_mn_major << 15) | ((uint32_t)p.b_mn_major << 16) |
+                             ((uint32_t)(PBN >> 3) << 17) | ((uint32_t)(PBM >> 4) << 24);
+      const uint32_t a_lbo = p.a_mn_major ? TILE_BYTES / 2 : 16, a_kstep = p.a_mn_major ? 2048 : 32;
+      const uint32_t b_lbo = p.b_mn_major ? TILE_BYTES / 2 : 16, b_kstep = p.b_mn_major ? 2048 : 32;
+      uint32_t stage = 0, phase = 0;
+      uint32_t acc_phase = 0;  // one parity bit per accumulator
+      int cidx = 0;
+      bool ok = true;
+      for (int item = pair; item < total_items && ok; item += npairs) {
+        const int sp = item / (p.tiles_n * p.tiles_m);
+        const int kb0 = sp * p.kb_per_split;
+        const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+        int kb = kb0;
+        while (kb < kb1 && ok) {
+          const int acc = cidx % PAIR_NACC;
+          ++cidx;
+          if (!mbar_wait_cluster(acce_bar(acc), ((acc_phase >> acc) & 1u) ^ 1u, abort_flag, p.err, 12)) { ok = false; break; }
+          acc_phase ^= 1u << acc;
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + acc * PBN;
+          const int kend = C::CHUNK ? min(kb1, kb + C::CHUNK) : kb1;
+          uint32_t first = 1;
+          for (; kb < kend; ++kb) {
+            if (!mbar_wait_cluster(full_bar(stage), phase, abort_flag, p.err, 13)) { ok = false; break; }
+            tc_fence_after();
+            const uint32_t sa = base + stage * C::STAGE_BYTES;
+            const uint32_t sb = sa + C::PLANES * TILE_BYTES;
+#pragma unroll
+            for (int pr = 0; pr < NPROD; ++pr) {
+              const int ia = pr == 2 ? 1 : (pr == 3 ? 1 : (pr == 5 ? 2 : 0));
+              const int ib = pr == 1 ? 1 : (pr == 3 ? 1 : (pr == 4 ? 2 : 0));
+              const uint32_t pa = sa + ia * TILE_BYTES;
+              const uint32_t pb = sb + ib * TILE_BYTES;
+#pragma unroll
+              for (int ks = 0; ks < BK / UK; ++ks) {
+                const uint64_t da = smem_desc(pa + ks * a_kstep, a_lbo, 1024);
+                const uint64_t db = smem_desc(pb + ks * b_kstep, b_lbo, 1024);
+                tc_mma_bf16_pair(d_tmem, da, db, idesc, first ? 0u : 1u);
+                first = 0;
+              }
+            }
+            tc_commit_pair(empty_bar(stage), 3);  // frees the stage in both CTAs
+            if (++stage == C::STAGES) { stage = 0; phase ^= 1u; }
+          }
+          if (ok) tc_commit_pair(accf_bar(acc), 3);  // this chunk is complete in both CTAs
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (both CTAs)
+    const int quad = warp & 3;         // tensor-memory lane quadrant this warp may read
+    const int half = (warp - 2) >> 2;  // which 128 columns of the accumulator
+    uint32_t acc_phase = 0;  // one parity bit per accumulator
+    int cidx = 0;
+    bool ok = true;
+    for (int item = pair; item < total_items; item += npairs) {
+      const int tn = item % p.tiles_n;
+      const int tm = (item / p.tiles_n) % p.tiles_m;
+      const int sp = item / (p.tiles_n * p.tiles_m);
+      const int kb0 = sp * p.kb_per_split;
+      const int kb1 = min(p.kb_total, kb0 + p.kb_per_split);
+      const int nchunks = C::CHUNK ? (kb1 - kb0 + C::CHUNK - 1) / C::CHUNK : 1;
+      const int m = tm * PBM + (int)rank * BM + quad * 32 + lane;
+      const int n0 = tn * PBN + half * BN;
+      float sum[C::CHUNK ? BN : 1];
+#pragma unroll
+      for (int j = 0; j < (C::CHUNK ? BN : 1); ++j) sum[j] = 0.f;
+      for (int c = 0; c < nchunks; ++c) {
+        const int acc = cidx % PAIR_NACC;
+        ++cidx;
+        if (ok) ok = mbar_wait(accf_bar(acc), (acc_phase >> acc) & 1u, abort_flag, p.err, 14);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        acc_phase ^= 1u << acc;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + acc * PBN + half * BN + ((uint32_t)(quad * 32) << 16);
+        if (C::CHUNK) {
+#pragma unroll
+          for (int ch = 0; ch < BN / 16; ++ch) {
+            uint32_t r[16];
+            tc_ld16(taddr + ch * 16, r);
+            tc_wait_ld();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) sum[(C::CHUNK ? ch * 16 : 0) + j] += __uint_as_float(r[j]);
+          }
+        } else {
+#pragma unroll 1
+          for (int ch = 0; ch < BN / 32; ++ch) {
+            uint32_t r[32];
+            tc_ld32(taddr + ch * 32, r);
+            tc_wait_ld();
+            store_chunk(p, sp, m, n0 + ch * 32, r);
+          }
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(mapa_u32(acce_bar(acc), 0));
+      }
+      if (!ok) break;
+      if (C::CHUNK) {
+#pragma unroll
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          uint32_t r[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(sum[(C::CHUNK ? ch * 32 : 0) + j]);
+          store_chunk(p, sp, m, n0 + ch * 32, r);
+        }
+      }
+    }
+  }
+
+  // Drain: every role of both CTAs arrives here, also after a time-out.  Neither CTA may leave
+  // while the other's MMAs can still read its shared memory or signal its barriers.
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base),
+                 "r"((uint32_t)(PAIR_NACC * PBN))
                  : "memory");
   }
 }
@@ -481,6 +721,54 @@ struct Operand {
 // opts in on each of them.
 constexpr int kMaxDevices = 64;
 std::atomic<bool> g_attr_set[kMaxDevices];
+std::atomic<int> g_max_pairs[kMaxDevices];  // 0: not asked yet, -1: no clusters, else the count
+
+int set_kernel_attributes() {
+  int dev = 0;
+  HB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < kMaxDevices && g_attr_set[dev].load(std::memory_order_acquire))
+    return HASTE_B200_OK;
+  const auto attr = cudaFuncAttributeMaxDynamicSharedMemorySize;
+  HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<1>, attr, Cfg<1>::SMEM));
+  HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<3>, attr, Cfg<3>::SMEM));
+  HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<6>, attr, Cfg<6>::SMEM));
+  HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<1>, attr, Cfg<1>::SMEM));
+  HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<3>, attr, Cfg<3>::SMEM));
+  HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_pair_kernel<6>, attr, Cfg<6>::SMEM));
+  if (dev >= 0 && dev < kMaxDevices) g_attr_set[dev].store(true, std::memory_order_release);
+  return HASTE_B200_OK;
+}
+
+// How many clusters of two CTAs of the pair kernel the device holds at once (its persistent
+// grid); 0 when cluster launch is not available.
+int max_pairs() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return 0;
+  int n = g_max_pairs[dev].load(std::memory_order_acquire);
+  if (n == 0) {
+    n = -1;
+    if (set_kernel_attributes() == HASTE_B200_OK) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * sm_count());
+      cfg.blockDim = dim3(PAIR_THREADS);
+      cfg.dynamicSmemBytes = Cfg<6>::SMEM;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 2;
+      attr[0].val.clusterDim.y = 1;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      int clusters = 0;
+      if (cudaOccupancyMaxActiveClusters(&clusters, gemm_tcgen05_pair_kernel<6>, &cfg) ==
+              cudaSuccess && clusters > 0)
+        n = min(clusters, sm_count() / 2);
+      cudaGetLastError();
+    }
+    g_max_pairs[dev].store(n, std::memory_order_release);
+  }
+  return n > 0 ? n : 0;
+}
 
 }  // namespace
 
@@ -513,25 +801,32 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
   const long long b_ld_src = b_k ? g.b_cs : g.b_rs;
 
   // scratch: planes for fp32 operands, partial tiles for split-K
-  const int tiles_m = ceil_div(M, BM), tiles_n = ceil_div(N, BN);
+  const int sms = sm_count();
+  // CTA pairs on 256 x 256 tiles where the output is wide enough to fill them
+  const int pairs = (gemm_path() == HASTE_B200_GEMM_TCGEN05_SINGLE || M < 192 || N < 192)
+                        ? 0 : max_pairs();
+  const bool pair = pairs > 0;
+  const int units = pair ? pairs : sms;
+  const int tiles_m = ceil_div(M, pair ? PBM : BM), tiles_n = ceil_div(N, pair ? PBN : BN);
   const int kb_total = ceil_div(K, BK);
   int splits = 1;
-  const int sms = sm_count();
-  if (tiles_m * tiles_n < sms && kb_total >= 8) {
+  if (tiles_m * tiles_n < units && kb_total >= 8) {
     // Split K so that the work items fill whole waves of the persistent grid: pick the split
     // count with the smallest estimated time = (waves / splits) x K blocks x time per K block
     // + the traffic of the partial tiles (written once, read once by the reduction).
     const int tiles = tiles_m * tiles_n;
     const int max_splits = min(kb_total / 4, 64);
     const double products = g.dtype == HASTE_B200_BF16 ? 1.0 : (g.precise ? 6.0 : 3.0);
-    const double t_kb = 0.13 * products;                              // us per K block and CTA
+    // us per K block and work unit (measured: the single-CTA kernel is bound by its operand
+    // loads, the pair kernel by the tensor pipe)
+    const double t_kb = pair ? 0.27 * products : (products == 1.0 ? 0.27 : 0.17 * products);
     const double t_part = 2.0 * (double)M * N * 4.0 / 6.0e6;          // us per split (HBM)
     double best = 1e30;
     for (int sp = 1; sp <= max_splits; ++sp) {
       const int per = ceil_div(kb_total, sp);
       const int real = ceil_div(kb_total, per);
       if (real != sp) continue;  // the same blocks per split as a smaller count: skip
-      const double t = (double)ceil_div(tiles * sp, sms) * per * t_kb + (sp > 1 ? sp * t_part : 0.0);
+      const double t = (double)ceil_div(tiles * sp, units) * per * t_kb + (sp > 1 ? sp * t_part : 0.0);
       if (t < best) { best = t; splits = sp; }
     }
   }
@@ -605,26 +900,38 @@ int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
   p.partial = partial;
   p.err = err;
 
-  {
-    int dev = 0;
-    HB_CUDA_OK(cudaGetDevice(&dev));
-    if (dev < 0 || dev >= kMaxDevices || !g_attr_set[dev].load(std::memory_order_acquire)) {
-      HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<1>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<1>::SMEM));
-      HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<3>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<3>::SMEM));
-      HB_CUDA_OK(cudaFuncSetAttribute(gemm_tcgen05_kernel<6>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg<6>::SMEM));
-      if (dev >= 0 && dev < kMaxDevices) g_attr_set[dev].store(true, std::memory_order_release);
+  HB_TRY(set_kernel_attributes());
+  if (pair) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * min(pairs, tiles_m * tiles_n * splits));
+    cfg.blockDim = dim3(PAIR_THREADS);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (planes == 3) {
+      cfg.dynamicSmemBytes = Cfg<6>::SMEM;
+      HB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<6>, m_a, m_b, p));
+    } else if (planes == 2) {
+      cfg.dynamicSmemBytes = Cfg<3>::SMEM;
+      HB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<3>, m_a, m_b, p));
+    } else {
+      cfg.dynamicSmemBytes = Cfg<1>::SMEM;
+      HB_CUDA_OK(cudaLaunchKernelEx(&cfg, gemm_tcgen05_pair_kernel<1>, m_a, m_b, p));
     }
+  } else {
+    const int grid = min(sms, tiles_m * tiles_n * splits);
+    if (planes == 3)
+      gemm_tcgen05_kernel<6><<<grid, THREADS, Cfg<6>::SMEM, stream>>>(m_a, m_b, p);
+    else if (planes == 2)
+      gemm_tcgen05_kernel<3><<<grid, THREADS, Cfg<3>::SMEM, stream>>>(m_a, m_b, p);
+    else
+      gemm_tcgen05_kernel<1><<<grid, THREADS, Cfg<1>::SMEM, stream>>>(m_a, m_b, p);
   }
-  const int grid = min(sms, tiles_m * tiles_n * splits);
-  if (planes == 3)
-    gemm_tcgen05_kernel<6><<<grid, THREADS, Cfg<6>::SMEM, stream>>>(m_a, m_b, p);
-  else if (planes == 2)
-    gemm_tcgen05_kernel<3><<<grid, THREADS, Cfg<3>::SMEM, stream>>>(m_a, m_b, p);
-  else
-    gemm_tcgen05_kernel<1><<<grid, THREADS, Cfg<1>::SMEM, stream>>>(m_a, m_b, p);
   HB_LAUNCH_OK();
   count_launch(1);
   if (splits > 1) {

@@ -185,6 +185,76 @@ def lstm_forward_from_host(training, zoneout_prob, x_host, h0, c0, kernel, recur
     return [h, c, cache, x]
 
 
+_host_stage = {}  # (device, shape, dtype) -> [device buffer, event of its last reader]
+
+
+def lstm_backward_from_host(x, kernel, recurrent_kernel, bias, zoneout_mask, h, c, cache,
+                            dh_new_host, dc_new, chunks=4, grads=None):
+    """`lstm_backward(..., transposed=False)` for an incoming gradient `dh_new_host`
+    `[T+1,N,H]` that still lives in pinned HOST memory.
+
+    The backward pass consumes the gradient from the last time step down, so it is copied in
+    `chunks` pieces in that order on the copy stream while the GPU is still busy with the
+    forward pass, and the pass itself runs as one C-ABI call per piece, latest piece first: the
+    carried `dh`, `dc` go from call to call through the `[N,H]` in/out buffers, `dW`, `dR`, `db`
+    accumulate, and each call assigns its own slice of `dx`.  The result equals one call on the
+    whole sequence up to the summation order of the weight gradients.  The device copy of the
+    gradient is kept between calls (one buffer per device and shape), guarded by an event of
+    its last reader.
+    Returns [dx, dh, dc, dW, dR, db].
+    """
+    _check(x, kernel, recurrent_kernel, bias, zoneout_mask, h, c, cache, dc_new)
+    if dh_new_host.is_cuda or not dh_new_host.is_pinned():
+        raise RuntimeError("haste_b200: dh_new_host must be a pinned CPU tensor")
+    T, N, C = x.shape
+    H = h.shape[2]
+    dev = h.device
+    with torch.cuda.device(dev):
+        main = torch.cuda.current_stream()
+        side = _copy_streams.get(dev.index)
+        if side is None:
+            side = _copy_streams[dev.index] = torch.cuda.Stream(device=dev)
+        key = (dev.index, tuple(dh_new_host.shape), h.dtype)
+        slot = _host_stage.get(key)
+        if slot is None:
+            slot = _host_stage[key] = [torch.empty(T + 1, N, H, device=dev, dtype=h.dtype), None]
+        dh_new = slot[0]
+        if slot[1] is not None:
+            side.wait_event(slot[1])  # the previous call's kernels have read the buffer
+        bounds = [round(i * T / chunks) for i in range(chunks + 1)]
+        events = [None] * chunks
+        with torch.cuda.stream(side):
+            for k in reversed(range(chunks)):
+                t0, t1 = bounds[k], bounds[k + 1]
+                if t1 > t0:  # steps t0..t1-1 read the gradient slots t0+1..t1
+                    dh_new[t0 + 1:t1 + 1].copy_(dh_new_host[t0 + 1:t1 + 1], non_blocking=True)
+                events[k] = torch.cuda.Event()
+                events[k].record(side)
+        dx = h.new_empty(T, N, C)
+        dW = _zeros(grads, h, C, 4 * H)
+        dR = _zeros(grads, h, H, 4 * H)
+        db = _zeros(grads, h, 4 * H)
+        dh = h.new_zeros(N, H)
+        dc = h.new_zeros(N, H)
+        es = h.element_size()
+        mp = _p(zoneout_mask)
+        for k in reversed(range(chunks)):
+            t0, t1 = bounds[k], bounds[k + 1]
+            if t1 == t0:
+                continue
+            main.wait_event(events[k])
+            o = t0 * N * es
+            _C.call("haste_b200_lstm_backward", _dtype(h), 0, t1 - t0, N, C, H, _p(kernel),
+                    _p(recurrent_kernel), _p(bias), x.data_ptr() + o * C, h.data_ptr() + o * H,
+                    c.data_ptr() + o * H, dh_new.data_ptr() + o * H, dc_new.data_ptr() + o * H,
+                    dx.data_ptr() + o * C, _p(dW), _p(dR), _p(db), _p(dh), _p(dc),
+                    cache.data_ptr() + o * 4 * H, (mp + o * H) if mp else None,
+                    main.cuda_stream)
+        slot[1] = torch.cuda.Event()
+        slot[1].record(main)
+    return [dx, dh, dc, dW, dR, db]
+
+
 # ---------------------------------------------------------------- GRU
 def gru_forward(training, zoneout_prob, x, h0, kernel, recurrent_kernel, bias, recurrent_bias,
                 zoneout_mask):

@@ -74,7 +74,8 @@ int haste_b200_set_recurrence_path(int path);
  * bidirectional layer, issued on two streams, are co-resident and run concurrently.  Honoured by
  * the tensor-core GRU recurrence; no reference counterpart. */
 int haste_b200_set_sm_budget(int sms);
-enum { HASTE_B200_GEMM_AUTO = 0, HASTE_B200_GEMM_SIMT = 1, HASTE_B200_GEMM_TCGEN05 = 2 };
+enum { HASTE_B200_GEMM_AUTO = 0, HASTE_B200_GEMM_SIMT = 1, HASTE_B200_GEMM_TCGEN05 = 2,
+       HASTE_B200_GEMM_TCGEN05_SINGLE = 3 /* tensor cores, never the CTA-pair kernel */ };
 int haste_b200_set_gemm_path(int path);
 /* Number of kernels this library has launched in the calling process. */
 long long haste_b200_launch_count(void);

@@ -219,6 +219,32 @@ def test_streamed_host_input_equals_single_call():
         assert torch.equal(got[3], cu(d["x"]))
 
 
+def test_streamed_host_gradient_equals_single_call():
+    """The backward pass fed with an incoming gradient in pinned host memory (copied and
+    consumed in pieces, latest first) equals one call on the whole sequence."""
+    from haste_b200 import ops
+    T, N, C, H = 37, 16, 32, 64
+    d = oracle.make_inputs("lstm", T, N, C, H, seed=9, zoneout=0.2)
+    cu = lambda t: t.float().cuda().contiguous()
+    x, mask = cu(d["x"]), cu(d["mask"])
+    W, R, b = cu(d["W"]), cu(d["R"]), cu(d["b"])
+    dh_new, dc_new = cu(d["dh"]), cu(d["dc"])
+    dh_host = d["dh"].float().pin_memory()
+
+    def forward():
+        return ops.lstm_forward(True, 0.2, x, cu(d["h0"]), cu(d["c0"]), W, R, b, mask)
+
+    h, c, cache = forward()
+    want = ops.lstm_backward(x, W, R, b, mask, h, c, cache, dh_new, dc_new, transposed=False)
+    for chunks in (1, 3, 4, 4):  # the repeated count reuses the staged device buffer
+        h, c, cache = forward()  # the backward pass overwrites the cache
+        got = ops.lstm_backward_from_host(x, W, R, b, mask, h, c, cache, dh_host, dc_new,
+                                          chunks=chunks)
+        torch.cuda.synchronize()
+        for a, e, name in zip(got, want, ["dx", "dh", "dc", "dW", "dR", "db"]):
+            assert_close(a, e, 2e-5, f"streamed {name} ({chunks} pieces)")
+
+
 @pytest.mark.parametrize("cell", ["lstm", "gru", "indrnn", "layer_norm_lstm", "layer_norm_gru",
                                   "layer_norm_indrnn"])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
