@@ -345,7 +345,9 @@ def main():
     with ClockSampler(local) as clocks:
         ms_total = timed(lambda: step(x), args.steps)
     launches = _C.launch_count() - launches0
+    _C.sync_check(torch.cuda.current_stream().cuda_stream)  # raises if a kernel gave up a wait
     ms_e2e = timed(e2e_step, args.steps)
+    _C.sync_check(torch.cuda.current_stream().cuda_stream)
 
     # per-phase device time, measured live (a separate pass so event overhead stays
     # out of the headline number)
@@ -396,6 +398,8 @@ def main():
         roof = {"kernel": dom, "bound": "hbm", "achieved": ach, "peak": peaks["hbm_gbs"],
                 "unit": "GB/s", "frac": ach / peaks["hbm_gbs"],
                 "traffic": ncu_bytes_per_step[dom] * T if captured else None,
+                "traffic_source": ("ncu capture of this kernel at T=200 (dram bytes read + "
+                                   "written), scaled by T") if captured else None,
                 "algorithmic_bytes": alg_bytes[dom],
                 "peak_source": peak_src,
                 "us_per_timestep": phases[dom] * 1e3 / T}

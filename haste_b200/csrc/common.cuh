@@ -127,6 +127,11 @@ struct GemmDesc {
 };
 int gemm(const GemmDesc& g, cudaStream_t stream);
 int gemm_simt(const GemmDesc& g, cudaStream_t stream);
+// fp32 [rows, cols] -> two bf16 planes (hi, lo), the a_pl / b_pl form, for an operand that
+// more than one contraction reads (gemm_sm100.cu).
+int gemm_split_planes(const float* src, long long ld_src, int rows, int cols,
+                      __nv_bfloat16* dst, long long ld_dst, long long plane_stride,
+                      cudaStream_t stream);
 
 // Row LayerNorm launchers (layer_norm.cu); see include/haste_b200.h for semantics.
 // `cache` is [rows,2] (mean, invstd) in `dtype`.  In the backward, dgamma/dbeta
@@ -140,8 +145,11 @@ int layer_norm_forward_from(int in_dtype, int dtype, int rows, int width, const 
                             const void* beta, const void* x, void* y, void* cache, void* x_copy,
                             cudaStream_t stream);
 size_t layer_norm_backward_scratch_floats(int rows, int width);
+// dx_planes (fp32 storage only, width a multiple of 8): dx is also written as two bf16 planes
+// (hi, then lo plane_stride elements later), the form GemmDesc::a_pl / b_pl takes.
 int layer_norm_backward(int dtype, int rows, int width, const void* gamma, const void* x,
                         const void* dy, void* dx, int acc_dtype, void* dgamma, void* dbeta,
-                        const void* cache, float* scratch, cudaStream_t stream);
+                        const void* cache, float* scratch, cudaStream_t stream,
+                        __nv_bfloat16* dx_planes = nullptr, long long plane_stride = 0);
 
 }  // namespace hb

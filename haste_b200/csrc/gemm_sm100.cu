@@ -772,6 +772,16 @@ int max_pairs() {
 
 }  // namespace
 
+// fp32 [rows, cols] (leading dimension ld_src) -> two bf16 planes of leading dimension ld_dst,
+// plane_stride elements apart: the form GemmDesc::a_pl / b_pl takes, for an operand that
+// several contractions read.
+int gemm_split_planes(const float* src, long long ld_src, int rows, int cols,
+                      __nv_bfloat16* dst, long long ld_dst, long long plane_stride,
+                      cudaStream_t stream) {
+  return launch_split(src, false, ld_src, rows, cols, dst, ld_dst, plane_stride, 2,
+                      8 * sm_count(), stream);
+}
+
 int gemm_sm100(const GemmDesc& g, cudaStream_t stream) {
   auto unsupported = [](const char* why) {
     set_last_error("gemm_sm100: %s", why);

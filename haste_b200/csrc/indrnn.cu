@@ -45,12 +45,16 @@ __global__ void indrnn_scan_fwd(int T_, long long NH, int H, const T* __restrict
   }
 }
 
-template <typename T, bool Zoneout>
+// Planes: dk is also written as two bf16 planes (hi, lo; `dk_planes`, the lo plane
+// `plane_stride` elements later) - the form the two contractions that read it take their
+// fp32 operands in, so that neither splits it again.
+template <typename T, bool Zoneout, bool Planes>
 __global__ void indrnn_scan_bwd(int T_, long long NH, int H, const T* __restrict__ u,
                                 const T* __restrict__ h, const T* __restrict__ dh_new,
                                 float* __restrict__ du_part, float* __restrict__ db_part,
                                 float* __restrict__ dh_carry, T* __restrict__ dk_out,
-                                const T* __restrict__ mask) {
+                                const T* __restrict__ mask,
+                                __nv_bfloat16* __restrict__ dk_planes, long long plane_stride) {
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= NH) return;
   const int j = (int)(idx % H);
@@ -80,6 +84,11 @@ __global__ void indrnn_scan_bwd(int T_, long long NH, int H, const T* __restrict
         }
         const float dk = d_tanh(hn[k]) * dh_total;
         st(dk_out + t * NH + idx, dk);
+        if (Planes) {
+          const __nv_bfloat16 hi = __float2bfloat16_rn(dk);
+          dk_planes[t * NH + idx] = hi;
+          dk_planes[plane_stride + t * NH + idx] = __float2bfloat16_rn(dk - __bfloat162float(hi));
+        }
         carry = keep + uj * dk;
         du += hpv[k] * dk;
         db += dk;
@@ -113,17 +122,20 @@ int scan_fwd(const IndrnnFwd& a, const void* Wx, cudaStream_t s) {
 }
 
 template <typename T>
-int scan_bwd(const IndrnnBwd& a, float* du_part, float* db_part, float* dh_carry, cudaStream_t s) {
+int scan_bwd(const IndrnnBwd& a, float* du_part, float* db_part, float* dh_carry,
+             __nv_bfloat16* planes, long long plane_stride, cudaStream_t s) {
   const long long NH = (long long)a.N * a.H;
   const int blocks = ceil_div(NH, 128);
-  if (a.zoneout_mask)
-    indrnn_scan_bwd<T, true><<<blocks, 128, 0, s>>>(
-        a.T, NH, a.H, (const T*)a.u, (const T*)a.h, (const T*)a.dh_new, du_part, db_part,
-        dh_carry, (T*)a.workspace, (const T*)a.zoneout_mask);
-  else
-    indrnn_scan_bwd<T, false><<<blocks, 128, 0, s>>>(
-        a.T, NH, a.H, (const T*)a.u, (const T*)a.h, (const T*)a.dh_new, du_part, db_part,
-        dh_carry, (T*)a.workspace, nullptr);
+#define HB_ARGS a.T, NH, a.H, (const T*)a.u, (const T*)a.h, (const T*)a.dh_new, du_part, db_part, \
+                dh_carry, (T*)a.workspace, (const T*)a.zoneout_mask, planes, plane_stride
+  if (planes) {
+    if (a.zoneout_mask) indrnn_scan_bwd<T, true, true><<<blocks, 128, 0, s>>>(HB_ARGS);
+    else                indrnn_scan_bwd<T, false, true><<<blocks, 128, 0, s>>>(HB_ARGS);
+  } else {
+    if (a.zoneout_mask) indrnn_scan_bwd<T, true, false><<<blocks, 128, 0, s>>>(HB_ARGS);
+    else                indrnn_scan_bwd<T, false, false><<<blocks, 128, 0, s>>>(HB_ARGS);
+  }
+#undef HB_ARGS
   HB_LAUNCH_OK();
   count_launch(1);
   return HASTE_B200_OK;
@@ -184,10 +196,21 @@ int indrnn_backward(const IndrnnBwd& a, cudaStream_t s) {
   float* lns = ws.take<float>(lnf);
   HB_REQUIRE(dh_carry && du_part && db_part && cs && (lns || !lnf), "scratch arena");
   HB_TRY(to_float(a.dtype, a.dh, dh_carry, NH, s));
+  // fp32: dk = d/d(x.W) is read by both contractions below as two bf16 planes.  Without
+  // LayerNorm the scan writes them next to the fp32 values; with LayerNorm its backward pass
+  // does.  (Grow-only library scratch; without it the contractions split for themselves.)
+  __nv_bfloat16* planes = nullptr;
+  long long plane_stride = 0;
+  if (a.dtype == HASTE_B200_F32 && (H % 8) == 0) {
+    const size_t pe = Arena::pad((size_t)TN * H * 2) / 2;  // elements per plane
+    planes = static_cast<__nv_bfloat16*>(workspace(s, 2 * pe * 2 + 256, /*slot=*/3));
+    plane_stride = (long long)pe;
+  }
   {
     ProfScope p(PH_REC_BWD, s);
-    if (a.dtype == HASTE_B200_F32) HB_TRY(scan_bwd<float>(a, du_part, db_part, dh_carry, s));
-    else HB_TRY(scan_bwd<__nv_bfloat16>(a, du_part, db_part, dh_carry, s));
+    __nv_bfloat16* sp = a.gamma ? nullptr : planes;
+    if (a.dtype == HASTE_B200_F32) HB_TRY(scan_bwd<float>(a, du_part, db_part, dh_carry, sp, plane_stride, s));
+    else HB_TRY(scan_bwd<__nv_bfloat16>(a, du_part, db_part, dh_carry, nullptr, 0, s));
   }
   HB_TRY(from_float(a.dtype, dh_carry, a.dh, NH, s));
   HB_TRY(colsum(HASTE_B200_F32, du_part, H, N, H, a.dtype, a.du, 1, cs, s));
@@ -196,7 +219,8 @@ int indrnn_backward(const IndrnnBwd& a, cudaStream_t s) {
     ProfScope p(PH_OTHER, s);
     // workspace holds dk = d/d(LN(x.W)); turn it into d/d(x.W) in place.
     HB_TRY(layer_norm_backward(a.dtype, (int)TN, H, a.gamma, a.act_Wx, a.workspace, a.workspace,
-                               a.dtype, a.dgamma, nullptr, a.cache_Wx, lns, s));
+                               a.dtype, a.dgamma, nullptr, a.cache_Wx, lns, s, planes,
+                               plane_stride));
   }
   const bool tr = a.transposed_inputs != 0;
   // dW[C,H] = x^T . dk   (assigned, as in the reference)
@@ -204,12 +228,14 @@ int indrnn_backward(const IndrnnBwd& a, cudaStream_t s) {
               a.dW, H, 0};
   // the backward contractions feed no recurrence: the three-product form is enough also for
   // the LayerNorm variant (six products measured the same 2.6e-5 on a six-layer stack)
+  if (planes) { gw.b_pl = planes; gw.b_pl_ld = H; gw.b_pl_stride = plane_stride; }
   {
     ProfScope p(PH_WGRAD, s);
     HB_TRY(gemm(gw, s));
   }
   GemmDesc gx{a.dtype, a.dtype, (int)TN, C, H, a.workspace, H, 1, a.W, tr ? C : 1, tr ? 1 : H,
               a.dx, C, 0};
+  if (planes) { gx.a_pl = planes; gx.a_pl_ld = H; gx.a_pl_stride = plane_stride; }
   {
     ProfScope p(PH_DGRAD, s);
     HB_TRY(gemm(gx, s));
