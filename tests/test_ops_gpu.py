@@ -29,6 +29,39 @@ def test_gemm_all_layouts(M, N, K, ta, tb, dtype):
     assert_close(got, want + c0.double(), tol, "gemm accumulate")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K,ta,tb", [(256, 256, 64, False, False), (700, 520, 200, False, True),
+                                         (1000, 456, 200, True, False), (2048, 1024, 4096, False, False),
+                                         (512, 2048, 16384, True, False), (1024, 3072, 1024, False, False),
+                                         (4000, 264, 520, True, True)])
+def test_gemm_pair_and_single_cta_kernels(M, N, K, ta, tb, dtype):
+    """Outputs of at least 192 x 192 take the CTA-pair kernel (256 x 256 tiles, cta_group::2);
+    HASTE_B200_GEMM_TCGEN05_SINGLE keeps the single-CTA kernel.  Both against float64, ragged
+    edges, every operand layout, long K (split along K) and many tiles per pair included."""
+    from haste_b200 import _C, ops
+    g = torch.Generator(device="cuda").manual_seed(M + N + K)
+    a = torch.randn((K, M) if ta else (M, K), generator=g, device="cuda").to(dtype)
+    b = torch.randn((N, K) if tb else (K, N), generator=g, device="cuda").to(dtype)
+    av = a.t() if ta else a
+    bv = b.t() if tb else b
+    want = av.double() @ bv.double()
+    tol = TOL_F32 if dtype == torch.float32 else TOL_BF16
+    try:
+        for path in (_C.GEMM_AUTO, _C.GEMM_TCGEN05_SINGLE):
+            _C.set_gemm_path(path)
+            n0 = _C.launch_count()
+            got = ops.gemm(av, bv)
+            torch.cuda.synchronize()
+            _C.sync_check(torch.cuda.current_stream().cuda_stream)
+            assert _C.launch_count() > n0
+            assert_close(got, want, tol, f"gemm path {path}")
+            c0 = torch.randn(M, N, generator=g, device="cuda").to(dtype)
+            got = ops.gemm(av, bv, out=c0.clone(), accumulate=True)
+            assert_close(got, want + c0.double(), tol, f"gemm accumulate path {path}")
+    finally:
+        _C.set_gemm_path(_C.GEMM_AUTO)
+
+
 @pytest.mark.parametrize("rows,width", [(1, 1), (5, 7), (33, 96), (256, 2048), (100, 1536)])
 @pytest.mark.parametrize("with_beta", [False, True])
 def test_layer_norm_forward_backward(rows, width, with_beta):
