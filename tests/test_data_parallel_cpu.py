@@ -159,6 +159,48 @@ def test_two_gloo_ranks_reproduce_the_single_process_gradients(cell):
     assert dict(results) == {0: "ok", 1: "ok"}
 
 
+def _failing_rank_main(rank, port, results):
+    """Rank 1 leaves between steps (it raises on the host before its all-reduce); rank 0's
+    all-reduce then ends with an error inside the process group's short time-out instead of
+    waiting for ever."""
+    import datetime
+    import time
+    from haste_b200 import data_parallel as dp
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=WORLD,
+                            timeout=datetime.timedelta(seconds=5))
+    t = torch.ones(8, dtype=torch.float64) * (rank + 1)
+    dp.all_reduce_tensors([t])  # a step both ranks complete
+    assert torch.equal(t, torch.full((8,), 3.0, dtype=torch.float64))
+    if rank == 1:
+        results[1] = "left"
+        os._exit(0)  # no collective in flight
+    t0 = time.time()
+    try:
+        dp.all_reduce_tensors([t])
+        results[0] = "no error"
+    except Exception as e:  # gloo reports the lost peer or the time-out
+        results[0] = f"error after {time.time() - t0:.1f}s: {type(e).__name__}"
+    os._exit(0)  # the group is unusable; skip its destructor
+
+
+def test_a_rank_that_leaves_ends_the_others_all_reduce_with_an_error():
+    ctx = mp.get_context("spawn")
+    results = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_failing_rank_main, args=(r, port, results)) for r in range(WORLD)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=120)
+    for p in procs:
+        if p.is_alive():
+            p.terminate()
+            pytest.fail("a rank hung on the lost peer")
+    assert results.get(1) == "left"
+    assert str(results.get(0, "")).startswith("error after"), dict(results)
+
+
 def test_shard_rejects_ragged_batches_and_is_identity_for_one_rank():
     from haste_b200 import data_parallel as dp
     x = torch.arange(24.0).reshape(2, 6, 2)
