@@ -115,6 +115,9 @@ int layer_norm_gru_backward(const LnGruBwd& a, cudaStream_t s);
 // Forward: the input projection is already in a.v (LSTM) / a.tmp_Wx (GRU).
 // Backward: carries are fp32 [N,H] buffers, read at entry and written at exit.
 int lstm_forward_persistent(const LstmFwd& a, cudaStream_t s);
+// single-step (Iterate) forward in one launch (iterate_fused.cu); UNSUPPORTED: take the general path
+int lstm_forward_step_fused(const LstmFwd& a, cudaStream_t s);
+int gru_forward_step_fused(const GruFwd& a, cudaStream_t s);
 // Optional bf16 (hi, lo) planes of the gate gradients, written by the persistent backward
 // kernels in fp32 mode (p: dv / dp, p2: dq; lo plane `stride` elements after hi).
 struct GradPlanes {

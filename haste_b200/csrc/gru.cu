@@ -187,6 +187,12 @@ int gru_forward(const GruFwd& a, cudaStream_t s) {
   HB_REQUIRE(a.x, "x is null");
   const long long TN = (long long)a.T * a.N;
   HB_REQUIRE(TN < (1LL << 31), "T*N too large");
+  if (a.T == 1 && a.h_out && recurrence_path() != HASTE_B200_PATH_STEPWISE) {
+    // the per-step (Iterate) form: one fused launch for small batches
+    ProfScope p(PH_REC_FWD, s);
+    const int st_ = gru_forward_step_fused(a, s);
+    if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
+  }
   GemmDesc g{a.dtype, a.dtype, (int)TN, 3 * a.H, a.C, a.x, a.C, 1, a.W, 3LL * a.H, 1, a.tmp_Wx,
              3LL * a.H, 0};
   {

@@ -159,6 +159,12 @@ int lstm_forward(const LstmFwd& a, cudaStream_t s) {
   if (a.T == 0) return HASTE_B200_OK;
   const long long TN = (long long)a.T * a.N;
   HB_REQUIRE(TN < (1LL << 31), "T*N too large");
+  if (a.T == 1 && a.h_out && recurrence_path() != HASTE_B200_PATH_STEPWISE) {
+    // the per-step (Iterate) form: one fused launch for small batches
+    ProfScope p(PH_REC_FWD, s);
+    const int st_ = lstm_forward_step_fused(a, s);
+    if (st_ != HASTE_B200_ERR_UNSUPPORTED) return st_;
+  }
   // v = x . W for all steps at once
   GemmDesc g{a.dtype, a.dtype, (int)TN, 4 * a.H, a.C, a.x, a.C, 1, a.W, 4LL * a.H, 1, a.v,
              4LL * a.H, 0};
