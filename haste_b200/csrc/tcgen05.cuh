@@ -185,7 +185,7 @@ __device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity,
   return true;
 }
 // Tile load into this CTA's shared memory whose completion is counted on an mbarrier of either
-// CTA of the pair (`bar_cluster`: an address from mapa_u32).  No multicast: every CTA fetches
+// CTA of the pair (`bar_cluster`: an address from mapa_u32).  Every CTA fetches
 // its own tiles.
 __device__ __forceinline__ void tma_load_3d_pair(uint32_t dst, const CUtensorMap* map,
                                                  uint32_t bar_cluster, int c0, int c1, int c2) {
