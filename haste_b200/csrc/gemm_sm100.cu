@@ -388,9 +388,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a,
 // both SMs read both halves of B, so every loaded byte feeds twice the arithmetic.  Each CTA's
 // tensor memory holds its 128 rows x 256 columns of the accumulator (two accumulators of 256
 // columns).  CTA 0 of the pair issues all MMAs; its full barriers count the bytes of both
-// CTAs' loads (the loads name the barrier through cta_group::2; every CTA fetches its own tiles), its
-// commits arrive on the empty and accumulator-full barriers of both CTAs, and both CTAs'
-// epilogue warps (eight per CTA: four lane quadrants x two column halves) arrive on its
+// CTAs' loads (the loads name the barrier through cta_group::2; every CTA fetches its own
+// tiles), its commits arrive on the empty and accumulator-full barriers of both CTAs, and both
+// CTAs' epilogue warps (eight per CTA: four lane quadrants x two column halves) arrive on its
 // accumulator-empty barriers.
 constexpr int PAIR_THREADS = 320;        // warp 0 TMA, warp 1 MMA / tensor memory, warps 2..9 epilogue
 constexpr int PBN = 256;                 // columns of the pair's tile and of one accumulator

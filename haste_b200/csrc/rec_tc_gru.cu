@@ -13,10 +13,10 @@
 // * The CTA's slice of R lives in SHARED MEMORY for the whole pass, written once in the
 //   128-byte-swizzled K-major layout that tcgen05.mma reads (96 KB at H = 1024): R is read
 //   from HBM once per pass.
-// * The other operand is streamed every step by TMA (cp.async.bulk.tensor; every CTA fetches its own copy)
-//   straight out of the tensor the step before wrote - h itself in the forward pass, the
-//   gate-gradient tensor dq in the backward pass - through an mbarrier ring; nothing is
-//   packed into a separate exchange buffer.
+// * The other operand is streamed every step by TMA (cp.async.bulk.tensor; every CTA fetches
+//   its own copy) straight out of the tensor the step before wrote - h itself in the forward
+//   pass, the gate-gradient tensor dq in the backward pass - through an mbarrier ring; nothing
+//   is packed into a separate exchange buffer.
 // * The accumulator lives in tensor memory (two buffers, so the tile that follows starts
 //   while this one is drained); four epilogue warps read it with tcgen05.ld, one batch row
 //   per thread, and do the whole gate math, zoneout and the stores for their 16 units.
