@@ -65,7 +65,13 @@ CASES = [
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    # the reference checkout: argument, else $HASTE_REFERENCE_ROOT, else a `reference` directory
+    # beside this repository
+    here = os.path.dirname(os.path.abspath(__file__))
+    sibling = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(here))), "reference")
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("HASTE_REFERENCE_ROOT", sibling)
+    if not os.path.isdir(root):
+        sys.exit("usage: make_golden.py /path/to/haste   (or HASTE_REFERENCE_ROOT=/path/to/haste)")
     ref = import_reference(root)
     script = {
         "lstm": ref.lstm.LSTMScript,
