@@ -73,12 +73,12 @@ def build_torch_ext(force=False):
     import sysconfig
     import torch
     from torch.utils import cpp_extension as ce
-    lib = build()
     header = os.path.join(HERE, "..", "include", "haste_b200.h")
-    if (not force and os.path.exists(TORCH_EXT)
+    if (not force and os.path.exists(TORCH_EXT) and os.path.exists(LIB)
             and os.path.getmtime(TORCH_EXT) > max(os.path.getmtime(TORCH_EXT_SRC),
                                                   os.path.getmtime(header))):
         return TORCH_EXT
+    lib = build()
     cuda_home = os.environ.get("CUDA_HOME", "/usr/local/cuda")
     incs = ce.include_paths() + [sysconfig.get_paths()["include"], os.path.join(HERE, "..", "include"),
                                  os.path.join(cuda_home, "include")]

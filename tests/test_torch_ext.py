@@ -24,7 +24,9 @@ NAMES = [c + p for c in ("lstm", "gru", "indrnn", "layer_norm_lstm", "layer_norm
 @pytest.fixture(scope="module")
 def LIB():
     from haste_b200 import build
-    path = build.build_torch_ext()
+    # the module is built in-tree by `python -m haste_b200.build --torch-ext` (and by the
+    # repository's build entry point); build it here only if that has not happened
+    path = build.TORCH_EXT if os.path.exists(build.TORCH_EXT) else build.build_torch_ext()
     d = os.path.dirname(path)
     if d not in sys.path:
         sys.path.insert(0, d)
