@@ -44,6 +44,12 @@ def _compile(src, force):
 
 
 def build(force=False, verbose=False):
+    # an existing library that is newer than every source and header needs nothing (the object
+    # files may be absent, e.g. on a machine that received only the built library)
+    if not force and os.path.exists(LIB):
+        newest = max([os.path.getmtime(os.path.join(CSRC, f)) for f in sources()] + [_newest_header()])
+        if os.path.getmtime(LIB) > newest:
+            return LIB
     os.makedirs(OBJ, exist_ok=True)
     with ThreadPoolExecutor(max_workers=8) as ex:
         results = list(ex.map(lambda s: _compile(s, force), sources()))
