@@ -66,3 +66,51 @@ def test_compiled_ops_equal_ctypes_ops_and_oracle(LIB, cell, dtype, zoneout):
     assert_close(out_c["h"], ref_out["h"], tol, "h")
     for k in ref_g:
         assert_close(g_c[k], ref_g[k], tol, "d" + k)
+
+
+def _reference_root():
+    env = os.environ.get("HASTE_REFERENCE_ROOT")
+    here = os.path.dirname(os.path.abspath(__file__))
+    sibling = os.path.join(os.path.dirname(os.path.dirname(here)), "reference")
+    root = env or sibling
+    return root if os.path.isdir(os.path.join(root, "frameworks", "pytorch")) else None
+
+
+@pytest.mark.skipif(_reference_root() is None, reason="needs a checkout of the reference")
+def test_the_reference_python_package_binds_to_the_compiled_module(LIB):
+    """`import haste_pytorch_lib as LIB` in the reference's own modules resolves to this
+    repository's compiled module: the package imports unchanged (only its generated version
+    file is stood in for) and every LIB.<op> its autograd functions call exists here."""
+    import importlib.util
+    import re
+    import types
+    pkg_dir = os.path.join(_reference_root(), "frameworks", "pytorch")
+    saved = {k: sys.modules.get(k) for k in ("haste_pytorch", "haste_pytorch._version")}
+    try:
+        ver = types.ModuleType("haste_pytorch._version")
+        ver.__version__ = "reference"
+        sys.modules["haste_pytorch._version"] = ver
+        spec = importlib.util.spec_from_file_location(
+            "haste_pytorch", os.path.join(pkg_dir, "__init__.py"),
+            submodule_search_locations=[pkg_dir])
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules["haste_pytorch"] = mod
+        spec.loader.exec_module(mod)
+        assert mod.lstm.LIB is LIB and mod.layer_norm_gru.LIB is LIB
+        called = set()
+        for name in ("lstm", "gru", "indrnn", "layer_norm_lstm", "layer_norm_gru", "layer_norm_indrnn"):
+            with open(os.path.join(pkg_dir, name + ".py")) as f:
+                called |= set(re.findall(r"LIB\.(\w+)\(", f.read()))
+        assert called == set(NAMES), called ^ set(NAMES)
+        # a CPU model of the reference still runs (its own fallback path), so the import is whole
+        m = mod.LSTM(4, 6)
+        y, _ = m(torch.zeros(3, 2, 4))
+        assert y.shape == (3, 2, 6)
+    finally:
+        for k, v in saved.items():
+            if v is None:
+                sys.modules.pop(k, None)
+            else:
+                sys.modules[k] = v
+        for k in [k for k in sys.modules if k.startswith("haste_pytorch.")]:
+            sys.modules.pop(k, None)
