@@ -560,6 +560,36 @@ class LayerNormIndRNN(BaseRNN):
         return self._permute(h[1:]), state
 
 
+_reversed_index = {}
+
+
+class _FlipTime(torch.autograd.Function):
+    """Time reversal of a `[T, ...]` tensor as a row gather (whole `[N, F]` slabs copied with
+    wide accesses; `torch.flip`'s element-indexed kernel runs at a fifth of the copy bandwidth
+    on these shapes).  Its gradient is the same reversal."""
+
+    @staticmethod
+    def forward(ctx, x):
+        return _flip_rows(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _flip_rows(g)
+
+
+def _flip_rows(x):
+    T = x.shape[0]
+    key = (T, x.device)
+    idx = _reversed_index.get(key)
+    if idx is None:
+        idx = _reversed_index[key] = torch.arange(T - 1, -1, -1, device=x.device)
+    return x.contiguous().index_select(0, idx)
+
+
+def _flip_time(x):
+    return _FlipTime.apply(x)
+
+
 class Stack(nn.Module):
     """`num_layers` layers of one cell type, optionally bidirectional.
 
@@ -613,9 +643,9 @@ class Stack(nn.Module):
             self._side.wait_stream(main)
             with torch.cuda.stream(self._side):
                 x.record_stream(self._side)
-                x_rev = torch.flip(x, [0])
+                x_rev = _flip_time(x)
                 y_bw, _ = level[1](x_rev, **kw[1])
-                y_bw = torch.flip(y_bw, [0])
+                y_bw = _flip_time(y_bw)
             y_fw, _ = level[0](x, **kw[0])
             main.wait_stream(self._side)
             y_bw.record_stream(main)
