@@ -435,12 +435,13 @@ def main():
         "phase_tflops": {k: flops[k] / (phases[k] * 1e-3) / 1e12 for k in flops if phases.get(k)},
     }
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        # about 30 s of host time: the whole workload once or twice where the host manages
-        # that, else a prefix of the sequence
+        # a bounded sample, 10-20 s of host time: the first quarter of the sequence, one warm-up
+        # and three timed runs (the whole workload is what `--impl reference` times; the CPU
+        # path slows down more than in proportion to T, so a shorter sample reads faster)
         threads = os.cpu_count() or 1
-        sample_T, first = _cpu_sample_length(T, N, C, H, threads, 1, 20.0)
-        secs = sorted([first] + [cpu_oracle_step(sample_T, N, C, H, threads)
-                                 for _ in range(2 if first < 8.0 else 0)])
+        sample_T = max(T // 4, 1)
+        cpu_oracle_step(sample_T, N, C, H, threads)
+        secs = sorted(cpu_oracle_step(sample_T, N, C, H, threads) for _ in range(3))
         out["cpu_baseline"] = {"value": N * sample_T / secs[len(secs) // 2], "unit": UNIT,
                                "cores": threads, "kind": "port",
                                "sample": (f"all T={T} steps" if sample_T == T else
